@@ -1,0 +1,21 @@
+// Per-device context shared by every entry point of the library: the stream work is issued on, the
+// device error word the kernels' bounded waits report through, and the SM count used to size
+// persistent grids.
+#pragma once
+#include <cuda_runtime.h>
+#include <string>
+
+struct flux_cuda_ctx {
+  int device = 0;
+  int num_sms = 0;
+  cudaStream_t stream = nullptr;  // owned
+  int *err_dev = nullptr;         // device word, 0 = no kernel reported a failed wait
+  int *err_host = nullptr;        // pinned mirror
+};
+
+namespace fx {
+void set_error(const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+// Synchronises the context's stream and returns FLUX_CUDA_ERR_KERNEL if a kernel recorded an error.
+int ctx_sync_check(flux_cuda_ctx *ctx);
+}  // namespace fx

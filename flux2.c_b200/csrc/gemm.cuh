@@ -1,0 +1,57 @@
+// Host-visible description of one launch of the tcgen05 GEMM  Y[M,N] = X[M,K] * W[N,K]^T
+// (both operands bf16, K contiguous, f32 accumulation in TMEM) and of what its epilogue does with
+// the accumulator. This is the engine's replacement for the reference's flux_linear_nobias /
+// cblas_sgemm call sites (flux_kernels.c:210-320) together with the elementwise passes the
+// reference runs right after each of them.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fx {
+
+enum EpiMode : int {
+  EPI_STORE_BF16 = 0,     // out_bf16[row, col] = acc
+  EPI_STORE_F32 = 1,      // out_f32[row, col] = acc
+  EPI_GATED_RES_F32 = 2,  // out_f32[row, col] += gate[col] * acc   (reference: gated_add, flux_transformer.c:90-97)
+  EPI_SWIGLU_BF16 = 3,    // tile columns [0,128) = gate, [128,256) = up; out_bf16[row, col/2..] = silu(g)*u
+  EPI_STORE_F32_T = 4,    // out_f32[col * ld + row] = acc          (token-major -> channel-major, NLC -> NCHW)
+};
+
+struct EpiSeg {
+  int mode;
+  int col0;           // first destination column of this segment
+  long long ld;       // destination leading dimension in elements
+  void *out;
+  const float *gate;  // EPI_GATED_RES_F32 only; indexed by the segment-relative column
+};
+
+struct alignas(64) GemmProblem {
+  CUtensorMap tmA;  // X  [M, K] bf16, box 64 x 128, 128B swizzle
+  CUtensorMap tmB;  // W  [N, K] bf16, box 64 x BN,  128B swizzle
+  int M, N, K;
+  int n_split;      // output columns [0, n_split) go to seg[0], [n_split, N) to seg[1]
+  EpiSeg seg[2];
+  int tiles_m, tiles_n;
+};
+
+struct alignas(64) GemmParams {
+  GemmProblem p[2];  // up to two independent problems share one persistent launch
+  int nprob;
+  int tiles0;        // tiles of problem 0
+  int total_tiles;
+  int *err;          // device word; first failing role stores a KernelError here
+};
+
+// Fills the tensor maps and tile counts of `p` for tile width bn (128 or 256). Returns 0 on success.
+int gemm_make_problem(GemmProblem *p, const void *X, const void *W, int M, int N, int K, int bn);
+// Launches the persistent kernel over P.nprob problems. bn must match gemm_make_problem.
+int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream);
+int gemm_init();  // resolves cuTensorMapEncodeTiled and opts the kernels into large shared memory
+
+// Tensor-map helper shared with the attention kernel: rank-2 bf16 tensor [rows, cols], cols contiguous,
+// row pitch `ld` elements, box = box_cols x box_rows, 128-byte swizzle.
+int make_tmap_2d_bf16(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols);
+
+}  // namespace fx

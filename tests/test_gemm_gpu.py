@@ -1,0 +1,111 @@
+"""tcgen05 GEMM (K1) against torch matmul in f32 on the same bf16 inputs, through the C ABI."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+# (M, N, K): the shapes one DiT step issues at 512x512 plus ragged / tiny M cases.
+SHAPES = [
+    (128, 256, 64),
+    (128, 256, 256),
+    (256, 512, 3072),
+    (1536, 9216, 3072),
+    (1536, 3072, 12288),
+    (1024, 3072, 9216),
+    (512, 3072, 7680),
+    (48, 3072, 3072),      # M not a multiple of the 128-row tile
+    (200, 768, 128),       # K = 128 (x_embedder), ragged M
+    (1000, 128, 3072),     # N = 128 (proj_out), ragged M
+]
+
+
+def _rel(a, b):
+    return ((a.double() - b.double()).norm() / b.double().norm()).item()
+
+
+def _inputs(M, N, K, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    return x, w
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_store_bf16(fx, ctx, M, N, K):
+    x, w = _inputs(M, N, K)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_BF16)
+    ctx.sync()
+    ref = x.float() @ w.float().t()
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out.float(), ref) < 4e-3  # bf16 output rounding only
+
+
+@pytest.mark.parametrize("M,N,K", [(1536, 3072, 3072), (48, 256, 128), (1000, 128, 3072)])
+def test_gemm_store_f32_exact_accumulation(fx, ctx, M, N, K):
+    x, w = _inputs(M, N, K, seed=1)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_F32, tile_n=128 if N == 128 else 0)
+    ctx.sync()
+    ref = x.double() @ w.double().t()
+    assert _rel(out, ref) < 1e-5  # f32 accumulation of exact bf16 products
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_tile_widths_agree(fx, ctx, tile_n):
+    M, N, K = 300, 1024, 512
+    x, w = _inputs(M, N, K, seed=2)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_F32, tile_n=tile_n)
+    ctx.sync()
+    assert _rel(out, x.double() @ w.double().t()) < 1e-5
+
+
+def test_gemm_gated_residual(fx, ctx):
+    M, N, K = 1536, 3072, 9216
+    x, w = _inputs(M, N, K, seed=3)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    h0 = torch.randn(M, N, device="cuda", generator=g)
+    gate = torch.randn(N, device="cuda", generator=g)
+    h = h0.clone()
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), h.data_ptr(), M, N, K, fx.EPI_GATED_RES_F32, gate_ptr=gate.data_ptr())
+    ctx.sync()
+    ref = h0.double() + gate.double() * (x.double() @ w.double().t())
+    assert _rel(h, ref) < 1e-5
+
+
+def test_gemm_swiglu(fx, ctx):
+    M, Nh, K = 1024, 9216, 3072  # Nh output columns, 2*Nh weight rows
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    wg = (torch.randn(Nh, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(Nh, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    # library layout: per 256 weight rows, 128 gate rows then the 128 matching up rows
+    w = torch.stack([wg.view(Nh // 128, 128, K), wu.view(Nh // 128, 128, K)], dim=1).reshape(2 * Nh, K).contiguous()
+    out = torch.zeros(M, Nh, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, 2 * Nh, K, fx.EPI_SWIGLU_BF16)
+    ctx.sync()
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert _rel(out.float(), ref) < 4e-3
+
+
+def test_gemm_store_transposed(fx, ctx):
+    M, N, K = 1000, 128, 3072
+    x, w = _inputs(M, N, K, seed=6)
+    out = torch.zeros(N, M, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_F32_T, ld_out=M, tile_n=128)
+    ctx.sync()
+    assert _rel(out, (x.double() @ w.double().t()).t()) < 1e-5
+
+
+def test_gemm_rejects_bad_shape(fx, ctx):
+    x, w = _inputs(128, 256, 64)
+    out = torch.zeros(128, 256, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(fx.FluxCudaError):
+        ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), 128, 256, 48, fx.EPI_STORE_BF16)  # K % 64 != 0
