@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 denoising engine on the reference's headline workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --micro gemm|attn|adaln [...]            # one kernel, small memory (for ncu captures)
+
+Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
+(1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
+seed 42. Metric: images/s (whole job). With N > 1 (launched by torchrun, one rank per GPU) every rank holds a
+full replica and denoises its own images: independent seeds, no collective on the data path, weak scaling.
+
+The JSON line also carries the end-to-end figure through the library's host-buffer API (`e2e`), the roofline of
+the dominant kernel (`roofline`) and the reference's CPU path timed on this machine's host cores
+(`cpu_baseline`). `--impl reference` times the reference's own CPU implementation (oracle/_ref, built from the
+reference's sources by oracle/Makefile) instead.
+"""
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+H_LAT, W_LAT, TXT, STEPS_PER_IMAGE = 32, 32, 512, 4
+WORKLOAD = "klein4b_512x512_4step_b1"
+METRIC = "images_per_sec_512x512_4step"
+
+
+def load_package():
+    name = "flux2_c_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    pkg = os.path.join(ROOT, "flux2.c_b200")
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg, "__init__.py"),
+                                                  submodule_search_locations=[pkg])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def step_flops(n_img, n_txt, d):
+    """Algorithmic FLOPs of one DiT forward (2 per MAC; GEMMs + attention), as a dict by kernel class."""
+    h, m, C, T = d.hidden, d.mlp, d.latent_ch, d.text_dim
+    N = n_img + n_txt
+    gemm = d.n_double * N * 2 * (4 * h * h + 3 * h * m) + d.n_single * N * 2 * (h * (3 * h + 2 * m) + (h + m) * h)
+    gemm += 2 * n_img * C * h + 2 * n_img * h * C
+    attn = (d.n_double + d.n_single) * 4 * N * N * h
+    return {"gemm": float(gemm), "attn": float(attn), "ctx_embed_once": float(2 * n_txt * T * h)}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        top = sorted(sm)[len(sm) // 2:]  # samples under load: the upper half (idle samples sit at the low clock)
+        return {"sm_mhz": statistics.median(top), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------- CPU arms
+def cpu_port_baseline(synth, weights, dims, z0, ctx, sched):
+    """The numpy restatement of the reference's forward, timed on the host cores: ONE DiT forward of the
+    512x512 workload (the first of an image's four), images/s = 1 / (4 x that)."""
+    sys.path.insert(0, ROOT)
+    from oracle import flux_oracle as fo
+    om = fo.OracleModel(weights, dims)
+    om.preload()  # bf16 -> f32 expansion of the weights is model loading, not the step
+    t0 = time.perf_counter()
+    om.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
+    dt = time.perf_counter() - t0
+    return {"value": 1.0 / (STEPS_PER_IMAGE * dt), "unit": "images/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": "1 of the 4 DiT forwards of one 512x512 image (%.1f s), x4; numpy f32 + its threaded BLAS" % dt,
+            "ms_per_dit_step": dt * 1e3}
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's own CPU code (oracle/_ref) on the same workload, host cores only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    load_package()
+    import numpy as np
+    import flux2_c_b200.synth as synth
+    import flux2_c_b200 as fx
+    sys.path.insert(0, ROOT)
+    from oracle import ref_binding as rb
+    kind = rb.best_kind()
+    if kind is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (run make -C oracle)"}))
+        return 0
+    dims = synth.Dims.klein4b()
+    tmpdir = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
+    path = os.path.join(tmpdir, "flux_bench_ref_%d.safetensors" % os.getpid())
+    try:
+        W = synth.make_transformer_weights(dims, seed=0)
+        synth.write_safetensors(path, W)
+        del W
+        lib = rb.RefLib(kind)
+        tf = lib.load_transformer(path)
+    finally:
+        if os.path.exists(path):
+            os.remove(path)
+    z0 = fx.init_noise(dims.latent_ch, H_LAT, W_LAT, 42)
+    ctx = synth.make_context(1234, TXT, dims.text_dim)
+    sched = fx.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
+    # one "step" of this arm = a bounded sample of one image: its first DiT forward, scaled by the 4 forwards
+    for _ in range(args.warmup):
+        tf.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tf.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 1.0 / (STEPS_PER_IMAGE * dt)
+    threads = lib.blas_threads
+    sample = "per step: 1 of the 4 DiT forwards of one 512x512 image, x4 (%s build, %d BLAS threads)" % (kind, threads)
+    line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": STEPS_PER_IMAGE * dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": WORKLOAD, "tokens": H_LAT * W_LAT + TXT, "dit_steps_per_image": STEPS_PER_IMAGE},
+            "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": "reference",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "ms_per_dit_step": dt * 1e3}
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------- micro benches
+def run_micro(args):
+    import torch
+    fx = load_package()
+    ctx = fx.Context(0)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    peaks = measured_peaks()
+    iters = args.steps
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        ctx.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+        ctx.sync()
+        return e0.elapsed_time(e1) / iters
+
+    if args.micro == "gemm":
+        M, N, K = args.shape
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K))
+        tf = 2.0 * M * N * K / ms / 1e9
+        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "ms": ms, "tflops": tf, "frac_of_burst_peak":
+                          tf / peaks["bf16"], "peak_source": peaks["source"]}))
+    elif args.micro == "attn":
+        seq, heads = args.seq, 24
+        hid = heads * 128
+        qkv = torch.randn(seq, 3 * hid, device="cuda").to(torch.bfloat16)
+        out = torch.zeros(seq, hid, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        ms = timed(lambda: ctx.attention(qkv.data_ptr(), 1, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid))
+        tf = 4.0 * seq * seq * hid / ms / 1e9
+        print(json.dumps({"micro": "attn", "seq": seq, "heads": heads, "ms": ms, "tflops": tf,
+                          "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]}))
+    elif args.micro == "adaln":
+        rows, hid = args.rows, 3072
+        x = torch.randn(rows, hid, device="cuda")
+        sh = torch.randn(hid, device="cuda")
+        sc = torch.randn(hid, device="cuda")
+        out = torch.zeros(rows, hid, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        ms = timed(lambda: ctx.adaln(x.data_ptr(), out.data_ptr(), rows, hid, sh.data_ptr(), sc.data_ptr()))
+        gbs = rows * hid * 6.0 / ms / 1e6
+        print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
+                          gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------- main arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the engine has no CPU path")
+
+    fx = load_package()
+    import flux2_c_b200.synth as synth
+    dims = synth.Dims.klein4b()
+    ctx = fx.Context(local)
+
+    # ---- model: rank 0 generates the seeded weights once; other ranks read the same file through the loader
+    W = None
+    if world == 1:
+        W = synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count())
+        model = fx.Model.from_tensors(ctx, dims, W)
+    else:
+        shm = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
+        path = os.path.join(shm, "flux_bench_%s.safetensors" % os.environ.get("MASTER_PORT", "0"))
+        if rank == 0:
+            synth.write_safetensors(path, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
+        dist.barrier()
+        model = fx.Model.load_safetensors(ctx, path)
+        dist.barrier()
+        if rank == 0:
+            os.remove(path)
+
+    # ---- inputs: every rank denoises its own image (seed 42 + rank), pinned host buffers
+    n_lat = dims.latent_ch * H_LAT * W_LAT
+    z0 = torch.from_numpy(fx.init_noise(dims.latent_ch, H_LAT, W_LAT, 42 + rank)).pin_memory()
+    cemb = torch.from_numpy(synth.make_context(1234 + rank, TXT, dims.text_dim)).pin_memory()
+    out = torch.zeros(n_lat, dtype=torch.float32).pin_memory()
+    sched = fx.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
+    sampler = fx.Sampler(model, H_LAT, W_LAT, TXT, batch=1, max_steps=STEPS_PER_IMAGE)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        ctx.sync()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing: inputs already in HBM, K images back to back
+    sampler.upload(z0.data_ptr(), cemb.data_ptr())
+    for _ in range(max(3, args.warmup)):
+        sampler.run(sched)
+    barrier()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    with torch.cuda.stream(stream):
+        e0.record()
+        for _ in range(args.steps):
+            sampler.run(sched)
+            launches += sampler.last_run()[1] if False else 0
+        e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = sampler.last_run()[1] * args.steps
+    sampler.download(out.data_ptr())
+    finite = bool(torch.isfinite(out).all())
+
+    # ---- end to end through the host-buffer API: H2D of the inputs and D2H of the latent inside the region
+    for _ in range(2):
+        sampler.upload(z0.data_ptr(), cemb.data_ptr())
+        sampler.run(sched)
+        sampler.download(out.data_ptr())
+    barrier()
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        e0.record()
+    for _ in range(args.steps):
+        sampler.upload(z0.data_ptr(), cemb.data_ptr())
+        sampler.run(sched)
+        sampler.download(out.data_ptr())  # waits for the image
+    with torch.cuda.stream(stream):
+        e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), 0.0))
+    e2e_wall_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    clk = clocks.stop() if rank == 0 else None
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM): per-class CUDA-event times of the same loop
+    fl = step_flops(H_LAT * W_LAT, TXT, dims)
+    prof = None
+    try:
+        sampler.set_profiling(True)
+        sampler.run(sched)
+        ctx.sync()
+        prof = sampler.profile()
+        sampler.set_profiling(False)
+    except AttributeError:
+        pass
+    peaks = measured_peaks()
+    roof = None
+    if prof and prof["gemm"]["ms"] > 0:
+        gemm_flops = STEPS_PER_IMAGE * fl["gemm"] + fl["ctx_embed_once"]
+        ach = gemm_flops / (prof["gemm"]["ms"] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "gemm_bf16_tn_kernel", "achieved": ach, "peak": peaks["bf16_sustained"],
+                "unit": "TFLOP/s", "frac": ach / peaks["bf16_sustained"], "traffic": None,
+                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "launches_per_image": prof["gemm"]["n"],
+                "per_class_ms_per_image": {k: v["ms"] for k, v in prof.items()}}
+
+    images = args.steps * world
+    value = images / (ms_total * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens": H_LAT * W_LAT + TXT, "dit_steps_per_image": STEPS_PER_IMAGE,
+                   "parallelism": "replica_dp%d" % world, "l2": "inputs larger than L2: 7.75 GB of weights per DiT step",
+                   "accumulate": "f32", "residual_stream": "f32"},
+        "ms_per_dit_step": ms_total / args.steps / STEPS_PER_IMAGE,
+        "model_tflops": (STEPS_PER_IMAGE * (fl["gemm"] + fl["attn"]) + fl["ctx_embed_once"]) * args.steps /
+                        (ms_total * 1e-3) / 1e12,
+        "e2e": {"value": images / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(z0.numel() * 4 +
+                cemb.numel() * 4), "d2h_bytes_per_step": int(out.numel() * 4), "wall_ms_per_step":
+                e2e_wall_ms / args.steps},
+        "gpu_launches": int(launches), "finite": finite, "clocks": clk, "roofline": roof,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                line["cpu_baseline"] = cpu_port_baseline(synth, W, dims, z0.numpy().reshape(dims.latent_ch, H_LAT, W_LAT),
+                                                         cemb.numpy(), sched)
+            except Exception as e:  # the baseline must never take the GPU numbers down with it
+                line["cpu_baseline"] = {"error": repr(e)}
+        print(json.dumps(line))
+    sampler.close()
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln"])
+    ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
+    ap.add_argument("--seq", type=int, default=1536)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps == 10:
+            args.steps, args.warmup = 2, 1
+        return run_reference_arm(args)
+    if args.micro:
+        return run_micro(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -50,6 +50,83 @@ def _declare(L):
                                       c_void_p, c_int]
 
 
+    fp = ctypes.POINTER(ctypes.c_float)
+    L.flux_cuda_attention.restype = c_int
+    L.flux_cuda_attention.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_int, c_int, c_int, c_int, c_void_p,
+                                      c_ll, c_int]
+    L.flux_cuda_adaln.restype = c_int
+    L.flux_cuda_adaln.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    L.flux_cuda_qk_norm_rope.restype = c_int
+    L.flux_cuda_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                         c_void_p, c_void_p, c_void_p]
+    L.flux_cuda_dims_klein4b.restype = None
+    L.flux_cuda_dims_klein4b.argtypes = [ctypes.POINTER(CDims)]
+    L.flux_cuda_model_load_safetensors.restype = c_int
+    L.flux_cuda_model_load_safetensors.argtypes = [c_void_p, c_char_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_model_create.restype = c_int
+    L.flux_cuda_model_create.argtypes = [c_void_p, ctypes.POINTER(CDims), ctypes.POINTER(c_void_p)]
+    L.flux_cuda_model_set_tensor.restype = c_int
+    L.flux_cuda_model_set_tensor.argtypes = [c_void_p, c_char_p, c_void_p, c_int, ctypes.POINTER(c_ll), c_int]
+    L.flux_cuda_model_finalize.restype = c_int
+    L.flux_cuda_model_finalize.argtypes = [c_void_p]
+    L.flux_cuda_model_free.restype = None
+    L.flux_cuda_model_free.argtypes = [c_void_p]
+    L.flux_cuda_model_dims.restype = c_int
+    L.flux_cuda_model_dims.argtypes = [c_void_p, ctypes.POINTER(CDims)]
+    L.flux_cuda_forward.restype = c_int
+    L.flux_cuda_forward.argtypes = [c_void_p, fp, c_int, c_int, ctypes.POINTER(CRef), c_int, fp, c_int,
+                                    ctypes.c_float, fp]
+    L.flux_cuda_sample.restype = c_int
+    L.flux_cuda_sample.argtypes = [c_void_p, ctypes.POINTER(CSampleParams), fp, fp, fp]
+    L.flux_cuda_sampler_create.restype = c_int
+    L.flux_cuda_sampler_create.argtypes = [c_void_p, c_int, c_int, c_int, ctypes.POINTER(CRefShape), c_int, c_int,
+                                           c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_sampler_free.restype = None
+    L.flux_cuda_sampler_free.argtypes = [c_void_p]
+    L.flux_cuda_sampler_upload.restype = c_int
+    L.flux_cuda_sampler_upload.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_sampler_run.restype = c_int
+    L.flux_cuda_sampler_run.argtypes = [c_void_p, fp, c_int, ctypes.c_float, c_int, c_int]
+    L.flux_cuda_sampler_download.restype = c_int
+    L.flux_cuda_sampler_download.argtypes = [c_void_p, c_void_p, c_void_p]
+    L.flux_cuda_sampler_last_run.restype = c_int
+    L.flux_cuda_sampler_last_run.argtypes = [c_void_p, fp, ctypes.POINTER(c_ll)]
+    L.flux_cuda_sampler_set_profiling.restype = c_int
+    L.flux_cuda_sampler_set_profiling.argtypes = [c_void_p, c_int]
+    L.flux_cuda_sampler_profile.restype = c_int
+    L.flux_cuda_sampler_profile.argtypes = [c_void_p, fp, ctypes.POINTER(c_ll)]
+    L.flux_cuda_official_schedule.restype = None
+    L.flux_cuda_official_schedule.argtypes = [c_int, c_int, fp]
+    L.flux_cuda_linear_schedule.restype = None
+    L.flux_cuda_linear_schedule.argtypes = [c_int, fp]
+    L.flux_cuda_power_schedule.restype = None
+    L.flux_cuda_power_schedule.argtypes = [c_int, ctypes.c_float, fp]
+    L.flux_cuda_init_noise.restype = None
+    L.flux_cuda_init_noise.argtypes = [c_int, c_int, c_int, c_ll, fp]
+
+
+class CDims(ctypes.Structure):  # flux_cuda_dims
+    _fields_ = [(n, ctypes.c_int) for n in ("hidden", "heads", "head_dim", "mlp", "n_double", "n_single", "text_dim",
+                                            "latent_ch", "time_dim")] + [("rope_theta", ctypes.c_float),
+                                                                         ("axis_dim", ctypes.c_int)]
+
+
+class CRef(ctypes.Structure):  # flux_cuda_ref
+    _fields_ = [("latent", ctypes.POINTER(ctypes.c_float)), ("h", ctypes.c_int), ("w", ctypes.c_int),
+                ("t_offset", ctypes.c_int)]
+
+
+class CRefShape(ctypes.Structure):  # flux_cuda_ref_shape
+    _fields_ = [("h", ctypes.c_int), ("w", ctypes.c_int), ("t_offset", ctypes.c_int)]
+
+
+class CSampleParams(ctypes.Structure):  # flux_cuda_sample_params
+    _fields_ = [("h", ctypes.c_int), ("w", ctypes.c_int), ("num_steps", ctypes.c_int),
+                ("schedule", ctypes.POINTER(ctypes.c_float)), ("ctx", ctypes.POINTER(ctypes.c_float)),
+                ("ctx_uncond", ctypes.POINTER(ctypes.c_float)), ("txt_seq", ctypes.c_int),
+                ("guidance", ctypes.c_float), ("refs", ctypes.POINTER(CRef)), ("num_refs", ctypes.c_int)]
+
+
 def check(rc):
     if rc != 0:
         raise FluxCudaError("flux_cuda error %d: %s" % (rc, lib().flux_cuda_last_error().decode()))
@@ -88,3 +165,189 @@ class Context:
             ld_out = N // 2 if epilogue == EPI_SWIGLU_BF16 else N
         check(lib().flux_cuda_gemm_bf16(self.handle, x_ptr, w_ptr, out_ptr, M, N, K, epilogue, ld_out, gate_ptr,
                                         tile_n))
+
+    def attention(self, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr, out_ld, out_col=0):
+        check(lib().flux_cuda_attention(self.handle, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr,
+                                        out_ld, out_col))
+
+    def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr):
+        check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr))
+
+    def qk_norm_rope(self, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr, cos_ptr, sin_ptr):
+        check(lib().flux_cuda_qk_norm_rope(self.handle, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr,
+                                           cos_ptr, sin_ptr))
+
+
+# ------------------------------------------------------------------------------------------------ host helpers
+def _np():
+    import numpy as np
+    return np
+
+
+def _fp(a):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def official_schedule(num_steps, image_seq_len):
+    """flux_official_schedule: num_steps + 1 timesteps from 1 to 0 (computed by the C library's host code)."""
+    np = _np()
+    out = np.zeros(num_steps + 1, dtype=np.float32)
+    lib().flux_cuda_official_schedule(num_steps, image_seq_len, _fp(out))
+    return out
+
+
+def linear_schedule(num_steps):
+    np = _np()
+    out = np.zeros(num_steps + 1, dtype=np.float32)
+    lib().flux_cuda_linear_schedule(num_steps, _fp(out))
+    return out
+
+
+def power_schedule(num_steps, alpha):
+    np = _np()
+    out = np.zeros(num_steps + 1, dtype=np.float32)
+    lib().flux_cuda_power_schedule(num_steps, alpha, _fp(out))
+    return out
+
+
+def init_noise(channels, h, w, seed):
+    """flux_init_noise: the reference's size-independent seeded noise, f32 [channels, h, w]."""
+    np = _np()
+    out = np.zeros((channels, h, w), dtype=np.float32)
+    lib().flux_cuda_init_noise(channels, h, w, seed, _fp(out))
+    return out
+
+
+_DTYPES = {"float32": 0, "float16": 1, "uint16": 2}  # uint16 arrays carry bf16 bit patterns
+
+
+class Model:
+    """The DiT on one GPU. Mirrors flux_transformer_load_safetensors / flux_transformer_forward* / flux_sample_euler*."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    @staticmethod
+    def load_safetensors(ctx, path):
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_model_load_safetensors(ctx.handle, path.encode(), ctypes.byref(h)))
+        return Model(ctx, h)
+
+    @staticmethod
+    def from_tensors(ctx, dims, tensors):
+        """dims: object with the fields of flux_cuda_dims; tensors: name -> numpy array (uint16 = bf16 bits)."""
+        cd = CDims()
+        for name, _ in CDims._fields_:
+            setattr(cd, name, getattr(dims, name))
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_model_create(ctx.handle, ctypes.byref(cd), ctypes.byref(h)))
+        m = Model(ctx, h)
+        np = _np()
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            shape = (ctypes.c_longlong * arr.ndim)(*arr.shape)
+            check(lib().flux_cuda_model_set_tensor(h, name.encode(), arr.ctypes.data, _DTYPES[str(arr.dtype)], shape,
+                                                   arr.ndim))
+        check(lib().flux_cuda_model_finalize(h))
+        return m
+
+    def dims(self):
+        cd = CDims()
+        check(lib().flux_cuda_model_dims(self.handle, ctypes.byref(cd)))
+        return cd
+
+    @staticmethod
+    def _refs(refs):
+        np = _np()
+        keep = [np.ascontiguousarray(lat, dtype=np.float32) for lat, _ in refs]
+        arr = (CRef * max(1, len(refs)))()
+        for i, (lat, toff) in enumerate(refs):
+            arr[i].latent = _fp(keep[i])
+            arr[i].h, arr[i].w, arr[i].t_offset = keep[i].shape[1], keep[i].shape[2], toff
+        return arr, keep
+
+    def forward(self, z, h, w, ctx_emb, t, refs=()):
+        """Velocity [C, h, w] for latent z at timestep t; refs = [(latent [C, rh, rw], t_offset), ...]."""
+        np = _np()
+        z = np.ascontiguousarray(z, dtype=np.float32)
+        ctx_emb = np.ascontiguousarray(ctx_emb, dtype=np.float32)
+        out = np.empty_like(z)
+        arr, keep = self._refs(refs)
+        check(lib().flux_cuda_forward(self.handle, _fp(z), h, w, arr, len(refs), _fp(ctx_emb), ctx_emb.shape[0], t,
+                                      _fp(out)))
+        return out
+
+    def sample(self, z0, h, w, ctx_emb, schedule, ctx_uncond=None, guidance=1.0, refs=(), return_velocities=False):
+        """Euler loop on the device; with ctx_uncond the guidance pair runs as a batch of two."""
+        np = _np()
+        z0 = np.ascontiguousarray(z0, dtype=np.float32)
+        ctx_emb = np.ascontiguousarray(ctx_emb, dtype=np.float32)
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        steps = len(sch) - 1
+        p = CSampleParams()
+        p.h, p.w, p.num_steps, p.schedule, p.ctx, p.txt_seq = h, w, steps, _fp(sch), _fp(ctx_emb), ctx_emb.shape[0]
+        if ctx_uncond is not None:
+            ctx_uncond = np.ascontiguousarray(ctx_uncond, dtype=np.float32)
+            p.ctx_uncond = _fp(ctx_uncond)
+        p.guidance = guidance
+        arr, keep = self._refs(refs)
+        p.refs, p.num_refs = arr, len(refs)
+        out = np.empty_like(z0)
+        vel = np.empty((steps,) + z0.shape, dtype=np.float32) if return_velocities else None
+        check(lib().flux_cuda_sample(self.handle, ctypes.byref(p), _fp(z0), _fp(out),
+                                     _fp(vel) if vel is not None else None))
+        return (out, vel) if return_velocities else out
+
+    def close(self):
+        if self.handle:
+            lib().flux_cuda_model_free(self.handle)
+            self.handle = ctypes.c_void_p()
+
+
+class Sampler:
+    """Buffers for one (h, w, txt_seq, refs, batch) shape: upload / run / download as separate phases."""
+
+    def __init__(self, model, h, w, txt_seq, ref_shapes=(), batch=1, max_steps=4):
+        self.model = model
+        arr = (CRefShape * max(1, len(ref_shapes)))()
+        for i, (rh, rw, toff) in enumerate(ref_shapes):
+            arr[i].h, arr[i].w, arr[i].t_offset = rh, rw, toff
+        self.handle = ctypes.c_void_p()
+        check(lib().flux_cuda_sampler_create(model.handle, h, w, txt_seq, arr, len(ref_shapes), batch, max_steps,
+                                             ctypes.byref(self.handle)))
+        self.n_refs = len(ref_shapes)
+
+    def upload(self, z0_ptr, ctx_ptr, ctx_uncond_ptr=None, ref_ptrs=()):
+        """Host pointers (ints) of f32 buffers; pinned memory makes the copies asynchronous."""
+        refs = (ctypes.c_void_p * max(1, len(ref_ptrs)))(*ref_ptrs)
+        check(lib().flux_cuda_sampler_upload(self.handle, z0_ptr, ctx_ptr, ctx_uncond_ptr, refs))
+
+    def run(self, schedule, guidance=1.0, record_velocities=False, apply_update=True):
+        np = _np()
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        check(lib().flux_cuda_sampler_run(self.handle, _fp(sch), len(sch) - 1, guidance, int(record_velocities),
+                                          int(apply_update)))
+
+    def download(self, latent_ptr, velocities_ptr=None):
+        check(lib().flux_cuda_sampler_download(self.handle, latent_ptr, velocities_ptr))
+
+    def last_run(self):
+        ms = ctypes.c_float()
+        n = ctypes.c_longlong()
+        check(lib().flux_cuda_sampler_last_run(self.handle, ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
+
+    def set_profiling(self, on):
+        check(lib().flux_cuda_sampler_set_profiling(self.handle, int(on)))
+
+    def profile(self):
+        """Device ms and launch count per kernel class of the last profiled run (synchronise first)."""
+        ms = (ctypes.c_float * 5)()
+        n = (ctypes.c_longlong * 5)()
+        check(lib().flux_cuda_sampler_profile(self.handle, ms, n))
+        return {k: {"ms": ms[i], "n": n[i]} for i, k in enumerate(("gemm", "attn", "adaln", "qknorm", "other"))}
+
+    def close(self):
+        if self.handle:
+            lib().flux_cuda_sampler_free(self.handle)
+            self.handle = ctypes.c_void_p()

@@ -54,8 +54,8 @@ def build(force=False, verbose=False):
         objs.append(obj)
         cmd = [nvcc] + NVCC_FLAGS + ["-I", INCLUDE, "-I", CSRC, "-c", src, "-o", obj]
         if src.endswith(".c"):
-            cmd = [nvcc, "-O3", "-Xcompiler", "-fPIC,-O3,-Wall", "-I", INCLUDE, "-I", CSRC, "-c", src, "-o", obj]
-        if verbose:
+            cmd = ["gcc", "-O2", "-fPIC", "-Wall", "-I", INCLUDE, "-I", CSRC, "-c", src, "-o", obj]
+        if verbose and not src.endswith(".c"):
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

@@ -6,7 +6,12 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <vector>
+
+#include "attention.cuh"
 #include "context.cuh"
+#include "elementwise.cuh"
+#include "engine.cuh"
 #include "gemm.cuh"
 
 namespace fx {
@@ -76,7 +81,7 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
     flux_cuda_ctx_destroy(c);
     return rc;
   }
-  if (gemm_init() != 0) {
+  if (gemm_init() != 0 || attn_init() != 0 || elementwise_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
     flux_cuda_ctx_destroy(c);
     return FLUX_CUDA_ERR_CUDA;
@@ -118,7 +123,7 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
   if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
   GemmParams P;
   memset(&P, 0, sizeof(P));
-  int rc = gemm_make_problem(&P.p[0], x, w, M, N, K, bn);
+  int rc = gemm_make_problem(&P.p[0], x, K, w, M, N, K, bn);
   if (rc) {
     set_error("gemm: unsupported shape/alignment M=%d N=%d K=%d tile_n=%d (rc %d)", M, N, K, bn, rc);
     return FLUX_CUDA_ERR_ARG;
@@ -136,6 +141,186 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
     return rc <= -8 ? FLUX_CUDA_ERR_CUDA : FLUX_CUDA_ERR_ARG;
   }
   return FLUX_CUDA_OK;
+}
+
+
+int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
+                        int v_col, int heads, void *out, long long out_ld, int out_col) {
+  if (!ctx || !qkv || !out) return FLUX_CUDA_ERR_ARG;
+  AttnParams A;
+  int rc = attn_make_params(&A, qkv, batch, seq, ld, q_col, k_col, v_col, out, out_ld, out_col, heads, ctx->err_dev);
+  if (rc) {
+    set_error("attention: unsupported shape/alignment (rc %d)", rc);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  rc = attn_launch(&A, ctx->stream);
+  if (rc) {
+    set_error("attention: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
+                    const float *scale) {
+  if (!ctx || !x || !out || !shift || !scale) return FLUX_CUDA_ERR_ARG;
+  int rc = launch_adaln(x, out, 0, rows, hidden, rows > 0 ? rows : 1, 0, shift, scale, shift, scale, ctx->stream);
+  if (rc) {
+    set_error("adaln: unsupported hidden size %d or launch failure", hidden);
+    return rc == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
+                           int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t) {
+  if (!ctx || !qkv || !wq || !wk || !cos_t || !sin_t) return FLUX_CUDA_ERR_ARG;
+  int rc = launch_qk_norm_rope(qkv, ld, q_col, k_col, seq, batch, heads, 0, wq, wk, wq, wk, cos_t, sin_t, ctx->stream);
+  if (rc) {
+    set_error("qk_norm_rope: launch failed");
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ model
+void flux_cuda_dims_klein4b(flux_cuda_dims *d) {
+  if (!d) return;
+  d->hidden = 3072;
+  d->heads = 24;
+  d->head_dim = 128;
+  d->mlp = 9216;
+  d->n_double = 5;
+  d->n_single = 20;
+  d->text_dim = 7680;
+  d->latent_ch = 128;
+  d->time_dim = 256;
+  d->rope_theta = 2000.0f;
+  d->axis_dim = 32;
+}
+
+static ModelDims to_dims(const flux_cuda_dims *d) {
+  ModelDims m;
+  m.hidden = d->hidden;
+  m.heads = d->heads;
+  m.head_dim = d->head_dim;
+  m.mlp = d->mlp;
+  m.n_double = d->n_double;
+  m.n_single = d->n_single;
+  m.text_dim = d->text_dim;
+  m.latent_ch = d->latent_ch;
+  m.time_dim = d->time_dim;
+  m.rope_theta = d->rope_theta;
+  m.axis_dim = d->axis_dim;
+  return m;
+}
+
+int flux_cuda_model_create(flux_cuda_ctx *ctx, const flux_cuda_dims *dims, flux_cuda_model **out) {
+  if (!ctx || !dims || !out) return FLUX_CUDA_ERR_ARG;
+  return model_create(ctx, to_dims(dims), out);
+}
+int flux_cuda_model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int dtype,
+                               const long long *shape, int ndim) {
+  return model_set_tensor(m, name, data, dtype, shape, ndim);
+}
+int flux_cuda_model_finalize(flux_cuda_model *m) { return model_finalize(m); }
+void flux_cuda_model_free(flux_cuda_model *m) { model_free(m); }
+int flux_cuda_model_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_model **out) {
+  if (!out) return FLUX_CUDA_ERR_ARG;
+  return model_load_safetensors(ctx, path, out);
+}
+int flux_cuda_model_dims(const flux_cuda_model *m, flux_cuda_dims *o) {
+  if (!m || !o) return FLUX_CUDA_ERR_ARG;
+  const ModelDims &d = m->d;
+  o->hidden = d.hidden;
+  o->heads = d.heads;
+  o->head_dim = d.head_dim;
+  o->mlp = d.mlp;
+  o->n_double = d.n_double;
+  o->n_single = d.n_single;
+  o->text_dim = d.text_dim;
+  o->latent_ch = d.latent_ch;
+  o->time_dim = d.time_dim;
+  o->rope_theta = d.rope_theta;
+  o->axis_dim = d.axis_dim;
+  return FLUX_CUDA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ sampler
+int flux_cuda_sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const flux_cuda_ref_shape *refs,
+                             int num_refs, int batch, int max_steps, flux_cuda_sampler **out) {
+  if (!out) return FLUX_CUDA_ERR_ARG;
+  std::vector<RefSpec> rs;
+  for (int i = 0; i < num_refs && refs; ++i) rs.push_back(RefSpec{refs[i].h, refs[i].w, refs[i].t_offset});
+  return sampler_create(m, h, w, txt_seq, rs.data(), num_refs, batch, max_steps, out);
+}
+void flux_cuda_sampler_free(flux_cuda_sampler *s) { sampler_free(s); }
+int flux_cuda_sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx, const float *ctx_uncond,
+                             const float *const *ref_latents) {
+  return sampler_upload(s, z0, ctx, ctx_uncond, ref_latents);
+}
+int flux_cuda_sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance,
+                          int record_velocities, int apply_update) {
+  return sampler_run(s, schedule, num_steps, guidance, record_velocities, apply_update);
+}
+int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
+  return sampler_download(s, latent_out, velocities_out);
+}
+int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kernel_launches) {
+  if (!s) return FLUX_CUDA_ERR_ARG;
+  if (ms) {
+    int rc = check_cuda(cudaEventElapsedTime(ms, s->ws->ev0, s->ws->ev1), "cudaEventElapsedTime");
+    if (rc) return rc;
+  }
+  if (kernel_launches) *kernel_launches = s->ws->launches;
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_sampler_set_profiling(flux_cuda_sampler *s, int on) {
+  if (!s) return FLUX_CUDA_ERR_ARG;
+  s->ws->profiling = on != 0;
+  return FLUX_CUDA_OK;
+}
+int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class) {
+  return sampler_profile(s, ms_by_class, launches_by_class);
+}
+
+static int run_once(flux_cuda_model *m, int h, int w, const flux_cuda_ref *refs, int num_refs, const float *ctx,
+                    const float *ctx_uncond, int txt_seq, const float *schedule, int num_steps, float guidance,
+                    const float *z0, float *latent_out, float *velocities_out, int apply_update) {
+  if (!m || !z0 || !ctx || !schedule || (num_refs > 0 && !refs)) {
+    set_error("null argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  std::vector<RefSpec> rs;
+  std::vector<const float *> lat;
+  for (int i = 0; i < num_refs; ++i) {
+    rs.push_back(RefSpec{refs[i].h, refs[i].w, refs[i].t_offset});
+    lat.push_back(refs[i].latent);
+  }
+  flux_cuda_sampler *s = nullptr;
+  int rc = sampler_create(m, h, w, txt_seq, rs.data(), num_refs, ctx_uncond ? 2 : 1, num_steps, &s);
+  if (rc) return rc;
+  rc = sampler_upload(s, z0, ctx, ctx_uncond, lat.data());
+  if (!rc) rc = sampler_run(s, schedule, num_steps, guidance, velocities_out != nullptr, apply_update);
+  if (!rc) rc = sampler_download(s, latent_out, velocities_out);
+  else ctx_sync_check(m->ctx);
+  sampler_free(s);
+  return rc;
+}
+
+int flux_cuda_forward(flux_cuda_model *m, const float *z, int h, int w, const flux_cuda_ref *refs, int num_refs,
+                      const float *ctx, int txt_seq, float timestep, float *v_out) {
+  if (!v_out) return FLUX_CUDA_ERR_ARG;
+  const float sched[2] = {timestep, timestep};
+  return run_once(m, h, w, refs, num_refs, ctx, nullptr, txt_seq, sched, 1, 1.0f, z, nullptr, v_out, 0);
+}
+
+int flux_cuda_sample(flux_cuda_model *m, const flux_cuda_sample_params *p, const float *z0, float *latent_out,
+                     float *velocities_out) {
+  if (!p || !latent_out) return FLUX_CUDA_ERR_ARG;
+  return run_once(m, p->h, p->w, p->refs, p->num_refs, p->ctx, p->ctx_uncond, p->txt_seq, p->schedule, p->num_steps,
+                  p->guidance, z0, latent_out, velocities_out, 1);
 }
 
 }  // extern "C"

@@ -1,0 +1,24 @@
+// Parameters of the fused joint-attention kernel (attention.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace fx {
+
+struct alignas(64) AttnParams {
+  CUtensorMap tm;          // [batch, seq, ld] bf16 view of the fused projection output; box 64 x 128 x 1
+  int seq, batch, heads;
+  int q_col, k_col, v_col; // first column of head 0 of Q / K / V inside a row of that buffer
+  void *out;               // bf16 [batch*seq, out_ld]; head h goes to columns out_col + 128*h ..
+  long long out_ld;
+  int out_col;
+  float scale_log2;        // log2(e) / sqrt(head_dim)
+  int *err;
+};
+
+int attn_init();
+int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col, int v_col,
+                     void *out, long long out_ld, int out_col, int heads, int *err);
+int attn_launch(const AttnParams *p, cudaStream_t stream);
+
+}  // namespace fx

@@ -1,0 +1,292 @@
+// Memory-bound kernels of the denoising step: AdaLN (K3), timestep/modulation projections (K4),
+// QK-RMSNorm + 2-axis RoPE (K5), sampler updates (K6), layout/dtype changes at the edges (K7).
+// All are bandwidth-bound: 128-bit accesses, warp-shuffle reductions, f32 statistics.
+#include "elementwise.cuh"
+#include "ptx.cuh"
+
+namespace fx {
+
+// ------------------------------------------------------------------------------------------------
+// K3  AdaLN:  out_bf16[r, :] = (1 + scale) * LayerNorm(x_f32[r, :]) + shift      (no affine, eps 1e-6,
+// biased variance, two-pass like the reference: flux_transformer.c:1021-1046). One warp per row; the
+// row stays in registers between the passes (VPL float4 per lane), so HBM sees one read and one write.
+// ------------------------------------------------------------------------------------------------
+template <int VPL>
+__global__ void __launch_bounds__(256) adaln_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out,
+                                                    int row0, int rows, int hidden, int seq, int n_txt,
+                                                    const float *__restrict__ shift_txt,
+                                                    const float *__restrict__ scale_txt,
+                                                    const float *__restrict__ shift_img,
+                                                    const float *__restrict__ scale_img) {
+  const int local = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (local >= rows) return;
+  const int row = row0 + local;
+  const bool is_txt = (row % seq) < n_txt;  // position inside the [txt ; img ; refs] sequence picks the stream
+  const float *shift = is_txt ? shift_txt : shift_img;
+  const float *scale = is_txt ? scale_txt : scale_img;
+  const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * hidden);
+  float4 v[VPL];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    v[i] = xr[i * 32 + lane];
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = warp_sum(s) / static_cast<float>(hidden);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(hidden) + 1e-6f);
+  const float4 *sh4 = reinterpret_cast<const float4 *>(shift);
+  const float4 *sc4 = reinterpret_cast<const float4 *>(scale);
+  uint2 *o2 = reinterpret_cast<uint2 *>(out + static_cast<size_t>(row) * hidden);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const float4 sh = __ldg(sh4 + i * 32 + lane);
+    const float4 sc = __ldg(sc4 + i * 32 + lane);
+    const float a = fmaf((v[i].x - mean) * rstd, 1.f + sc.x, sh.x);
+    const float b = fmaf((v[i].y - mean) * rstd, 1.f + sc.y, sh.y);
+    const float c = fmaf((v[i].z - mean) * rstd, 1.f + sc.z, sh.z);
+    const float d = fmaf((v[i].w - mean) * rstd, 1.f + sc.w, sh.w);
+    o2[i * 32 + lane] = make_uint2(pack_bf16x2(a, b), pack_bf16x2(c, d));
+  }
+}
+
+int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int seq, int n_txt,
+                 const float *shift_txt, const float *scale_txt, const float *shift_img, const float *scale_img,
+                 cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const int grid = (rows + 7) / 8;
+  __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
+#define FX_ADALN(V)                                                                                               \
+  adaln_kernel<V><<<grid, 256, 0, st>>>(x, o, row0, rows, hidden, seq, n_txt, shift_txt, scale_txt, shift_img, \
+                                        scale_img)
+  switch (hidden) {
+    case 3072: FX_ADALN(24); break;
+    case 256: FX_ADALN(2); break;
+    case 512: FX_ADALN(4); break;
+    case 1024: FX_ADALN(8); break;
+    default: return -1;
+  }
+#undef FX_ADALN
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// ------------------------------------------------------------------------------------------------
+// K5  per-head RMSNorm of Q and K followed by the consecutive-pair rotation (apply_qk_norm,
+// flux_transformer.c:1083-1101; apply_rope_2d, 719-741), in place on the bf16 projection output.
+// One warp per (token, head, q|k): lane l owns elements 4l..4l+3 = two rotation pairs. Rows below
+// `n_txt` use the text stream's norm weights (double-stream blocks), the others the image stream's;
+// cos/sin come from one table over the whole [txt ; img ; refs] sequence.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) qk_norm_rope_kernel(__nv_bfloat16 *__restrict__ qkv, long long ld, int q_col,
+                                                           int k_col, int seq, int batch, int heads, int n_txt,
+                                                           const float *__restrict__ wq_txt,
+                                                           const float *__restrict__ wk_txt,
+                                                           const float *__restrict__ wq_img,
+                                                           const float *__restrict__ wk_img,
+                                                           const float *__restrict__ cos_t,
+                                                           const float *__restrict__ sin_t) {
+  const long long gw = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(batch) * seq * heads * 2;
+  if (gw >= total) return;
+  const int which = static_cast<int>(gw & 1);  // 0 = Q, 1 = K
+  const int head = static_cast<int>((gw >> 1) % heads);
+  const long long tok = (gw >> 1) / heads;  // batch * seq + position
+  const int pos = static_cast<int>(tok % seq);
+  __nv_bfloat16 *p = qkv + tok * ld + (which ? k_col : q_col) + head * 128 + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+  float x0 = bf16_lo(raw.x), x1 = bf16_hi(raw.x), x2 = bf16_lo(raw.y), x3 = bf16_hi(raw.y);
+  const float ss = warp_sum((x0 * x0 + x1 * x1) + (x2 * x2 + x3 * x3));
+  const float rinv = rsqrtf(ss * (1.0f / 128.0f) + 1e-6f);
+  const float *w = (pos < n_txt) ? (which ? wk_txt : wq_txt) : (which ? wk_img : wq_img);
+  const float4 w4 = __ldg(reinterpret_cast<const float4 *>(w) + lane);
+  x0 *= rinv * w4.x;
+  x1 *= rinv * w4.y;
+  x2 *= rinv * w4.z;
+  x3 *= rinv * w4.w;
+  const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cos_t + static_cast<size_t>(pos) * 128) + lane);
+  const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sin_t + static_cast<size_t>(pos) * 128) + lane);
+  const float y0 = x0 * c4.x - x1 * s4.x;
+  const float y1 = x1 * c4.x + x0 * s4.x;
+  const float y2 = x2 * c4.z - x3 * s4.z;
+  const float y3 = x3 * c4.z + x2 * s4.z;
+  *reinterpret_cast<uint2 *>(p) = make_uint2(pack_bf16x2(y0, y1), pack_bf16x2(y2, y3));
+}
+
+int launch_qk_norm_rope(void *qkv, long long ld, int q_col, int k_col, int seq, int batch, int heads, int n_txt,
+                        const float *wq_txt, const float *wk_txt, const float *wq_img, const float *wk_img,
+                        const float *cos_t, const float *sin_t, cudaStream_t st) {
+  const long long total = static_cast<long long>(batch) * seq * heads * 2;
+  if (total <= 0) return 0;
+  const unsigned grid = static_cast<unsigned>((total + 7) / 8);
+  qk_norm_rope_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16 *>(qkv), ld, q_col, k_col, seq, batch,
+                                            heads, n_txt, wq_txt, wk_txt, wq_img, wk_img, cos_t, sin_t);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// ------------------------------------------------------------------------------------------------
+// K4  timestep embedding and modulation projections for up to GEMV_S timesteps at once
+// (get_timestep_embedding + time_embed_forward, flux_transformer.c:940-969; modulation projections,
+// 3226-3234, 3016-3024, 3523-3534). The schedule is known before the loop starts, so the weights
+// (341 MB in bf16 for klein-4B) are streamed once per group of GEMV_S steps instead of once per step
+// (and instead of once per single-stream block, as the reference does).
+//   y[s, r] = act( sum_k W_bf16[r, k] * x_f32[s, k] ),   one warp per output row r.
+// ------------------------------------------------------------------------------------------------
+__global__ void timestep_sincos_kernel(const float *__restrict__ t, int S, int dim, float *__restrict__ out) {
+  const int s = blockIdx.x;
+  const int half = dim / 2;
+  const float log_max = logf(10000.0f);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float freq = expf(-log_max * static_cast<float>(i) / static_cast<float>(half));
+    const float ang = t[s] * 1000.0f * freq;
+    out[static_cast<size_t>(s) * dim + i] = cosf(ang);
+    out[static_cast<size_t>(s) * dim + i + half] = sinf(ang);
+  }
+  (void)S;
+}
+
+template <int S>
+__global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__restrict__ W,
+                                                         const float *__restrict__ x, float *__restrict__ y, int R,
+                                                         int K, int silu_out) {
+  extern __shared__ float xs[];  // [S, K]
+  for (int i = threadIdx.x; i < S * K / 4; i += blockDim.x)
+    reinterpret_cast<float4 *>(xs)[i] = reinterpret_cast<const float4 *>(x)[i];
+  __syncthreads();
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= R) return;
+  const uint4 *wr = reinterpret_cast<const uint4 *>(W + static_cast<size_t>(r) * K);
+  float acc[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) acc[s] = 0.f;
+  for (int i = lane; i < K / 8; i += 32) {
+    const uint4 w = __ldg(wr + i);
+    const float wf[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
+                         bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const float4 a = *reinterpret_cast<const float4 *>(xs + s * K + i * 8);
+      const float4 b = *reinterpret_cast<const float4 *>(xs + s * K + i * 8 + 4);
+      acc[s] += (wf[0] * a.x + wf[1] * a.y) + (wf[2] * a.z + wf[3] * a.w) + (wf[4] * b.x + wf[5] * b.y) +
+                (wf[6] * b.z + wf[7] * b.w);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    float v = warp_sum(acc[s]);
+    if (silu_out) v = v / (1.0f + expf(-v));
+    if (lane == 0) y[static_cast<size_t>(s) * R + r] = v;
+  }
+}
+
+int launch_timestep_sincos(const float *t, int S, int dim, float *out, cudaStream_t st) {
+  timestep_sincos_kernel<<<S, 128, 0, st>>>(t, S, dim, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+int elementwise_init() {
+  cudaError_t e = cudaFuncSetAttribute(gemv_multi_kernel<GEMV_S>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GEMV_S * 12288 * 4);
+  return e == cudaSuccess ? 0 : -2;
+}
+
+// x [S, K] f32 (S <= GEMV_S; unused rows are read as zero padding by the caller's buffer), y [S, R] f32.
+int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int silu_out, cudaStream_t st) {
+  if (K % 8 || K > 12288) return -1;
+  const size_t smem = static_cast<size_t>(GEMV_S) * K * 4;
+  gemv_multi_kernel<GEMV_S><<<(R + 7) / 8, 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
+                                                             silu_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// ------------------------------------------------------------------------------------------------
+// K7  edges: channel-major f32 latents -> token-major bf16 (the NCHW -> NLC transpose of
+// flux_transformer.c:3156-3161 / 3650-3664 fused with the cast), and f32 -> bf16 for the context.
+// ------------------------------------------------------------------------------------------------
+__global__ void pack_tokens_kernel(const float *__restrict__ z, __nv_bfloat16 *__restrict__ tok, int C, int n) {
+  __shared__ float tile[32][33];
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, p = p0 + tx;
+    tile[i][tx] = (c < C && p < n) ? z[static_cast<size_t>(c) * n + p] : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int p = p0 + i, c = c0 + tx;
+    if (p < n && c < C) tok[static_cast<size_t>(p) * C + c] = __float2bfloat16_rn(tile[tx][i]);
+  }
+}
+
+int launch_pack_tokens(const float *z, void *tok, int C, int n, cudaStream_t st) {
+  dim3 grid((n + 31) / 32, (C + 31) / 32);
+  pack_tokens_kernel<<<grid, dim3(32, 8), 0, st>>>(z, reinterpret_cast<__nv_bfloat16 *>(tok), C, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+__global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = in[i];
+    out[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
+int launch_f32_to_bf16(const float *in, void *out, long long n, cudaStream_t st) {
+  if (n % 4) return -1;
+  const long long n4 = n / 4;
+  const int grid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  f32_to_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float4 *>(in), reinterpret_cast<uint2 *>(out), n4);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// ------------------------------------------------------------------------------------------------
+// K6  sampler updates: Euler  z += dt * v  (flux_axpy, flux_kernels.c:126-130; flux_sample.c:248) and
+// the classifier-free-guidance combine  v = v_u + g (v_c - v_u); z += dt * v  (flux_sample.c:495-499).
+// dt is read from the device-resident schedule so that a captured launch works for every step.
+// ------------------------------------------------------------------------------------------------
+__global__ void euler_kernel(float *__restrict__ z, const float *__restrict__ v, const float *__restrict__ sched,
+                             int step, long long n) {
+  const float dt = sched[step + 1] - sched[step];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    z[i] = fmaf(dt, v[i], z[i]);
+}
+
+__global__ void cfg_euler_kernel(float *__restrict__ z, const float *__restrict__ v_cond,
+                                 const float *__restrict__ v_uncond, float *__restrict__ v_out, float g,
+                                 const float *__restrict__ sched, int step, long long n, int apply_update) {
+  const float dt = sched[step + 1] - sched[step];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float vu = v_uncond[i];
+    const float v = vu + g * (v_cond[i] - vu);
+    if (v_out) v_out[i] = v;
+    if (apply_update) z[i] = fmaf(dt, v, z[i]);
+  }
+}
+
+static int ew_grid(long long n) {
+  long long b = (n + 255) / 256;
+  return static_cast<int>(b < 148 * 4 ? (b > 0 ? b : 1) : 148 * 4);
+}
+
+int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st) {
+  euler_kernel<<<ew_grid(n), 256, 0, st>>>(z, v, sched, step, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+int launch_cfg_euler(float *z, const float *v_cond, const float *v_uncond, float *v_out, float g, const float *sched,
+                     int step, long long n, int apply_update, cudaStream_t st) {
+  cfg_euler_kernel<<<ew_grid(n), 256, 0, st>>>(z, v_cond, v_uncond, v_out, g, sched, step, n, apply_update);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+}  // namespace fx

@@ -1,0 +1,780 @@
+// Model residency, the DiT forward pass and the on-device sampler loop.
+//
+// Replaces, behind the C ABI, the reference's flux_transformer_load_safetensors (flux_transformer.c:4411-4656),
+// flux_transformer_forward / _with_refs / _with_multi_refs (3115-3577, 3605-4043) and the Euler samplers
+// flux_sample_euler* / flux_sample_euler_cfg* (flux_sample.c:212-691). The whole loop (steps x forward +
+// update) is queued on one stream; the host sees only the inputs it uploads and the latent it downloads.
+#include "engine.cuh"
+
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "attention.cuh"
+#include "elementwise.cuh"
+#include "flux_cuda.h"
+#include "gemm.cuh"
+
+namespace fx {
+
+typedef __nv_bfloat16 bf16;
+
+// ------------------------------------------------------------------------------------------------ helpers
+static uint16_t f32_to_bf16_host(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return static_cast<uint16_t>((u >> 16) | 0x40);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+static float bf16_to_f32_host(uint16_t b) {
+  uint32_t u = static_cast<uint32_t>(b) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+static float f16_to_f32_host(uint16_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16;
+  int exp = (h >> 10) & 0x1F;
+  uint32_t man = h & 0x3FFu;
+  uint32_t u;
+  if (exp == 0) {
+    if (man == 0) {
+      u = sign;
+    } else {
+      exp = 127 - 15 + 1;
+      while (!(man & 0x400u)) {
+        man <<= 1;
+        --exp;
+      }
+      man &= 0x3FFu;
+      u = sign | (static_cast<uint32_t>(exp) << 23) | (man << 13);
+    }
+  } else if (exp == 31) {
+    u = sign | 0x7F800000u | (man << 13);
+  } else {
+    u = sign | (static_cast<uint32_t>(exp - 15 + 127) << 23) | (man << 13);
+  }
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+template <typename T>
+static int dev_alloc(std::vector<void *> &bag, T **p, size_t count) {
+  void *q = nullptr;
+  const size_t bytes = count * sizeof(T);
+  cudaError_t e = cudaMalloc(&q, bytes ? bytes : 16);
+  if (e != cudaSuccess) {
+    set_error("cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    return FLUX_CUDA_ERR_NOMEM;
+  }
+  bag.push_back(q);
+  *p = reinterpret_cast<T *>(q);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ model
+int model_create(flux_cuda_ctx *ctx, const ModelDims &d, flux_cuda_model **out) {
+  *out = nullptr;
+  if (d.head_dim != 128 || d.heads * d.head_dim != d.hidden || d.hidden % 256 || d.mlp % 128 || (2 * d.mlp) % 256 ||
+      d.text_dim % 64 || d.latent_ch % 64 || d.latent_ch % 128 || d.time_dim % 8 || d.axis_dim * 4 != d.head_dim ||
+      d.n_double < 0 || d.n_single < 0 ||
+      !(d.hidden == 256 || d.hidden == 512 || d.hidden == 1024 || d.hidden == 3072)) {
+    set_error("unsupported model dimensions (head_dim must be 128, hidden in {256,512,1024,3072}, mlp %% 128 == 0)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(ctx->device);
+  flux_cuda_model *m = new flux_cuda_model();
+  m->ctx = ctx;
+  m->d = d;
+  const size_t h = d.hidden, mlp = d.mlp;
+  int rc = 0;
+  auto A = [&](bf16 **p, size_t n) {
+    if (!rc) {
+      rc = dev_alloc(m->allocs, p, n);
+      m->weight_bytes += n * 2;
+    }
+  };
+  auto AF = [&](float **p, size_t n) {
+    if (!rc) rc = dev_alloc(m->allocs, p, n);
+  };
+  A(&m->x_emb, h * d.latent_ch);
+  A(&m->ctx_emb, h * d.text_dim);
+  A(&m->t1, h * d.time_dim);
+  A(&m->t2, h * h);
+  A(&m->mod_all, 17 * h * h);
+  A(&m->proj_out, static_cast<size_t>(d.latent_ch) * h);
+  m->dbl.resize(d.n_double);
+  m->sgl.resize(d.n_single);
+  for (auto &b : m->dbl)
+    for (int s = 0; s < 2; ++s) {
+      A(&b.qkv[s], 3 * h * h);
+      A(&b.out[s], h * h);
+      A(&b.ffin[s], 2 * mlp * h);
+      A(&b.ffout[s], h * mlp);
+      AF(&b.nq[s], 128);
+      AF(&b.nk[s], 128);
+    }
+  for (auto &b : m->sgl) {
+    A(&b.lin1, (3 * h + 2 * mlp) * h);
+    A(&b.lin2, h * (h + mlp));
+    AF(&b.nq, 128);
+    AF(&b.nk, 128);
+  }
+  m->staging_bytes = (3 * h + 2 * mlp) * h * 2;
+  if (!rc) {
+    bf16 *st = nullptr;
+    rc = dev_alloc(m->allocs, &st, m->staging_bytes / 2);
+    m->staging = st;
+  }
+  if (rc) {
+    model_free(m);
+    return rc;
+  }
+  m->expected = 9 + static_cast<size_t>(d.n_double) * 16 + static_cast<size_t>(d.n_single) * 4;
+  *out = m;
+  return 0;
+}
+
+void model_free(flux_cuda_model *m) {
+  if (!m) return;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (void *p : m->allocs) cudaFree(p);
+  delete m;
+}
+
+// Converts `count` elements of the source dtype (0 = F32, 1 = F16, 2 = BF16) to bf16 bits on the host.
+static const uint16_t *to_bf16_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp) {
+  if (dtype == 2) return reinterpret_cast<const uint16_t *>(data);
+  tmp.resize(count);
+  if (dtype == 0) {
+    const float *f = reinterpret_cast<const float *>(data);
+    for (size_t i = 0; i < count; ++i) tmp[i] = f32_to_bf16_host(f[i]);
+  } else {
+    const uint16_t *hh = reinterpret_cast<const uint16_t *>(data);
+    for (size_t i = 0; i < count; ++i) tmp[i] = f32_to_bf16_host(f16_to_f32_host(hh[i]));
+  }
+  return tmp.data();
+}
+
+// dst rows [0, 2*half): per block of 128 output columns, 128 rows of the first half then the matching 128 of the second.
+static int upload_interleaved(flux_cuda_model *m, bf16 *dst, const uint16_t *src, size_t half_rows, size_t cols) {
+  const size_t bytes = 2 * half_rows * cols * 2;
+  if (bytes > m->staging_bytes) return FLUX_CUDA_ERR_ARG;
+  int rc = check_cuda(cudaMemcpy(m->staging, src, bytes, cudaMemcpyHostToDevice), "upload weights");
+  if (rc) return rc;
+  const char *st = reinterpret_cast<const char *>(m->staging);
+  const size_t blk = 128 * cols * 2;
+  for (size_t b = 0; b < half_rows / 128; ++b) {
+    char *d = reinterpret_cast<char *>(dst) + 2 * b * blk;
+    cudaMemcpyAsync(d, st + b * blk, blk, cudaMemcpyDeviceToDevice, m->ctx->stream);
+    cudaMemcpyAsync(d + blk, st + (half_rows / 128 + b) * blk, blk, cudaMemcpyDeviceToDevice, m->ctx->stream);
+  }
+  return check_cuda(cudaStreamSynchronize(m->ctx->stream), "interleave weights");
+}
+
+int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int dtype, const long long *shape,
+                     int ndim) {
+  if (!m || !name || !data || !shape || dtype < 0 || dtype > 2 || ndim < 1 || ndim > 2) {
+    set_error("set_tensor: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(m->ctx->device);
+  const ModelDims &d = m->d;
+  const long long h = d.hidden, mlp = d.mlp;
+  const long long r = shape[0], c = ndim == 2 ? shape[1] : 1;
+  const size_t count = static_cast<size_t>(r) * c;
+  std::vector<uint16_t> tmp;
+  std::string n(name);
+
+  auto want = [&](long long er, long long ec) -> int {
+    if (r != er || c != ec) {
+      set_error("tensor %s has shape [%lld, %lld], expected [%lld, %lld]", name, r, c, er, ec);
+      return FLUX_CUDA_ERR_MODEL;
+    }
+    return 0;
+  };
+  auto plain = [&](bf16 *dst, long long er, long long ec) -> int {
+    int rc = want(er, ec);
+    if (rc) return rc;
+    const uint16_t *src = to_bf16_host(data, dtype, count, tmp);
+    return check_cuda(cudaMemcpy(dst, src, count * 2, cudaMemcpyHostToDevice), "upload weights");
+  };
+  auto vec_f32 = [&](float *dst) -> int {
+    if (ndim != 1 || r != 128) {
+      set_error("tensor %s must have shape [128]", name);
+      return FLUX_CUDA_ERR_MODEL;
+    }
+    float v[128];
+    for (int i = 0; i < 128; ++i) {
+      if (dtype == 0) v[i] = reinterpret_cast<const float *>(data)[i];
+      else if (dtype == 1) v[i] = f16_to_f32_host(reinterpret_cast<const uint16_t *>(data)[i]);
+      else v[i] = bf16_to_f32_host(reinterpret_cast<const uint16_t *>(data)[i]);
+    }
+    return check_cuda(cudaMemcpy(dst, v, sizeof(v), cudaMemcpyHostToDevice), "upload norm weights");
+  };
+
+  int rc = FLUX_CUDA_ERR_MODEL;
+  int idx = -1;
+  char rest[128] = "";
+  if (n == "x_embedder.weight") rc = plain(m->x_emb, h, d.latent_ch);
+  else if (n == "context_embedder.weight") rc = plain(m->ctx_emb, h, d.text_dim);
+  else if (n == "time_guidance_embed.timestep_embedder.linear_1.weight") rc = plain(m->t1, h, d.time_dim);
+  else if (n == "time_guidance_embed.timestep_embedder.linear_2.weight") rc = plain(m->t2, h, h);
+  else if (n == "double_stream_modulation_img.linear.weight") rc = plain(m->mod_all, 6 * h, h);
+  else if (n == "double_stream_modulation_txt.linear.weight") rc = plain(m->mod_all + 6 * h * h, 6 * h, h);
+  else if (n == "single_stream_modulation.linear.weight") rc = plain(m->mod_all + 12 * h * h, 3 * h, h);
+  else if (n == "norm_out.linear.weight") rc = plain(m->mod_all + 15 * h * h, 2 * h, h);
+  else if (n == "proj_out.weight") rc = plain(m->proj_out, d.latent_ch, h);
+  else if (sscanf(name, "transformer_blocks.%d.%127s", &idx, rest) == 2 && idx >= 0 && idx < d.n_double) {
+    DoubleW &b = m->dbl[idx];
+    std::string t(rest);
+    if (t == "attn.norm_q.weight") rc = vec_f32(b.nq[1]);
+    else if (t == "attn.norm_k.weight") rc = vec_f32(b.nk[1]);
+    else if (t == "attn.norm_added_q.weight") rc = vec_f32(b.nq[0]);
+    else if (t == "attn.norm_added_k.weight") rc = vec_f32(b.nk[0]);
+    else if (t == "attn.to_q.weight") rc = plain(b.qkv[1], h, h);
+    else if (t == "attn.to_k.weight") rc = plain(b.qkv[1] + h * h, h, h);
+    else if (t == "attn.to_v.weight") rc = plain(b.qkv[1] + 2 * h * h, h, h);
+    else if (t == "attn.add_q_proj.weight") rc = plain(b.qkv[0], h, h);
+    else if (t == "attn.add_k_proj.weight") rc = plain(b.qkv[0] + h * h, h, h);
+    else if (t == "attn.add_v_proj.weight") rc = plain(b.qkv[0] + 2 * h * h, h, h);
+    else if (t == "attn.to_out.0.weight") rc = plain(b.out[1], h, h);
+    else if (t == "attn.to_add_out.weight") rc = plain(b.out[0], h, h);
+    else if (t == "ff.linear_out.weight") rc = plain(b.ffout[1], h, mlp);
+    else if (t == "ff_context.linear_out.weight") rc = plain(b.ffout[0], h, mlp);
+    else if (t == "ff.linear_in.weight" || t == "ff_context.linear_in.weight") {
+      // rows [0, mlp) = gate, [mlp, 2 mlp) = up (flux_transformer.c:4503-4523)
+      if (!(rc = want(2 * mlp, h)))
+        rc = upload_interleaved(m, b.ffin[t == "ff.linear_in.weight" ? 1 : 0], to_bf16_host(data, dtype, count, tmp),
+                                mlp, h);
+    } else {
+      set_error("unknown tensor %s", name);
+    }
+  } else if (sscanf(name, "single_transformer_blocks.%d.%127s", &idx, rest) == 2 && idx >= 0 && idx < d.n_single) {
+    SingleW &b = m->sgl[idx];
+    std::string t(rest);
+    if (t == "attn.norm_q.weight") rc = vec_f32(b.nq);
+    else if (t == "attn.norm_k.weight") rc = vec_f32(b.nk);
+    else if (t == "attn.to_out.weight") rc = plain(b.lin2, h, h + mlp);
+    else if (t == "attn.to_qkv_mlp_proj.weight") {
+      // rows [Q | K | V | gate | up] (flux_transformer.c:3051-3058): Q, K, V stay; gate/up are interleaved
+      if (!(rc = want(3 * h + 2 * mlp, h))) {
+        const uint16_t *src = to_bf16_host(data, dtype, count, tmp);
+        rc = check_cuda(cudaMemcpy(b.lin1, src, 3 * h * h * 2, cudaMemcpyHostToDevice), "upload weights");
+        if (!rc) rc = upload_interleaved(m, b.lin1 + 3 * h * h, src + 3 * h * h, mlp, h);
+      }
+    } else {
+      set_error("unknown tensor %s", name);
+    }
+  } else {
+    set_error("unknown tensor %s", name);
+  }
+  if (rc == 0) m->seen.insert(n);
+  return rc;
+}
+
+int model_finalize(flux_cuda_model *m) {
+  if (!m) return FLUX_CUDA_ERR_ARG;
+  if (m->seen.size() != m->expected) {
+    set_error("model incomplete: %zu of %zu tensors were provided", m->seen.size(), m->expected);
+    return FLUX_CUDA_ERR_MODEL;
+  }
+  m->finalized = true;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ workspace
+static void build_rope(const ModelDims &d, const Workspace &ws, std::vector<float> &cs, std::vector<float> &sn) {
+  // cos/sin [N, 128] over [txt ; img ; refs]; 4 axes (T, Y, X, L) x 16 frequencies, each duplicated over its
+  // (even, odd) pair (flux_transformer.c:591-779), evaluated in float like the reference.
+  const int ax = d.axis_dim, half = ax / 2, hd = d.head_dim;
+  std::vector<float> fr(half);
+  for (int k = 0; k < half; ++k) fr[k] = 1.0f / powf(d.rope_theta, static_cast<float>(2 * k) / static_cast<float>(ax));
+  cs.assign(static_cast<size_t>(ws.N) * hd, 1.0f);
+  sn.assign(static_cast<size_t>(ws.N) * hd, 0.0f);
+  auto put = [&](int row, int axis, int pos) {
+    for (int k = 0; k < half; ++k) {
+      const float a = static_cast<float>(pos) * fr[k];
+      const float c = cosf(a), s = sinf(a);
+      const size_t o = static_cast<size_t>(row) * hd + axis * ax + 2 * k;
+      cs[o] = cs[o + 1] = c;
+      sn[o] = sn[o + 1] = s;
+    }
+  };
+  for (int i = 0; i < ws.n_txt; ++i) put(i, 3, i);
+  int row = ws.n_txt;
+  for (int y = 0; y < ws.h; ++y)
+    for (int x = 0; x < ws.w; ++x, ++row) {
+      put(row, 1, y);
+      put(row, 2, x);
+    }
+  for (const RefSpec &r : ws.refs)
+    for (int y = 0; y < r.h; ++y)
+      for (int x = 0; x < r.w; ++x, ++row) {
+        put(row, 0, r.t_offset);
+        put(row, 1, y);
+        put(row, 2, x);
+      }
+}
+
+void sampler_free(flux_cuda_sampler *s) {
+  if (!s) return;
+  if (s->ws) {
+    cudaSetDevice(s->model->ctx->device);
+    cudaStreamSynchronize(s->model->ctx->stream);
+    for (void *p : s->ws->allocs) cudaFree(p);
+    for (cudaEvent_t e : s->ws->prof_events) cudaEventDestroy(e);
+    if (s->ws->ev0) cudaEventDestroy(s->ws->ev0);
+    if (s->ws->ev1) cudaEventDestroy(s->ws->ev1);
+    delete s->ws;
+  }
+  delete s;
+}
+
+int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec *refs, int num_refs, int batch,
+                   int max_steps, flux_cuda_sampler **out) {
+  *out = nullptr;
+  if (!m || !m->finalized) {
+    set_error("sampler: model is not finalized");
+    return FLUX_CUDA_ERR_MODEL;
+  }
+  if (h <= 0 || w <= 0 || txt_seq <= 0 || num_refs < 0 || (num_refs && !refs) || batch < 1 || batch > 2 ||
+      max_steps < 1) {
+    set_error("sampler: bad shape h=%d w=%d txt=%d refs=%d batch=%d steps=%d", h, w, txt_seq, num_refs, batch,
+              max_steps);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(m->ctx->device);
+  const ModelDims &d = m->d;
+  flux_cuda_sampler *s = new flux_cuda_sampler();
+  s->model = m;
+  Workspace *ws = s->ws = new Workspace();
+  ws->h = h;
+  ws->w = w;
+  ws->n_txt = txt_seq;
+  ws->n_img = h * w;
+  ws->B = batch;
+  ws->max_steps = (max_steps + GEMV_S - 1) / GEMV_S * GEMV_S;
+  for (int i = 0; i < num_refs; ++i) {
+    if (refs[i].h <= 0 || refs[i].w <= 0) {
+      sampler_free(s);
+      set_error("sampler: bad reference shape");
+      return FLUX_CUDA_ERR_ARG;
+    }
+    ws->refs.push_back(refs[i]);
+    ws->n_ref += refs[i].h * refs[i].w;
+  }
+  ws->N = ws->n_txt + ws->n_img + ws->n_ref;
+  const size_t rows = static_cast<size_t>(ws->B) * ws->N, hid = d.hidden, C = d.latent_ch;
+  const size_t S = ws->max_steps;
+  int rc = 0;
+#define WS_ALLOC(ptr, count) \
+  if (!rc) rc = dev_alloc(ws->allocs, &ws->ptr, (count))
+  WS_ALLOC(hs, rows * hid);
+  WS_ALLOC(txt0, static_cast<size_t>(ws->B) * ws->n_txt * hid);
+  WS_ALLOC(norm, rows * hid);
+  WS_ALLOC(qkv, rows * 3 * hid);
+  WS_ALLOC(cat, rows * (hid + d.mlp));
+  WS_ALLOC(tok, static_cast<size_t>(ws->n_img + ws->n_ref) * C);
+  WS_ALLOC(ctx_bf, static_cast<size_t>(ws->B) * ws->n_txt * d.text_dim);
+  WS_ALLOC(z, C * ws->n_img);
+  WS_ALLOC(v, static_cast<size_t>(ws->B) * C * ws->n_img);
+  WS_ALLOC(vcomb, C * ws->n_img);
+  WS_ALLOC(vel_rec, S * C * ws->n_img);
+  WS_ALLOC(z_in, C * ws->n_img);
+  WS_ALLOC(ctx_in, static_cast<size_t>(ws->B) * ws->n_txt * d.text_dim);
+  WS_ALLOC(ref_in, C * static_cast<size_t>(ws->n_ref ? ws->n_ref : 1));
+  WS_ALLOC(sched, S + 1);
+  WS_ALLOC(tsin, S * d.time_dim);
+  WS_ALLOC(th, S * hid);
+  WS_ALLOC(svec, S * hid);
+  WS_ALLOC(mod, S * 17 * hid);
+  WS_ALLOC(rope_cos, static_cast<size_t>(ws->N) * d.head_dim);
+  WS_ALLOC(rope_sin, static_cast<size_t>(ws->N) * d.head_dim);
+#undef WS_ALLOC
+  if (!rc) rc = check_cuda(cudaEventCreate(&ws->ev0), "cudaEventCreate");
+  if (!rc) rc = check_cuda(cudaEventCreate(&ws->ev1), "cudaEventCreate");
+  if (!rc) {
+    // zero what kernels read before anyone writes it (padding rows of the timestep buffers)
+    cudaMemsetAsync(ws->sched, 0, (S + 1) * 4, m->ctx->stream);
+    cudaMemsetAsync(ws->tsin, 0, S * d.time_dim * 4, m->ctx->stream);
+    cudaMemsetAsync(ws->th, 0, S * hid * 4, m->ctx->stream);
+    cudaMemsetAsync(ws->svec, 0, S * hid * 4, m->ctx->stream);
+    std::vector<float> cs, sn;
+    build_rope(d, *ws, cs, sn);
+    rc = check_cuda(cudaMemcpy(ws->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice), "upload rope");
+    if (!rc) rc = check_cuda(cudaMemcpy(ws->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice), "upload rope");
+  }
+  if (rc) {
+    sampler_free(s);
+    return rc;
+  }
+  *out = s;
+  return 0;
+}
+
+int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, const float *ctx1,
+                   const float *const *ref_latents) {
+  if (!s || !z0 || !ctx0) {
+    set_error("upload: null argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  Workspace *ws = s->ws;
+  const ModelDims &d = s->model->d;
+  cudaStream_t st = s->model->ctx->stream;
+  cudaSetDevice(s->model->ctx->device);
+  if (ws->B == 2 && !ctx1) {
+    set_error("upload: a batch-2 sampler needs two contexts");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  if (ws->refs.size() && !ref_latents) {
+    set_error("upload: reference latents missing");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  const size_t C = d.latent_ch, ctx_n = static_cast<size_t>(ws->n_txt) * d.text_dim;
+  int rc = check_cuda(cudaMemcpyAsync(ws->z_in, z0, C * ws->n_img * 4, cudaMemcpyHostToDevice, st), "upload z");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->ctx_in, ctx0, ctx_n * 4, cudaMemcpyHostToDevice, st), "upload ctx");
+  if (!rc && ws->B == 2)
+    rc = check_cuda(cudaMemcpyAsync(ws->ctx_in + ctx_n, ctx1, ctx_n * 4, cudaMemcpyHostToDevice, st), "upload ctx");
+  size_t off = 0;
+  for (size_t i = 0; !rc && i < ws->refs.size(); ++i) {
+    const size_t n = static_cast<size_t>(ws->refs[i].h) * ws->refs[i].w;
+    if (!ref_latents[i]) {
+      set_error("upload: reference latent %zu is null", i);
+      return FLUX_CUDA_ERR_ARG;
+    }
+    rc = check_cuda(cudaMemcpyAsync(ws->ref_in + off * C, ref_latents[i], C * n * 4, cudaMemcpyHostToDevice, st),
+                    "upload ref");
+    off += n;
+  }
+  return rc;
+}
+
+// ------------------------------------------------------------------------------------------------ forward
+struct Launcher {
+  flux_cuda_model *m;
+  Workspace *ws;
+  cudaStream_t st;
+  int rc = 0;
+
+  void fail(const char *what, int code) {
+    if (!rc) {
+      rc = code <= -8 ? FLUX_CUDA_ERR_CUDA : FLUX_CUDA_ERR_ARG;
+      set_error("%s failed (rc %d, cuda: %s)", what, code, cudaGetErrorString(cudaGetLastError()));
+    }
+  }
+  // begin(cls) ... launch ... count(): counts the launch and, when profiling, brackets it with an event pair
+  void begin(int cls) {
+    if (!ws->profiling) return;
+    if (ws->prof_used * 2 + 2 > ws->prof_events.size()) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+      ws->prof_events.push_back(a);
+      ws->prof_events.push_back(b);
+      ws->prof_class.push_back(cls);
+    }
+    ws->prof_class[ws->prof_used] = cls;
+    cudaEventRecord(ws->prof_events[ws->prof_used * 2], st);
+    open = true;
+  }
+  void count() {
+    ws->launches++;
+    if (open) {
+      cudaEventRecord(ws->prof_events[ws->prof_used * 2 + 1], st);
+      ws->prof_used++;
+      open = false;
+    }
+  }
+  bool open = false;
+
+  static EpiSeg seg(int mode, void *out, long long ld, int col0, const float *gate = nullptr) {
+    EpiSeg s;
+    s.mode = mode;
+    s.col0 = col0;
+    s.ld = ld;
+    s.out = out;
+    s.gate = gate;
+    return s;
+  }
+  // One problem per entry; launched together.
+  struct Prob {
+    const void *X;
+    long long ldx;
+    const void *W;
+    int M, N, K;
+    EpiSeg s0;
+    int n_split;
+    EpiSeg s1;
+  };
+  void gemm(const Prob *pr, int n, int bn) {
+    if (rc) return;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.nprob = n;
+    P.err = m->ctx->err_dev;
+    for (int i = 0; i < n; ++i) {
+      int r = gemm_make_problem(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K, bn);
+      if (r) return fail("gemm_make_problem", r);
+      P.p[i].seg[0] = pr[i].s0;
+      if (pr[i].n_split > 0 && pr[i].n_split < pr[i].N) {
+        P.p[i].n_split = pr[i].n_split;
+        P.p[i].seg[1] = pr[i].s1;
+      }
+    }
+    begin(KC_GEMM);
+    int r = gemm_launch(&P, bn, m->ctx->num_sms, st);
+    count();
+    if (r) return fail("gemm_launch", r);
+  }
+  void adaln(int row0, int rows, const float *sh_t, const float *sc_t, const float *sh_i, const float *sc_i) {
+    if (rc) return;
+    begin(KC_ADALN);
+    int r = launch_adaln(ws->hs, ws->norm, row0, rows, m->d.hidden, ws->N, ws->n_txt, sh_t, sc_t, sh_i, sc_i, st);
+    count();
+    if (r) return fail("adaln", r);
+  }
+  void qknorm(const float *nq_t, const float *nk_t, const float *nq_i, const float *nk_i) {
+    if (rc) return;
+    const int h = m->d.hidden;
+    begin(KC_QKNORM);
+    int r = launch_qk_norm_rope(ws->qkv, 3 * h, 0, h, ws->N, ws->B, m->d.heads, ws->n_txt, nq_t, nk_t, nq_i, nk_i,
+                                ws->rope_cos, ws->rope_sin, st);
+    count();
+    if (r) return fail("qk_norm_rope", r);
+  }
+  void attention() {
+    if (rc) return;
+    const int h = m->d.hidden;
+    AttnParams A;
+    int r = attn_make_params(&A, ws->qkv, ws->B, ws->N, 3 * h, 0, h, 2 * h, ws->cat, h + m->d.mlp, 0, m->d.heads,
+                             m->ctx->err_dev);
+    if (r) return fail("attn_make_params", r);
+    begin(KC_ATTN);
+    r = attn_launch(&A, st);
+    count();
+    if (r) return fail("attn_launch", r);
+  }
+};
+
+// One DiT forward over the workspace's current tokens, using modulation row `step` (ws->mod + step*17h).
+// Writes the velocity of batch element b to ws->v + b*C*n_img (channel-major, like the reference's output).
+static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_t st) {
+  const ModelDims &d = m->d;
+  const int h = d.hidden, mlp = d.mlp, N = ws->N, B = ws->B, n_txt = ws->n_txt, n_it = ws->n_img + ws->n_ref;
+  const int C = d.latent_ch;
+  const long long cat_ld = h + mlp;
+  Launcher L{m, ws, st};
+  const float *mod = ws->mod + static_cast<size_t>(step) * 17 * h;
+  const float *mi = mod, *mt = mod + 6 * h, *ms = mod + 12 * h, *mf = mod + 15 * h;
+
+  // target tokens of the current latent: NCHW f32 -> NLC bf16 (reference tokens were packed once per sample)
+  L.begin(KC_OTHER);
+  if (launch_pack_tokens(ws->z, ws->tok, C, ws->n_img, st)) L.fail("pack_tokens", -8);
+  L.count();
+  // embedders: image tokens every step; the text projection is step-invariant and was computed once
+  {
+    Launcher::Prob pr[2];
+    for (int b = 0; b < B; ++b)
+      pr[b] = {ws->tok, C, m->x_emb, n_it, h, C,
+               Launcher::seg(EPI_STORE_F32, ws->hs + (static_cast<size_t>(b) * N + n_txt) * h, h, 0), 0, {}};
+    L.gemm(pr, B, 256);
+    if (!L.rc &&
+        cudaMemcpy2DAsync(ws->hs, static_cast<size_t>(N) * h * 4, ws->txt0, static_cast<size_t>(n_txt) * h * 4,
+                          static_cast<size_t>(n_txt) * h * 4, B, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      L.fail("copy text stream", -8);
+  }
+
+  // ---- double-stream blocks (flux_transformer.c:1774-1986)
+  for (int blk = 0; blk < d.n_double; ++blk) {
+    const DoubleW &w = m->dbl[blk];
+    Launcher::Prob pr[4];
+    auto per_stream = [&](auto make) {
+      int n = 0;
+      for (int b = 0; b < B; ++b)
+        for (int s = 0; s < 2; ++s) pr[n++] = make(b, s, static_cast<size_t>(b) * N + (s ? n_txt : 0), s ? n_it : n_txt);
+      return n;
+    };
+    L.adaln(0, B * N, mt + 0 * h, mt + 1 * h, mi + 0 * h, mi + 1 * h);
+    int n = per_stream([&](int, int s, size_t row, int M) {
+      return Launcher::Prob{ws->norm + row * h, h, w.qkv[s], M, 3 * h, h,
+                            Launcher::seg(EPI_STORE_BF16, ws->qkv + row * 3 * h, 3 * h, 0), 0, {}};
+    });
+    L.gemm(pr, n, 256);
+    L.qknorm(w.nq[0], w.nk[0], w.nq[1], w.nk[1]);
+    L.attention();
+    n = per_stream([&](int, int s, size_t row, int M) {
+      return Launcher::Prob{ws->cat + row * cat_ld, cat_ld, w.out[s], M, h, h,
+                            Launcher::seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 2 * h), 0, {}};
+    });
+    L.gemm(pr, n, 256);
+    L.adaln(0, B * N, mt + 3 * h, mt + 4 * h, mi + 3 * h, mi + 4 * h);
+    n = per_stream([&](int, int s, size_t row, int M) {
+      return Launcher::Prob{ws->norm + row * h, h, w.ffin[s], M, 2 * mlp, h,
+                            Launcher::seg(EPI_SWIGLU_BF16, ws->cat + row * cat_ld, cat_ld, h), 0, {}};
+    });
+    L.gemm(pr, n, 256);
+    n = per_stream([&](int, int s, size_t row, int M) {
+      return Launcher::Prob{ws->cat + row * cat_ld + h, cat_ld, w.ffout[s], M, h, mlp,
+                            Launcher::seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 5 * h), 0, {}};
+    });
+    L.gemm(pr, n, 256);
+  }
+
+  // ---- single-stream blocks (flux_transformer.c:2992-3109)
+  for (int blk = 0; blk < d.n_single; ++blk) {
+    const SingleW &w = m->sgl[blk];
+    L.adaln(0, B * N, ms, ms + h, ms, ms + h);
+    Launcher::Prob p1{ws->norm, h, w.lin1, B * N, 3 * h + 2 * mlp, h,
+                      Launcher::seg(EPI_STORE_BF16, ws->qkv, 3 * h, 0), 3 * h,
+                      Launcher::seg(EPI_SWIGLU_BF16, ws->cat, cat_ld, h)};
+    L.gemm(&p1, 1, 256);
+    L.qknorm(w.nq, w.nk, w.nq, w.nk);
+    L.attention();
+    Launcher::Prob p2{ws->cat, cat_ld, w.lin2, B * N, h, h + mlp,
+                      Launcher::seg(EPI_GATED_RES_F32, ws->hs, h, 0, ms + 2 * h), 0, {}};
+    L.gemm(&p2, 1, 256);
+  }
+
+  // ---- final layer on the target tokens only: modulation is (scale, shift) (flux_transformer.c:3523-3552)
+  {
+    Launcher::Prob pr[2];
+    for (int b = 0; b < B; ++b) {
+      const size_t row = static_cast<size_t>(b) * N + n_txt;
+      L.adaln(static_cast<int>(row), ws->n_img, mf + h, mf, mf + h, mf);
+      pr[b] = {ws->norm + row * h, h, m->proj_out, ws->n_img, C, h,
+               Launcher::seg(EPI_STORE_F32_T, ws->v + static_cast<size_t>(b) * C * ws->n_img, ws->n_img, 0), 0, {}};
+    }
+    L.gemm(pr, B, 128);
+  }
+  return L.rc;
+}
+
+// Everything that depends on the inputs but not on the step: bf16 context and its projection, reference
+// tokens, and the timestep MLP + modulation vectors of ALL steps (the schedule is known up front).
+static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_t st) {
+  const ModelDims &d = m->d;
+  const int h = d.hidden, C = d.latent_ch;
+  Launcher L{m, ws, st};
+  const long long ctx_n = static_cast<long long>(ws->B) * ws->n_txt * d.text_dim;
+  L.begin(KC_OTHER);
+  if (launch_f32_to_bf16(ws->ctx_in, ws->ctx_bf, ctx_n, st)) L.fail("f32_to_bf16", -8);
+  L.count();
+  Launcher::Prob pc{ws->ctx_bf, d.text_dim, m->ctx_emb, ws->B * ws->n_txt, h, d.text_dim,
+                    Launcher::seg(EPI_STORE_F32, ws->txt0, h, 0), 0, {}};
+  L.gemm(&pc, 1, 256);
+  size_t off = 0;
+  for (const RefSpec &r : ws->refs) {
+    const int n = r.h * r.w;
+    L.begin(KC_OTHER);
+    if (launch_pack_tokens(ws->ref_in + off * C, ws->tok + (ws->n_img + off) * C, C, n, st)) L.fail("pack refs", -8);
+    L.count();
+    off += n;
+  }
+  L.begin(KC_OTHER);
+  if (launch_timestep_sincos(ws->sched, num_steps, d.time_dim, ws->tsin, st)) L.fail("timestep_sincos", -8);
+  L.count();
+  for (int s0 = 0; s0 < num_steps && !L.rc; s0 += GEMV_S) {
+    L.begin(KC_OTHER);  // the three projections of this group of steps share one event pair
+    int r = launch_gemv_multi(m->t1, ws->tsin + static_cast<size_t>(s0) * d.time_dim,
+                              ws->th + static_cast<size_t>(s0) * h, h, d.time_dim, 1, st);
+    if (!r)  // svec = silu(t_emb): every consumer of t_emb applies SiLU first (flux_transformer.c:3227-3230)
+      r = launch_gemv_multi(m->t2, ws->th + static_cast<size_t>(s0) * h, ws->svec + static_cast<size_t>(s0) * h, h, h,
+                            1, st);
+    if (!r)
+      r = launch_gemv_multi(m->mod_all, ws->svec + static_cast<size_t>(s0) * h,
+                            ws->mod + static_cast<size_t>(s0) * 17 * h, 17 * h, h, 0, st);
+    L.count();
+    if (r) L.fail("modulation gemv", r);
+    ws->launches += 2;
+  }
+  return L.rc;
+}
+
+int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance, int record_velocities,
+                int apply_update) {
+  if (!s || !schedule || num_steps < 1) {
+    set_error("run: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  flux_cuda_model *m = s->model;
+  Workspace *ws = s->ws;
+  if (num_steps > ws->max_steps) {
+    set_error("run: %d steps exceed the sampler's capacity of %d", num_steps, ws->max_steps);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(m->ctx->device);
+  cudaStream_t st = m->ctx->stream;
+  const size_t n = static_cast<size_t>(m->d.latent_ch) * ws->n_img;
+  ws->launches = 0;
+  ws->prof_used = 0;
+  ws->last_steps = num_steps;
+  cudaEventRecord(ws->ev0, st);
+  // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and no
+  // host synchronisation is needed between consecutive runs.
+  int rc = check_cuda(cudaMemcpyAsync(ws->sched, schedule, (num_steps + 1) * 4, cudaMemcpyHostToDevice, st), "schedule");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->z, ws->z_in, n * 4, cudaMemcpyDeviceToDevice, st), "init latent");
+  if (!rc) rc = prepare(m, ws, num_steps, st);
+  for (int i = 0; !rc && i < num_steps; ++i) {
+    rc = forward_step(m, ws, i, st);
+    if (rc) break;
+    const float *v = ws->v;
+    if (ws->B == 2) {
+      // row 0 = conditional, row 1 = unconditional: v = v_u + g (v_c - v_u) (flux_sample.c:495-499)
+      int r = launch_cfg_euler(ws->z, ws->v, ws->v + n, ws->vcomb, guidance, ws->sched, i, static_cast<long long>(n),
+                               apply_update, st);
+      if (r) rc = FLUX_CUDA_ERR_CUDA;
+      v = ws->vcomb;
+      ws->launches++;
+    } else if (apply_update) {
+      if (launch_euler(ws->z, ws->v, ws->sched, i, static_cast<long long>(n), st)) rc = FLUX_CUDA_ERR_CUDA;
+      ws->launches++;
+    }
+    if (!rc && record_velocities)
+      rc = check_cuda(cudaMemcpyAsync(ws->vel_rec + static_cast<size_t>(i) * n, v, n * 4, cudaMemcpyDeviceToDevice, st),
+                      "record velocity");
+  }
+  cudaEventRecord(ws->ev1, st);
+  return rc;
+}
+
+int sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
+  if (!s) return FLUX_CUDA_ERR_ARG;
+  flux_cuda_model *m = s->model;
+  Workspace *ws = s->ws;
+  cudaSetDevice(m->ctx->device);
+  cudaStream_t st = m->ctx->stream;
+  const size_t n = static_cast<size_t>(m->d.latent_ch) * ws->n_img;
+  int rc = 0;
+  if (latent_out) rc = check_cuda(cudaMemcpyAsync(latent_out, ws->z, n * 4, cudaMemcpyDeviceToHost, st), "download");
+  if (!rc && velocities_out)
+    rc = check_cuda(cudaMemcpyAsync(velocities_out, ws->vel_rec, n * 4 * ws->last_steps, cudaMemcpyDeviceToHost, st),
+                    "download velocities");
+  if (!rc) rc = ctx_sync_check(m->ctx);
+  return rc;
+}
+
+int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class) {
+  if (!s || !ms_by_class || !launches_by_class) return FLUX_CUDA_ERR_ARG;
+  Workspace *ws = s->ws;
+  for (int c = 0; c < KC_COUNT; ++c) {
+    ms_by_class[c] = 0.f;
+    launches_by_class[c] = 0;
+  }
+  for (size_t i = 0; i < ws->prof_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ws->prof_events[2 * i], ws->prof_events[2 * i + 1]) != cudaSuccess) {
+      set_error("profile: events not complete (synchronize first)");
+      return FLUX_CUDA_ERR_CUDA;
+    }
+    ms_by_class[ws->prof_class[i]] += ms;
+    launches_by_class[ws->prof_class[i]]++;
+  }
+  return 0;
+}
+
+}  // namespace fx

@@ -1,0 +1,110 @@
+// Device-resident model and sampler state of the denoising engine.
+//
+// Layout in HBM (all row-major):
+//   weights       bf16, [out, in] as in the file; Q/K/V of a stream concatenated to one [3h, h] matrix;
+//                 gate/up halves of every SwiGLU input projection interleaved in 128-row blocks so that
+//                 one 256-column GEMM tile holds matching gate and up columns; the four modulation
+//                 projections concatenated to one [17h, h] matrix; QK-norm vectors f32.
+//   activations   one sequence [txt ; img ; refs] per batch element (batch = 2 only for the
+//                 classifier-free-guidance pair), residual stream f32 [B*N, h]; AdaLN output, fused
+//                 Q|K|V and [attention | mlp] buffers bf16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <set>
+#include <string>
+#include <vector>
+
+#include "context.cuh"
+
+namespace fx {
+
+struct ModelDims {
+  int hidden, heads, head_dim, mlp, n_double, n_single, text_dim, latent_ch, time_dim;
+  float rope_theta;
+  int axis_dim;
+};
+
+struct DoubleW {  // index 0 = text stream, 1 = image stream
+  __nv_bfloat16 *qkv[2], *out[2], *ffin[2], *ffout[2];
+  float *nq[2], *nk[2];
+};
+struct SingleW {
+  __nv_bfloat16 *lin1, *lin2;
+  float *nq, *nk;
+};
+
+struct RefSpec {
+  int h, w, t_offset;
+};
+
+struct Workspace;
+
+}  // namespace fx
+
+struct flux_cuda_model {
+  flux_cuda_ctx *ctx = nullptr;
+  fx::ModelDims d{};
+  __nv_bfloat16 *x_emb = nullptr, *ctx_emb = nullptr, *t1 = nullptr, *t2 = nullptr, *mod_all = nullptr,
+                *proj_out = nullptr;
+  std::vector<fx::DoubleW> dbl;
+  std::vector<fx::SingleW> sgl;
+  std::vector<void *> allocs;
+  void *staging = nullptr;
+  size_t staging_bytes = 0;
+  std::set<std::string> seen;
+  size_t expected = 0;
+  bool finalized = false;
+  size_t weight_bytes = 0;
+};
+
+struct flux_cuda_sampler {
+  flux_cuda_model *model = nullptr;
+  fx::Workspace *ws = nullptr;
+};
+
+namespace fx {
+
+struct Workspace {
+  int h = 0, w = 0, n_txt = 0, n_img = 0, n_ref = 0, N = 0, B = 1, max_steps = 0;
+  std::vector<RefSpec> refs;
+  std::vector<void *> allocs;
+  float *hs = nullptr, *txt0 = nullptr;
+  __nv_bfloat16 *norm = nullptr, *qkv = nullptr, *cat = nullptr, *tok = nullptr, *ctx_bf = nullptr;
+  float *z = nullptr, *v = nullptr, *vcomb = nullptr, *vel_rec = nullptr;
+  float *z_in = nullptr, *ctx_in = nullptr, *ref_in = nullptr;  // raw uploads
+  float *sched = nullptr, *tsin = nullptr, *th = nullptr, *svec = nullptr, *mod = nullptr;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int last_steps = 0;
+  long long launches = 0;  // kernels launched by the last run
+  // optional per-kernel-class timing of a run: one CUDA event pair per launch
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;  // pairs: [2i] before, [2i+1] after launch i
+  std::vector<int> prof_class;
+  size_t prof_used = 0;
+};
+
+enum KernelClass : int { KC_GEMM = 0, KC_ATTN = 1, KC_ADALN = 2, KC_QKNORM = 3, KC_OTHER = 4, KC_COUNT = 5 };
+
+int model_create(flux_cuda_ctx *ctx, const ModelDims &d, flux_cuda_model **out);
+int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int dtype, const long long *shape,
+                     int ndim);
+int model_finalize(flux_cuda_model *m);
+void model_free(flux_cuda_model *m);
+int model_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_model **out);
+
+int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec *refs, int num_refs, int batch,
+                   int max_steps, flux_cuda_sampler **out);
+void sampler_free(flux_cuda_sampler *s);
+int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, const float *ctx1,
+                   const float *const *ref_latents);
+// guidance is used only when the sampler was created with batch 2 (row 0 = conditional context).
+int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance, int record_velocities,
+                int apply_update);
+int sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
+// Sums the event pairs of the last profiled run per kernel class (call after a sync).
+int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
+
+}  // namespace fx

@@ -35,16 +35,20 @@ struct alignas(64) GemmProblem {
   int tiles_m, tiles_n;
 };
 
+static constexpr int GEMM_MAX_PROBLEMS = 4;
+
 struct alignas(64) GemmParams {
-  GemmProblem p[2];  // up to two independent problems share one persistent launch
+  GemmProblem p[GEMM_MAX_PROBLEMS];  // independent problems sharing one persistent launch (e.g. the text and
+                                     // image streams of a double-stream block, per batch element)
   int nprob;
-  int tiles0;        // tiles of problem 0
+  int tile_end[GEMM_MAX_PROBLEMS];   // exclusive prefix sums of the problems' tile counts
   int total_tiles;
   int *err;          // device word; first failing role stores a KernelError here
 };
 
 // Fills the tensor maps and tile counts of `p` for tile width bn (128 or 256). Returns 0 on success.
-int gemm_make_problem(GemmProblem *p, const void *X, const void *W, int M, int N, int K, int bn);
+// ldx = row pitch of X in elements (>= K), so X may be a column slice of a wider buffer.
+int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn);
 // Launches the persistent kernel over P.nprob problems. bn must match gemm_make_problem.
 int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream);
 int gemm_init();  // resolves cuTensorMapEncodeTiled and opts the kernels into large shared memory

@@ -193,8 +193,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
     atomicCAS(P.err, 0, code);
   };
   auto decode = [&](int tile, int &prob, int &m0, int &n0) {
-    prob = (tile >= P.tiles0) ? 1 : 0;
-    const int local = tile - (prob ? P.tiles0 : 0);
+    prob = 0;
+    while (prob + 1 < P.nprob && tile >= P.tile_end[prob]) ++prob;
+    const int local = tile - (prob ? P.tile_end[prob - 1] : 0);
     const int tm = P.p[prob].tiles_m;
     m0 = (local % tm) * BM;
     n0 = (local / tm) * BN;
@@ -203,11 +204,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&P.p[0].tmA);
-      tma_prefetch_desc(&P.p[0].tmB);
-      if (P.nprob > 1) {
-        tma_prefetch_desc(&P.p[1].tmA);
-        tma_prefetch_desc(&P.p[1].tmB);
+      for (int i = 0; i < P.nprob; ++i) {
+        tma_prefetch_desc(&P.p[i].tmA);
+        tma_prefetch_desc(&P.p[i].tmB);
       }
       uint32_t kiter = 0;
       bool ok = true;
@@ -341,9 +340,9 @@ int make_tmap_2d_bf16(CUtensorMap *m, const void *base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -4;
 }
 
-int gemm_make_problem(GemmProblem *p, const void *X, const void *W, int M, int N, int K, int bn) {
-  if (M <= 0 || N <= 0 || K <= 0 || (K % BK) || (N % bn) || (bn != 128 && bn != 256)) return -5;
-  int rc = make_tmap_2d_bf16(&p->tmA, X, M, K, K, BM, BK);
+int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % BK) || (N % bn) || (bn != 128 && bn != 256) || ldx < K) return -5;
+  int rc = make_tmap_2d_bf16(&p->tmA, X, M, K, ldx, BM, BK);
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&p->tmB, W, N, K, K, bn, BK);
   if (rc) return rc;
@@ -357,8 +356,13 @@ int gemm_make_problem(GemmProblem *p, const void *X, const void *W, int M, int N
 }
 
 int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream) {
-  P->tiles0 = P->p[0].tiles_m * P->p[0].tiles_n;
-  P->total_tiles = P->tiles0 + (P->nprob > 1 ? P->p[1].tiles_m * P->p[1].tiles_n : 0);
+  if (P->nprob < 1 || P->nprob > GEMM_MAX_PROBLEMS) return -5;
+  int acc = 0;
+  for (int i = 0; i < P->nprob; ++i) {
+    acc += P->p[i].tiles_m * P->p[i].tiles_n;
+    P->tile_end[i] = acc;
+  }
+  P->total_tiles = acc;
   for (int i = 0; i < P->nprob; ++i) {
     const GemmProblem &pb = P->p[i];
     if (pb.n_split % bn) return -6;

@@ -37,6 +37,123 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx);
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx);
 
 /* ------------------------------------------------------------------------------------------------
+ * Model: the FLUX.2-klein diffusion transformer resident on one GPU (bf16 weights).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_model flux_cuda_model;
+
+typedef struct flux_cuda_dims {
+  int hidden, heads, head_dim, mlp, n_double, n_single, text_dim, latent_ch, time_dim;
+  float rope_theta;
+  int axis_dim;
+} flux_cuda_dims;
+
+/* The shape the reference hard-codes (flux_transformer.c:4418-4434). */
+void flux_cuda_dims_klein4b(flux_cuda_dims *d);
+
+#define FLUX_CUDA_F32 0
+#define FLUX_CUDA_F16 1
+#define FLUX_CUDA_BF16 2
+
+/*
+ * Loads `transformer/diffusion_pytorch_model.safetensors`. Replaces
+ * flux_transformer_load_safetensors / _mmap (flux_transformer.c:4411-4656, 4659-4786): same tensor
+ * names, but every tensor's shape is checked, dimensions are inferred from the file, and weights
+ * stay bf16 on the device (the mmap streaming mode has no equivalent: 7.75 GB fit in HBM).
+ */
+int flux_cuda_model_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_model **out);
+/* The same, tensor by tensor from host memory (dtype FLUX_CUDA_F32 / F16 / BF16; data is copied). */
+int flux_cuda_model_create(flux_cuda_ctx *ctx, const flux_cuda_dims *dims, flux_cuda_model **out);
+int flux_cuda_model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int dtype,
+                               const long long *shape, int ndim);
+int flux_cuda_model_finalize(flux_cuda_model *m); /* fails if a tensor is missing */
+/* flux_transformer_free (flux_transformer.c:4189-4312); NULL-safe. */
+void flux_cuda_model_free(flux_cuda_model *m);
+int flux_cuda_model_dims(const flux_cuda_model *m, flux_cuda_dims *out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Forward pass and samplers with HOST buffers (the calls the reference's link seam maps onto).
+ * Latents / velocities are f32 [latent_ch, h, w]; contexts f32 [txt_seq, text_dim]; h, w in latent
+ * pixels (image size / 16).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_ref { /* flux_ref_t, flux.c:68-72 */
+  const float *latent;         /* [latent_ch, h, w] */
+  int h, w;
+  int t_offset;                /* RoPE T coordinate: 10, 20, ... */
+} flux_cuda_ref;
+
+/*
+ * One velocity prediction. Replaces flux_transformer_forward (flux_transformer.c:3115-3577),
+ * flux_transformer_forward_with_refs (3605-3799) and _with_multi_refs (3815-4043): num_refs == 0
+ * is the plain forward. v_out receives f32 [latent_ch, h, w].
+ */
+int flux_cuda_forward(flux_cuda_model *m, const float *z, int h, int w, const flux_cuda_ref *refs, int num_refs,
+                      const float *ctx, int txt_seq, float timestep, float *v_out);
+
+typedef struct flux_cuda_sample_params {
+  int h, w;                 /* latent size */
+  int num_steps;
+  const float *schedule;    /* num_steps + 1 timesteps, 1 -> 0 */
+  const float *ctx;         /* conditional context [txt_seq, text_dim] */
+  const float *ctx_uncond;  /* NULL: no guidance (flux_sample_euler*); else flux_sample_euler_cfg* */
+  int txt_seq;
+  float guidance;           /* used only with ctx_uncond */
+  const flux_cuda_ref *refs;
+  int num_refs;
+} flux_cuda_sample_params;
+
+/*
+ * The whole Euler loop on the device. Replaces flux_sample_euler (flux_sample.c:212-290),
+ * _with_refs (303-375), _with_multi_refs (381-444), flux_sample_euler_cfg (457-529), _cfg_with_refs
+ * (534-610), _cfg_with_multi_refs (615-691). With guidance the conditional and unconditional passes
+ * run as one batch of two. z0 is not modified; latent_out receives the final latent;
+ * velocities_out (may be NULL) receives the num_steps velocities the loop used, [num_steps, C, h, w].
+ */
+int flux_cuda_sample(flux_cuda_model *m, const flux_cuda_sample_params *p, const float *z0, float *latent_out,
+                     float *velocities_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * The same loop in three phases, for callers that keep a shape's buffers alive across images and
+ * for measuring the device time without the PCIe copies.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_sampler flux_cuda_sampler;
+typedef struct flux_cuda_ref_shape { int h, w, t_offset; } flux_cuda_ref_shape;
+
+/* batch = 1, or 2 for the guidance pair (element 0 conditional, element 1 unconditional). */
+int flux_cuda_sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const flux_cuda_ref_shape *refs,
+                             int num_refs, int batch, int max_steps, flux_cuda_sampler **out);
+void flux_cuda_sampler_free(flux_cuda_sampler *s);
+/* Asynchronous host -> device copies of the raw f32 inputs (pinned host memory makes them overlap). */
+int flux_cuda_sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx, const float *ctx_uncond,
+                             const float *const *ref_latents);
+/* Queues input preparation + num_steps x (forward, update) on the context's stream; does not wait.
+ * apply_update = 0 leaves the latent untouched (velocity of the uploaded latent at schedule[i]). */
+int flux_cuda_sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance,
+                          int record_velocities, int apply_update);
+/* Device -> host copy of the latent (and recorded velocities), then waits and checks for kernel errors. */
+int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
+/* CUDA-event time of the last flux_cuda_sampler_run in ms (valid after a sync), and its kernel count. */
+int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kernel_launches);
+
+/* Per-kernel-class device time of a run: when on, every launch of the next runs is bracketed by a CUDA
+ * event pair. Classes: 0 GEMM, 1 attention, 2 AdaLN, 3 QK-norm+RoPE, 4 everything else. The reference's
+ * counterpart is its flux_timing_transformer_* wall-clock globals (flux_sample.c:22-39). */
+#define FLUX_CUDA_KERNEL_CLASSES 5
+int flux_cuda_sampler_set_profiling(flux_cuda_sampler *s, int on);
+int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host-side pieces of the sampler (plain C, no GPU involved).
+ * ---------------------------------------------------------------------------------------------- */
+/* flux_official_schedule (flux_sample.c:122-155); out has num_steps + 1 entries. */
+void flux_cuda_official_schedule(int num_steps, int image_seq_len, float *out);
+/* flux_linear_schedule / flux_power_schedule (flux_sample.c:49-69). */
+void flux_cuda_linear_schedule(int num_steps, float *out);
+void flux_cuda_power_schedule(int num_steps, float alpha, float *out);
+/* flux_init_noise (flux_sample.c:835-877) with its xoshiro256** / Box-Muller stream
+ * (flux_kernels.c:45-102): out is f32 [channels, h, w] (batch 1). */
+void flux_cuda_init_noise(int channels, int h, int w, long long seed, float *out);
+
+/* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points on DEVICE pointers (unit tests, microbenchmarks). Asynchronous on the
  * context's stream.
  * ---------------------------------------------------------------------------------------------- */
@@ -60,6 +177,20 @@ void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx);
  */
 int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int N, int K,
                         int epilogue, long long ld_out, const float *gate, int tile_n);
+
+/*
+ * Joint attention over a fused projection buffer qkv[batch*seq, ld] (bf16): for every head,
+ * out[:, out_col + 128*head ..] = softmax(Q K^T / sqrt(128)) V with Q/K/V at columns q_col/k_col/v_col
+ * (+128*head). Replaces mha_forward / joint_attention (flux_transformer.c:1249-1330, 1335-1460).
+ */
+int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
+                        int v_col, int heads, void *out, long long out_ld, int out_col);
+/* apply_adaln (flux_transformer.c:979-1048): out_bf16 = (1 + scale) * LayerNorm(x_f32) + shift, rows x hidden. */
+int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
+                    const float *scale);
+/* apply_qk_norm + apply_rope_2d (flux_transformer.c:1052-1106, 719-741) in place on bf16 Q and K. */
+int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
+                           int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,185 @@
+"""ctypes binding of the reference implementation compiled by oracle/Makefile into oracle/_ref/.
+
+TEST INFRASTRUCTURE ONLY (parity checker and timed CPU baseline). It calls the reference's own
+link-seam symbols (declared extern in flux.c:36-119): safetensors_open, flux_transformer_load_safetensors,
+flux_transformer_forward[_with_multi_refs], flux_sample_euler[_cfg], flux_official_schedule,
+flux_init_noise. The shared objects are built from the reference's sources where they lie; this
+file contains none of them.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.path.join(HERE, "_ref")
+OB_DIR = "/opt/prime-rl/.venv/lib/python3.12/site-packages/opencv_python_headless.libs"
+
+c_float_p = ctypes.POINTER(ctypes.c_float)
+
+
+class FluxRefT(ctypes.Structure):  # flux_ref_t, flux.c:68-72
+    _fields_ = [("latent", c_float_p), ("h", ctypes.c_int), ("w", ctypes.c_int), ("t_offset", ctypes.c_int)]
+
+
+def _preload(prefix):
+    """Loads a wheel-bundled shared object by file-name prefix from any <site-packages>/*.libs directory."""
+    site = os.path.dirname(OB_DIR)
+    for d in [OB_DIR] + sorted(os.path.join(site, x) for x in os.listdir(site) if x.endswith(".libs")):
+        for f in sorted(os.listdir(d)):
+            if f.startswith(prefix):
+                return ctypes.CDLL(os.path.join(d, f), mode=ctypes.RTLD_GLOBAL)
+    raise OSError("no bundled library starting with %s" % prefix)
+
+
+def available(kind="blas"):
+    return os.path.exists(os.path.join(REF_DIR, "libflux_ref_%s.so" % kind))
+
+
+def best_kind():
+    for k in ("blas", "generic"):
+        if available(k):
+            try:
+                RefLib(k)
+                return k
+            except OSError:
+                continue
+    return None
+
+
+def _fp(a):
+    return a.ctypes.data_as(c_float_p)
+
+
+class RefLib:
+    def __init__(self, kind="blas"):
+        path = os.path.join(REF_DIR, "libflux_ref_%s.so" % kind)
+        self.kind = kind
+        if kind == "blas":
+            # the bundled OpenBLAS needs the libgfortran that sits next to it; load both by full path first
+            _preload("libquadmath-2284e583")
+            _preload("libgfortran-83c28eba")
+            _preload("libopenblasp-")
+        self.L = L = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+        self.libc = ctypes.CDLL(None)
+        self.libc.free.argtypes = [ctypes.c_void_p]
+        vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        L.safetensors_open.restype = vp
+        L.safetensors_open.argtypes = [ctypes.c_char_p]
+        L.safetensors_close.argtypes = [vp]
+        L.flux_transformer_load_safetensors.restype = vp
+        L.flux_transformer_load_safetensors.argtypes = [vp]
+        L.flux_transformer_free.argtypes = [vp]
+        L.flux_transformer_forward.restype = vp
+        L.flux_transformer_forward.argtypes = [vp, c_float_p, ci, ci, c_float_p, ci, cf]
+        L.flux_transformer_forward_with_multi_refs.restype = vp
+        L.flux_transformer_forward_with_multi_refs.argtypes = [vp, c_float_p, ci, ci, ctypes.POINTER(FluxRefT), ci,
+                                                               c_float_p, ci, cf]
+        L.flux_sample_euler.restype = vp
+        L.flux_sample_euler.argtypes = [vp, vp, c_float_p, ci, ci, ci, ci, c_float_p, ci, c_float_p, ci, vp]
+        L.flux_sample_euler_with_multi_refs.restype = vp
+        L.flux_sample_euler_with_multi_refs.argtypes = [vp, vp, c_float_p, ci, ci, ci, ci, ctypes.POINTER(FluxRefT),
+                                                        ci, c_float_p, ci, c_float_p, ci, vp]
+        L.flux_sample_euler_cfg.restype = vp
+        L.flux_sample_euler_cfg.argtypes = [vp, vp, c_float_p, ci, ci, ci, ci, c_float_p, ci, c_float_p, ci, cf,
+                                            c_float_p, ci, vp]
+        L.flux_official_schedule.restype = vp
+        L.flux_official_schedule.argtypes = [ci, ci]
+        L.flux_linear_schedule.restype = vp
+        L.flux_linear_schedule.argtypes = [ci]
+        L.flux_power_schedule.restype = vp
+        L.flux_power_schedule.argtypes = [ci, cf]
+        L.flux_init_noise.restype = vp
+        L.flux_init_noise.argtypes = [ci, ci, ci, ci, ctypes.c_int64]
+        if kind == "blas":
+            try:
+                self.blas_threads = L.openblas_get_num_threads()
+            except AttributeError:
+                ob = ctypes.CDLL([os.path.join(OB_DIR, f) for f in os.listdir(OB_DIR) if f.startswith("libopenblasp")][0])
+                self.blas_threads = ob.openblas_get_num_threads()
+        else:
+            self.blas_threads = 1
+
+    def _take(self, ptr, n):
+        if not ptr:
+            raise RuntimeError("reference returned NULL")
+        out = np.ctypeslib.as_array(ctypes.cast(ptr, c_float_p), shape=(n,)).copy()
+        self.libc.free(ptr)
+        return out
+
+    def official_schedule(self, steps, seq_len):
+        return self._take(self.L.flux_official_schedule(steps, seq_len), steps + 1)
+
+    def linear_schedule(self, steps):
+        return self._take(self.L.flux_linear_schedule(steps), steps + 1)
+
+    def power_schedule(self, steps, alpha):
+        return self._take(self.L.flux_power_schedule(steps, alpha), steps + 1)
+
+    def init_noise(self, channels, h, w, seed):
+        return self._take(self.L.flux_init_noise(1, channels, h, w, seed), channels * h * w).reshape(channels, h, w)
+
+    def load_transformer(self, safetensors_path):
+        sf = self.L.safetensors_open(safetensors_path.encode())
+        if not sf:
+            raise RuntimeError("reference could not open %s" % safetensors_path)
+        tf = self.L.flux_transformer_load_safetensors(sf)
+        self.L.safetensors_close(sf)
+        if not tf:
+            raise RuntimeError("reference could not load the transformer")
+        return RefTransformer(self, tf)
+
+
+class RefTransformer:
+    def __init__(self, lib, handle):
+        self.lib, self.h = lib, handle
+
+    def close(self):
+        if self.h:
+            self.lib.L.flux_transformer_free(self.h)
+            self.h = None
+
+    @staticmethod
+    def _refs(refs):
+        keep = [np.ascontiguousarray(lat, dtype=np.float32) for lat, _ in refs]
+        arr = (FluxRefT * max(1, len(refs)))()
+        for i, (lat, toff) in enumerate(refs):
+            arr[i].latent = _fp(keep[i])
+            arr[i].h, arr[i].w, arr[i].t_offset = lat.shape[1], lat.shape[2], toff
+        return arr, keep
+
+    def forward(self, z, h, w, ctx, t, refs=()):
+        z = np.ascontiguousarray(z, dtype=np.float32)
+        ctx = np.ascontiguousarray(ctx, dtype=np.float32)
+        L = self.lib.L
+        if refs:
+            arr, keep = self._refs(refs)
+            p = L.flux_transformer_forward_with_multi_refs(self.h, _fp(z), h, w, arr, len(refs), _fp(ctx),
+                                                           ctx.shape[0], t)
+        else:
+            p = L.flux_transformer_forward(self.h, _fp(z), h, w, _fp(ctx), ctx.shape[0], t)
+        return self.lib._take(p, z.size).reshape(z.shape)
+
+    def sample_euler(self, z0, h, w, ctx, schedule, refs=()):
+        z0 = np.ascontiguousarray(z0, dtype=np.float32).copy()
+        ctx = np.ascontiguousarray(ctx, dtype=np.float32)
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        L = self.lib.L
+        C = z0.shape[0]
+        if refs:
+            arr, keep = self._refs(refs)
+            p = L.flux_sample_euler_with_multi_refs(self.h, None, _fp(z0), 1, C, h, w, arr, len(refs), _fp(ctx),
+                                                    ctx.shape[0], _fp(sch), len(sch) - 1, None)
+        else:
+            p = L.flux_sample_euler(self.h, None, _fp(z0), 1, C, h, w, _fp(ctx), ctx.shape[0], _fp(sch),
+                                    len(sch) - 1, None)
+        return self.lib._take(p, z0.size).reshape(z0.shape)
+
+    def sample_euler_cfg(self, z0, h, w, ctx_c, ctx_u, guidance, schedule):
+        z0 = np.ascontiguousarray(z0, dtype=np.float32).copy()
+        ctx_c = np.ascontiguousarray(ctx_c, dtype=np.float32)
+        ctx_u = np.ascontiguousarray(ctx_u, dtype=np.float32)
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        p = self.lib.L.flux_sample_euler_cfg(self.h, None, _fp(z0), 1, z0.shape[0], h, w, _fp(ctx_c), ctx_c.shape[0],
+                                             _fp(ctx_u), ctx_u.shape[0], guidance, _fp(sch), len(sch) - 1, None)
+        return self.lib._take(p, z0.size).reshape(z0.shape)

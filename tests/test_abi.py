@@ -1,0 +1,45 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/flux_cuda.h declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "flux_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(flux_cuda_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(fx):
+    L = fx.lib()
+    names = declared_symbols()
+    assert len(names) >= 25
+    missing = [n for n in names if not hasattr(L, n)]
+    assert not missing, "declared in flux_cuda.h but not exported: %s" % missing
+
+
+def test_no_cpu_fallback_without_gpu(fx):
+    import torch
+    if torch.cuda.is_available():
+        return
+    h = ctypes.c_void_p()
+    rc = fx.lib().flux_cuda_ctx_create(0, ctypes.byref(h))
+    assert rc != 0 and not h.value
+    assert b"no CUDA device" in fx.lib().flux_cuda_last_error()
+
+
+def test_product_does_not_touch_the_oracle():
+    """Nothing in the package, the headers or the C sources may import, link or read oracle/."""
+    bad = []
+    for base in ("flux2.c_b200", "include"):
+        for dirpath, _, files in os.walk(os.path.join(ROOT, base)):
+            if "build" in dirpath.split(os.sep):
+                continue
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".c", ".cc", ".h")):
+                    src = open(os.path.join(dirpath, f), errors="ignore").read()
+                    if re.search(r"\boracle[/.]|from oracle|import oracle|_ref/", src):
+                        bad.append(os.path.join(dirpath, f))
+    assert not bad, bad

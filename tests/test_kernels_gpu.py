@@ -1,0 +1,81 @@
+"""Attention (K2), AdaLN (K3) and QK-norm+RoPE (K5) kernels against plain torch f32 references, through the C ABI."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.double() - b.double()).norm() / b.double().norm()).item()
+
+
+@pytest.mark.parametrize("batch,seq,heads,sharp", [
+    (1, 128, 1, 1.0), (1, 256, 2, 1.0), (1, 48, 2, 1.0), (1, 300, 3, 3.0), (1, 1536, 24, 1.0), (2, 200, 2, 2.0),
+    (1, 768, 24, 0.02),
+])
+def test_attention_matches_torch(fx, ctx, batch, seq, heads, sharp):
+    hid = heads * 128
+    g = torch.Generator(device="cuda").manual_seed(seq + heads)
+    qkv = (torch.randn(batch * seq, 3 * hid, device="cuda", generator=g) * sharp).to(torch.bfloat16)
+    out_ld = hid + 256  # output lands inside a wider [attention | mlp] buffer
+    out = torch.zeros(batch * seq, out_ld, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), out_ld, 0)
+    ctx.sync()
+    q, k, v = [t.float().reshape(batch, seq, heads, 128).transpose(1, 2) for t in qkv.split(hid, dim=1)]
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(128.0)
+    ref = (torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(batch * seq, hid)
+    assert torch.isfinite(out.float()).all()
+    assert (out[:, hid:] == 0).all()
+    assert _rel(out[:, :hid].float(), ref) < 1e-2  # bf16 P and bf16 output
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (37, 256), (1536, 3072), (1000, 1024)])
+def test_adaln_matches_torch(fx, ctx, rows, hidden):
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = torch.randn(rows, hidden, device="cuda", generator=g) * 3 + 0.5
+    shift = torch.randn(hidden, device="cuda", generator=g)
+    scale = torch.randn(hidden, device="cuda", generator=g)
+    out = torch.zeros(rows, hidden, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.adaln(x.data_ptr(), out.data_ptr(), rows, hidden, shift.data_ptr(), scale.data_ptr())
+    ctx.sync()
+    ref = torch.nn.functional.layer_norm(x, (hidden,), eps=1e-6) * (1 + scale) + shift
+    assert _rel(out.float(), ref) < 4e-3
+
+
+def test_adaln_rejects_unsupported_hidden(fx, ctx):
+    x = torch.zeros(4, 384, device="cuda")
+    o = torch.zeros(4, 384, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(fx.FluxCudaError):
+        ctx.adaln(x.data_ptr(), o.data_ptr(), 4, 384, x.data_ptr(), x.data_ptr())
+
+
+@pytest.mark.parametrize("batch,seq,heads", [(1, 48, 2), (2, 100, 3), (1, 1536, 24)])
+def test_qk_norm_rope_matches_torch(fx, ctx, batch, seq, heads):
+    hid = heads * 128
+    g = torch.Generator(device="cuda").manual_seed(seq)
+    qkv = torch.randn(batch * seq, 3 * hid, device="cuda", generator=g).to(torch.bfloat16)
+    wq = torch.randn(128, device="cuda", generator=g)
+    wk = torch.randn(128, device="cuda", generator=g)
+    ang = torch.rand(seq, 64, device="cuda", generator=g) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, dim=1).contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, dim=1).contiguous()
+    work = qkv.clone()
+    torch.cuda.synchronize()
+    ctx.qk_norm_rope(work.data_ptr(), 3 * hid, 0, hid, seq, batch, heads, wq.data_ptr(), wk.data_ptr(), cos.data_ptr(),
+                     sin.data_ptr())
+    ctx.sync()
+
+    def ref_one(x, w):
+        x = x.float().reshape(batch, seq, heads, 128)
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * w
+        x0, x1 = x[..., 0::2], x[..., 1::2]
+        c, s = cos[None, :, None, 0::2], sin[None, :, None, 0::2]
+        return torch.stack([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1).reshape(batch * seq, hid)
+
+    assert _rel(work[:, :hid].float(), ref_one(qkv[:, :hid], wq)) < 4e-3
+    assert _rel(work[:, hid:2 * hid].float(), ref_one(qkv[:, hid:2 * hid], wk)) < 4e-3
+    assert torch.equal(work[:, 2 * hid:], qkv[:, 2 * hid:])  # V untouched

@@ -1,0 +1,237 @@
+"""The whole DiT step and the sampler loops on the GPU against the numpy oracle (tiny model, many shapes) and
+against golden outputs of the reference implementation itself (klein-4B shape).
+
+Tolerances are the ones the path is specified with, relative L2 = ||a - b|| / ||b||, b = oracle:
+per-step velocity <= 2e-2, final latent <= 3e-2.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+VEL_TOL = 2e-2
+LATENT_TOL = 3e-2
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def rel(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.fixture(scope="module")
+def synth(fx):
+    import flux2_c_b200.synth as s
+    return s
+
+
+@pytest.fixture(scope="module")
+def tiny(fx, ctx, synth):
+    from oracle import flux_oracle as fo
+    d = synth.Dims.tiny()
+    # std 0.08 and QK-norm weights of 1 give sharp, position-sensitive attention at this small width
+    W = synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08)
+    model = fx.Model.from_tensors(ctx, d, W)
+    yield d, W, model, fo.OracleModel(W, d)
+    model.close()
+
+
+@pytest.mark.parametrize("h,w,ntxt", [(4, 4, 32), (8, 8, 64), (3, 5, 17), (16, 16, 128), (1, 1, 1), (12, 20, 200)])
+def test_tiny_forward_matches_oracle(tiny, synth, h, w, ntxt):
+    d, W, model, om = tiny
+    z = synth.make_latent(11, d.latent_ch, h, w)
+    c = synth.make_context(12, ntxt, d.text_dim)
+    for t in (1.0, 0.37):
+        assert rel(model.forward(z, h, w, c, t), om.forward(z, h, w, c, t)) < VEL_TOL
+
+
+def test_tiny_forward_is_sensitive_to_positions(tiny, synth):
+    """Guards the test above against a blind spot: with these weights, dropping RoPE moves the output by far
+    more than the tolerance, so a wrong rotation could not pass."""
+    from oracle import flux_oracle as fo
+    d, W, model, om = tiny
+    z = synth.make_latent(11, d.latent_ch, 8, 8)
+    c = synth.make_context(12, 64, d.text_dim)
+    good = om.forward(z, 8, 8, c, 0.5)
+    saved = fo.apply_rope
+    fo.apply_rope = lambda x, cos, sin: x
+    try:
+        bad = om.forward(z, 8, 8, c, 0.5)
+    finally:
+        fo.apply_rope = saved
+    assert rel(bad, good) > 5 * VEL_TOL
+
+
+def test_tiny_forward_with_references(tiny, synth):
+    d, W, model, om = tiny
+    z = synth.make_latent(21, d.latent_ch, 6, 6)
+    c = synth.make_context(22, 40, d.text_dim)
+    refs = [(synth.make_latent(23, d.latent_ch, 6, 6), 10), (synth.make_latent(24, d.latent_ch, 3, 7), 20)]
+    assert rel(model.forward(z, 6, 6, c, 0.8, refs[:1]), om.forward(z, 6, 6, c, 0.8, refs[:1])) < VEL_TOL
+    assert rel(model.forward(z, 6, 6, c, 0.8, refs), om.forward(z, 6, 6, c, 0.8, refs)) < VEL_TOL
+    # the reference image must matter
+    assert rel(model.forward(z, 6, 6, c, 0.8, refs[:1]), model.forward(z, 6, 6, c, 0.8)) > 1e-2
+
+
+def test_tiny_sampler_euler(tiny, synth, fx):
+    d, W, model, om = tiny
+    h, w, ntxt, steps = 8, 8, 64, 6
+    z0 = fx.init_noise(d.latent_ch, h, w, 42)
+    c = synth.make_context(31, ntxt, d.text_dim)
+    sch = fx.official_schedule(steps, h * w)
+    rec = []
+    want = om.sample_euler(z0, h, w, c, sch, record=rec)
+    got, vel = model.sample(z0, h, w, c, sch, return_velocities=True)
+    assert rel(got, want) < LATENT_TOL
+    # per-step velocity, engine fed the oracle's own state so that drift does not confound the step error
+    for i, (zi, vi) in enumerate(rec):
+        assert rel(model.forward(zi, h, w, c, float(sch[i])), vi) < VEL_TOL
+    assert rel(vel[0], rec[0][1]) < VEL_TOL
+    # the loop really integrates: z_final = z0 + sum dt_i v_i of the velocities it reports
+    acc = z0.astype(np.float64).copy()
+    for i in range(steps):
+        acc += np.float64(np.float32(sch[i + 1] - sch[i])) * vel[i]
+    assert rel(got, acc) < 1e-5
+
+
+def test_tiny_sampler_cfg_pair(tiny, synth, fx):
+    d, W, model, om = tiny
+    h, w, ntxt, steps = 6, 6, 48, 5
+    z0 = fx.init_noise(d.latent_ch, h, w, 7)
+    cc = synth.make_context(41, ntxt, d.text_dim)
+    cu = synth.make_context(42, ntxt, d.text_dim)
+    sch = fx.official_schedule(steps, h * w)
+    want = om.sample_euler_cfg(z0, h, w, cc, cu, 4.0, sch)
+    got = model.sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=4.0)
+    assert rel(got, want) < LATENT_TOL
+    # guidance 1 collapses to the conditional pass
+    assert rel(model.sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=1.0), model.sample(z0, h, w, cc, sch)) < 1e-3
+
+
+def test_tiny_sampler_with_reference(tiny, synth, fx):
+    d, W, model, om = tiny
+    h, w, ntxt = 4, 6, 24
+    z0 = fx.init_noise(d.latent_ch, h, w, 9)
+    c = synth.make_context(51, ntxt, d.text_dim)
+    refs = [(synth.make_latent(52, d.latent_ch, 4, 6), 10)]
+    sch = fx.official_schedule(3, h * w)
+    assert rel(model.sample(z0, h, w, c, sch, refs=refs), om.sample_euler(z0, h, w, c, sch, refs=refs)) < LATENT_TOL
+
+
+def test_forward_is_deterministic(tiny, synth):
+    d, W, model, om = tiny
+    z = synth.make_latent(61, d.latent_ch, 8, 8)
+    c = synth.make_context(62, 64, d.text_dim)
+    a = model.forward(z, 8, 8, c, 0.6)
+    b = model.forward(z, 8, 8, c, 0.6)
+    assert np.array_equal(a, b)
+
+
+def test_safetensors_loader_round_trip(tiny, synth, fx, ctx, tmp_path):
+    d, W, model, om = tiny
+    path = str(tmp_path / "tiny.safetensors")
+    synth.write_safetensors(path, W)
+    m2 = fx.Model.load_safetensors(ctx, path)
+    try:
+        dims = m2.dims()
+        assert (dims.hidden, dims.mlp, dims.n_double, dims.n_single, dims.text_dim) == (d.hidden, d.mlp, d.n_double,
+                                                                                        d.n_single, d.text_dim)
+        z = synth.make_latent(71, d.latent_ch, 4, 4)
+        c = synth.make_context(72, 16, d.text_dim)
+        assert np.array_equal(m2.forward(z, 4, 4, c, 0.5), model.forward(z, 4, 4, c, 0.5))
+    finally:
+        m2.close()
+
+
+def test_loader_failures_are_reported(tiny, synth, fx, ctx, tmp_path):
+    d, W, model, om = tiny
+    with pytest.raises(fx.FluxCudaError):
+        fx.Model.load_safetensors(ctx, str(tmp_path / "missing.safetensors"))
+    # truncated file
+    path = str(tmp_path / "tiny.safetensors")
+    synth.write_safetensors(path, W)
+    data = open(path, "rb").read()
+    open(str(tmp_path / "cut.safetensors"), "wb").write(data[:len(data) // 2])
+    with pytest.raises(fx.FluxCudaError):
+        fx.Model.load_safetensors(ctx, str(tmp_path / "cut.safetensors"))
+    # a tensor missing
+    W2 = dict(W)
+    del W2["proj_out.weight"]
+    with pytest.raises(fx.FluxCudaError):
+        fx.Model.from_tensors(ctx, d, W2)
+    # a tensor with the wrong shape
+    W3 = dict(W)
+    W3["proj_out.weight"] = W["proj_out.weight"][:, :-64]
+    with pytest.raises(fx.FluxCudaError):
+        fx.Model.from_tensors(ctx, d, W3)
+    with pytest.raises(fx.FluxCudaError):
+        model.forward(np.zeros((d.latent_ch, 0, 4), np.float32), 0, 4, np.zeros((4, d.text_dim), np.float32), 0.5)
+
+
+# ------------------------------------------------------------------------------------------------ klein-4B shape
+@pytest.fixture(scope="module", params=["sharp", "base"])
+def klein(request, fx, ctx, synth):
+    path = os.path.join(GOLDEN, "reference_%s.npz" % request.param)
+    if not os.path.exists(path):
+        pytest.skip("golden fixture %s missing" % path)
+    gold = np.load(path)
+    d = synth.Dims.klein4b()
+    W = synth.make_transformer_weights(d, seed=0, sharp=request.param == "sharp")
+    chk = float(np.abs(synth.bf16_bits_to_f32(W["proj_out.weight"]).astype(np.float64)).sum() +
+                np.abs(synth.bf16_bits_to_f32(W["x_embedder.weight"]).astype(np.float64)).sum())
+    assert abs(chk - float(gold["weights_checksum"])) < 1e-6 * chk, "weight generator drifted from the fixtures"
+    model = fx.Model.from_tensors(ctx, d, W)
+    del W
+    yield request.param, d, model, gold
+    model.close()
+
+
+def test_klein_forward_matches_reference(klein, synth):
+    kind, d, model, gold = klein
+    z = synth.make_latent(42, 128, 4, 4)
+    c = synth.make_context(1234, 32, d.text_dim)
+    r1 = synth.make_latent(7, 128, 2, 3)
+    r2 = synth.make_latent(8, 128, 3, 2)
+    assert rel(model.forward(z, 4, 4, c, 0.7), gold["A_v"]) < VEL_TOL
+    assert rel(model.forward(z, 4, 4, c, 0.4, [(r1, 10)]), gold["B_v"]) < VEL_TOL
+    assert rel(model.forward(z, 4, 4, c, 0.4, [(r1, 10), (r2, 20)]), gold["B2_v"]) < VEL_TOL
+
+
+def test_klein_samplers_match_reference(klein, synth, fx):
+    kind, d, model, gold = klein
+    h, w, ntxt = 6, 4, 48
+    z0 = fx.init_noise(128, h, w, 42)
+    assert np.allclose(z0, gold["C_z0"], atol=2e-6)
+    c = synth.make_context(1234, ntxt, d.text_dim)
+    cu = synth.make_context(4321, ntxt, d.text_dim)
+    sch = gold["C_sched"]
+    zs = [gold["C_z0"], gold["C_z0"] + np.float32(sch[1] - sch[0]) * gold["C_v"][0]]
+    for i in range(2):
+        assert rel(model.forward(zs[i], h, w, c, float(sch[i])), gold["C_v"][i]) < VEL_TOL
+    assert rel(model.sample(z0, h, w, c, sch), gold["C_final"]) < LATENT_TOL
+    assert rel(model.sample(z0, h, w, c, sch, ctx_uncond=cu, guidance=4.0), gold["D_final"]) < LATENT_TOL
+    r1 = synth.make_latent(7, 128, 2, 3)
+    assert rel(model.sample(z0, h, w, c, sch, refs=[(r1, 10)]), gold["C_ref_final"]) < LATENT_TOL
+
+
+def test_klein_config1_and_2_match_reference(klein, synth, fx):
+    """256x256 and 512x512, 512 text tokens, 4 steps, noise seed 42: the benchmark's own configurations."""
+    kind, d, model, gold = klein
+    c = synth.make_context(1234, 512, d.text_dim)
+    if kind == "sharp":
+        z0 = fx.init_noise(128, 16, 16, 42)
+        assert rel(model.forward(z0, 16, 16, c, 1.0), gold["cfg1_v0"]) < VEL_TOL
+        return
+    for tag, h, w in (("cfg1", 16, 16), ("cfg2", 32, 32)):
+        sch = gold[tag + "_sched"]
+        assert np.allclose(fx.official_schedule(4, h * w), sch, atol=1e-6)
+        z = fx.init_noise(128, h, w, 42)
+        z0 = z.copy()
+        for i in range(4):  # velocities along the reference's own trajectory
+            v = gold[tag + "_v"][i]
+            assert rel(model.forward(z, h, w, c, float(sch[i])), v) < VEL_TOL
+            z = z + np.float32(sch[i + 1] - sch[i]) * v
+        assert rel(model.sample(z0, h, w, c, sch), gold[tag + "_final"]) < LATENT_TOL

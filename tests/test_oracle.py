@@ -1,0 +1,87 @@
+"""Pins the numpy oracle (oracle/flux_oracle.py) to the reference implementation: its forward pass and sampler
+loops must reproduce outputs the reference itself produced for the same seeded weights and inputs
+(tests/golden/reference_sharp.npz, written by tests/golden/make_golden.py). f32 on both sides; the only
+difference is summation order inside the BLAS calls."""
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = 2e-4
+
+
+def rel(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.fixture(scope="module")
+def pinned(fx):
+    import flux2_c_b200.synth as synth
+    from oracle import flux_oracle as fo
+    path = os.path.join(GOLDEN, "reference_sharp.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_sharp.npz missing")
+    gold = np.load(path)
+    d = synth.Dims.klein4b()
+    W = synth.make_transformer_weights(d, seed=0, sharp=True)
+    om = fo.OracleModel(W, d)
+    om.preload()
+    return synth, d, om, gold
+
+
+def test_oracle_forward_matches_reference(pinned):
+    synth, d, om, gold = pinned
+    z = synth.make_latent(42, 128, 4, 4)
+    c = synth.make_context(1234, 32, d.text_dim)
+    r1 = synth.make_latent(7, 128, 2, 3)
+    r2 = synth.make_latent(8, 128, 3, 2)
+    assert rel(om.forward(z, 4, 4, c, 0.7), gold["A_v"]) < TOL
+    assert rel(om.forward(z, 4, 4, c, 0.4, [(r1, 10)]), gold["B_v"]) < TOL
+    assert rel(om.forward(z, 4, 4, c, 0.4, [(r1, 10), (r2, 20)]), gold["B2_v"]) < TOL
+
+
+def test_oracle_samplers_match_reference(pinned):
+    synth, d, om, gold = pinned
+    h, w, ntxt = 6, 4, 48
+    c = synth.make_context(1234, ntxt, d.text_dim)
+    cu = synth.make_context(4321, ntxt, d.text_dim)
+    z0, sch = gold["C_z0"], gold["C_sched"]
+    rec = []
+    assert rel(om.sample_euler(z0, h, w, c, sch, record=rec), gold["C_final"]) < TOL
+    assert rel(rec[0][1], gold["C_v"][0]) < TOL and rel(rec[1][1], gold["C_v"][1]) < TOL
+    assert rel(om.sample_euler_cfg(z0, h, w, c, cu, 4.0, sch), gold["D_final"]) < TOL
+
+
+def test_tiny_oracle_structure():
+    """Shape/ordering invariants of the restatement that need no reference run."""
+    import importlib
+    import sys
+    sys.path.insert(0, os.path.dirname(GOLDEN))
+    from conftest import load_package
+    load_package()
+    synth = importlib.import_module("flux2_c_b200.synth")
+    from oracle import flux_oracle as fo
+    d = synth.Dims.tiny()
+    om = fo.OracleModel(synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08), d)
+    z = synth.make_latent(1, d.latent_ch, 4, 4)
+    c = synth.make_context(2, 16, d.text_dim)
+    v = om.forward(z, 4, 4, c, 0.5)
+    assert v.shape == (d.latent_ch, 4, 4) and np.isfinite(v).all()
+    # velocity depends on the timestep and on the context
+    assert rel(om.forward(z, 4, 4, c, 0.9), v) > 1e-2
+    assert rel(om.forward(z, 4, 4, -c, 0.5), v) > 1e-2
+    # a reference image changes the prediction, and its T offset matters
+    r = synth.make_latent(3, d.latent_ch, 4, 4)
+    va = om.forward(z, 4, 4, c, 0.5, [(r, 10)])
+    vb = om.forward(z, 4, 4, c, 0.5, [(r, 20)])
+    assert rel(va, v) > 1e-2 and rel(vb, va) > 1e-4
+    # Euler: one step of the loop equals z + dt * v
+    sch = np.array([1.0, 0.5, 0.0], dtype=np.float32)
+    rec = []
+    zf = om.sample_euler(z, 4, 4, c, sch, record=rec)
+    z1 = z + np.float32(-0.5) * rec[0][1]
+    assert np.allclose(rec[1][0], z1)
+    assert np.allclose(zf, z1 + np.float32(-0.5) * rec[1][1])
