@@ -132,9 +132,7 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     load_package()
-    import numpy as np
     import flux2_c_b200.synth as synth
-    import flux2_c_b200 as fx
     sys.path.insert(0, ROOT)
     from oracle import ref_binding as rb
     kind = rb.best_kind()
@@ -153,9 +151,9 @@ def run_reference_arm(args):
     finally:
         if os.path.exists(path):
             os.remove(path)
-    z0 = fx.init_noise(dims.latent_ch, H_LAT, W_LAT, 42)
+    z0 = lib.init_noise(dims.latent_ch, H_LAT, W_LAT, 42)
     ctx = synth.make_context(1234, TXT, dims.text_dim)
-    sched = fx.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
+    sched = lib.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
     # one "step" of this arm = a bounded sample of one image: its first DiT forward, scaled by the 4 forwards
     for _ in range(args.warmup):
         tf.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
@@ -293,8 +291,19 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident timing: inputs already in HBM, K images back to back
     sampler.upload(z0.data_ptr(), cemb.data_ptr())
+    if args.ncu_range:
+        # one warm image, then exactly one image between cudaProfilerStart/Stop (ncu --profile-from-start off)
+        sampler.run(sched)
+        ctx.sync()
+        torch.cuda.profiler.start()
+        sampler.run(sched)
+        ctx.sync()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"ncu_range": "one image", "launches": sampler.last_run()[1]}))
+        return 0
+
+    # ---- device-resident timing: inputs already in HBM, K images back to back
     for _ in range(max(3, args.warmup)):
         sampler.run(sched)
     barrier()
@@ -302,12 +311,10 @@ def run_ours(args):
     if rank == 0:
         clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches = 0
     with torch.cuda.stream(stream):
         e0.record()
         for _ in range(args.steps):
             sampler.run(sched)
-            launches += sampler.last_run()[1] if False else 0
         e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
@@ -400,6 +407,7 @@ def main():
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ncu-range", action="store_true", help="profile exactly one image (for ncu launch lists)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 10:

@@ -87,6 +87,8 @@ def _declare(L):
     L.flux_cuda_sampler_upload.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p)]
     L.flux_cuda_sampler_run.restype = c_int
     L.flux_cuda_sampler_run.argtypes = [c_void_p, fp, c_int, ctypes.c_float, c_int, c_int]
+    L.flux_cuda_sampler_run_steps.restype = c_int
+    L.flux_cuda_sampler_run_steps.argtypes = [c_void_p, fp, c_int, c_int, c_int, ctypes.c_float, c_int]
     L.flux_cuda_sampler_download.restype = c_int
     L.flux_cuda_sampler_download.argtypes = [c_void_p, c_void_p, c_void_p]
     L.flux_cuda_sampler_last_run.restype = c_int
@@ -327,6 +329,12 @@ class Sampler:
         sch = np.ascontiguousarray(schedule, dtype=np.float32)
         check(lib().flux_cuda_sampler_run(self.handle, _fp(sch), len(sch) - 1, guidance, int(record_velocities),
                                           int(apply_update)))
+
+    def run_steps(self, schedule, first, count, guidance=1.0, record_velocities=False):
+        np = _np()
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        check(lib().flux_cuda_sampler_run_steps(self.handle, _fp(sch), len(sch) - 1, first, count, guidance,
+                                                int(record_velocities)))
 
     def download(self, latent_ptr, velocities_ptr=None):
         check(lib().flux_cuda_sampler_download(self.handle, latent_ptr, velocities_ptr))

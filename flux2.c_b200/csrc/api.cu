@@ -261,7 +261,11 @@ int flux_cuda_sampler_upload(flux_cuda_sampler *s, const float *z0, const float 
 }
 int flux_cuda_sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance,
                           int record_velocities, int apply_update) {
-  return sampler_run(s, schedule, num_steps, guidance, record_velocities, apply_update);
+  return sampler_run(s, schedule, num_steps, 0, num_steps, guidance, record_velocities, apply_update);
+}
+int flux_cuda_sampler_run_steps(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count,
+                                float guidance, int record_velocities) {
+  return sampler_run(s, schedule, num_steps, first, count, guidance, record_velocities, 1);
 }
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
   return sampler_download(s, latent_out, velocities_out);
@@ -302,7 +306,7 @@ static int run_once(flux_cuda_model *m, int h, int w, const flux_cuda_ref *refs,
   int rc = sampler_create(m, h, w, txt_seq, rs.data(), num_refs, ctx_uncond ? 2 : 1, num_steps, &s);
   if (rc) return rc;
   rc = sampler_upload(s, z0, ctx, ctx_uncond, lat.data());
-  if (!rc) rc = sampler_run(s, schedule, num_steps, guidance, velocities_out != nullptr, apply_update);
+  if (!rc) rc = sampler_run(s, schedule, num_steps, 0, num_steps, guidance, velocities_out != nullptr, apply_update);
   if (!rc) rc = sampler_download(s, latent_out, velocities_out);
   else ctx_sync_check(m->ctx);
   sampler_free(s);

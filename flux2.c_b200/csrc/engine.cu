@@ -695,9 +695,9 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   return L.rc;
 }
 
-int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance, int record_velocities,
-                int apply_update) {
-  if (!s || !schedule || num_steps < 1) {
+int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
+                int record_velocities, int apply_update) {
+  if (!s || !schedule || num_steps < 1 || first < 0 || count < 1 || first + count > num_steps) {
     set_error("run: bad argument");
     return FLUX_CUDA_ERR_ARG;
   }
@@ -714,20 +714,23 @@ int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, floa
   ws->prof_used = 0;
   ws->last_steps = num_steps;
   cudaEventRecord(ws->ev0, st);
-  // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and no
-  // host synchronisation is needed between consecutive runs.
-  int rc = check_cuda(cudaMemcpyAsync(ws->sched, schedule, (num_steps + 1) * 4, cudaMemcpyHostToDevice, st), "schedule");
-  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->z, ws->z_in, n * 4, cudaMemcpyDeviceToDevice, st), "init latent");
-  if (!rc) rc = prepare(m, ws, num_steps, st);
-  for (int i = 0; !rc && i < num_steps; ++i) {
+  int rc = 0;
+  if (first == 0) {
+    // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and
+    // no host synchronisation is needed between consecutive runs.
+    rc = check_cuda(cudaMemcpyAsync(ws->sched, schedule, (num_steps + 1) * 4, cudaMemcpyHostToDevice, st), "schedule");
+    if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->z, ws->z_in, n * 4, cudaMemcpyDeviceToDevice, st), "init latent");
+    if (!rc) rc = prepare(m, ws, num_steps, st);
+  }
+  for (int i = first; !rc && i < first + count; ++i) {
     rc = forward_step(m, ws, i, st);
     if (rc) break;
     const float *v = ws->v;
     if (ws->B == 2) {
       // row 0 = conditional, row 1 = unconditional: v = v_u + g (v_c - v_u) (flux_sample.c:495-499)
-      int r = launch_cfg_euler(ws->z, ws->v, ws->v + n, ws->vcomb, guidance, ws->sched, i, static_cast<long long>(n),
-                               apply_update, st);
-      if (r) rc = FLUX_CUDA_ERR_CUDA;
+      if (launch_cfg_euler(ws->z, ws->v, ws->v + n, ws->vcomb, guidance, ws->sched, i, static_cast<long long>(n),
+                           apply_update, st))
+        rc = FLUX_CUDA_ERR_CUDA;
       v = ws->vcomb;
       ws->launches++;
     } else if (apply_update) {

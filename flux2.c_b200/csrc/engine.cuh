@@ -101,8 +101,10 @@ void sampler_free(flux_cuda_sampler *s);
 int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, const float *ctx1,
                    const float *const *ref_latents);
 // guidance is used only when the sampler was created with batch 2 (row 0 = conditional context).
-int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance, int record_velocities,
-                int apply_update);
+// Runs steps [first, first + count) of a num_steps schedule. first == 0 (re)starts from the uploaded latent and
+// prepares the step-invariant inputs; first > 0 continues from the current latent.
+int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
+                int record_velocities, int apply_update);
 int sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
 // Sums the event pairs of the last profiled run per kernel class (call after a sync).
 int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);

@@ -1,0 +1,318 @@
+/*
+ * flux_cuda_seam.c - the reference's internal link seam, served by the B200 engine.
+ *
+ * The reference's flux.c declares its transformer and sampler as `extern` symbols (flux.c:36-119) and
+ * flux_sample.c / flux_transformer.c define them. This file defines the same symbols on top of
+ * flux_cuda.h, so that building the reference with this file (and libflux_cuda.so) IN PLACE OF
+ * flux_transformer.c and flux_sample.c gives the unmodified CLI / library (main.c, flux.c, flux_cli.c,
+ * flux_vae.c, flux_qwen3.c, flux_kernels.c, ...) a GPU denoising path. It is compiled inside the
+ * reference's source tree (it includes the reference's own flux_safetensors.h and flux_kernels.h for the
+ * struct layouts and the global callback pointers those files own).
+ *
+ * Behaviour kept from the reference: argument meaning, malloc ownership of returned buffers (caller
+ * frees), NULL on failure, input latent not modified, callback order (step callback before a step,
+ * progress callback after it, 5 + 20 + 1 sub-step events per forward, step-image callback after every
+ * step but the last), timing globals. Difference: there is no CPU fallback - a CUDA failure returns NULL
+ * with the reason on stderr.
+ */
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/time.h>
+
+#include "flux.h"
+#include "flux_cuda.h"
+#include "flux_kernels.h"
+#include "flux_safetensors.h"
+
+typedef struct flux_vae flux_vae_t;
+extern flux_image *flux_vae_decode(flux_vae_t *vae, const float *latent, int batch, int latent_h, int latent_w);
+
+typedef struct flux_transformer {
+  flux_cuda_model *model;
+  safetensors_file_t *owned_sf; /* set by the _mmap loader, which takes ownership of the file */
+  flux_cuda_dims dims;
+} flux_transformer_t;
+
+typedef struct { /* flux.c:68-72 */
+  const float *latent;
+  int h, w;
+  int t_offset;
+} flux_ref_t;
+
+double flux_timing_transformer_total = 0.0;
+double flux_timing_transformer_double = 0.0;
+double flux_timing_transformer_single = 0.0;
+double flux_timing_transformer_final = 0.0;
+
+void flux_reset_timing(void) {
+  flux_timing_transformer_total = flux_timing_transformer_double = 0.0;
+  flux_timing_transformer_single = flux_timing_transformer_final = 0.0;
+}
+
+static flux_cuda_ctx *g_ctx = NULL;
+
+static double now_ms(void) {
+  struct timeval tv;
+  gettimeofday(&tv, NULL);
+  return tv.tv_sec * 1000.0 + tv.tv_usec / 1000.0;
+}
+
+static flux_cuda_ctx *seam_ctx(void) {
+  if (!g_ctx) {
+    const char *dev = getenv("FLUX_CUDA_DEVICE");
+    if (flux_cuda_ctx_create(dev ? atoi(dev) : 0, &g_ctx) != FLUX_CUDA_OK) {
+      fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+      g_ctx = NULL;
+    }
+  }
+  return g_ctx;
+}
+
+/* ------------------------------------------------------------------------------------------ loading */
+static flux_transformer_t *load_from(safetensors_file_t *sf) {
+  flux_cuda_ctx *ctx = seam_ctx();
+  if (!ctx || !sf) return NULL;
+  flux_transformer_t *tf = (flux_transformer_t *)calloc(1, sizeof(*tf));
+  if (!tf) return NULL;
+  /* the file is already open and mapped by the caller: hand the path to the engine's own validating loader */
+  if (flux_cuda_model_load_safetensors(ctx, sf->path, &tf->model) != FLUX_CUDA_OK) {
+    fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+    free(tf);
+    return NULL;
+  }
+  flux_cuda_model_dims(tf->model, &tf->dims);
+  return tf;
+}
+
+flux_transformer_t *flux_transformer_load_safetensors(safetensors_file_t *sf) { return load_from(sf); }
+
+flux_transformer_t *flux_transformer_load_safetensors_mmap(safetensors_file_t *sf) {
+  /* 7.75 GB of bf16 weights stay resident in HBM, so "mmap mode" is the same load; the ownership
+   * contract is kept: the file now belongs to the transformer and is closed by flux_transformer_free. */
+  flux_transformer_t *tf = load_from(sf);
+  if (tf) tf->owned_sf = sf;
+  return tf;
+}
+
+flux_transformer_t *flux_transformer_load(FILE *f) {
+  (void)f; /* legacy binary format: declared by flux.c, never called */
+  return NULL;
+}
+
+void flux_transformer_free(flux_transformer_t *tf) {
+  if (!tf) return;
+  flux_cuda_model_free(tf->model);
+  if (tf->owned_sf) safetensors_close(tf->owned_sf);
+  free(tf);
+}
+
+/* ------------------------------------------------------------------------------------------ forward */
+static void fire_substeps(const flux_transformer_t *tf) {
+  if (!flux_substep_callback) return;
+  for (int i = 0; i < tf->dims.n_double; i++) flux_substep_callback(FLUX_SUBSTEP_DOUBLE_BLOCK, i, tf->dims.n_double);
+  for (int i = 0; i < tf->dims.n_single; i++) flux_substep_callback(FLUX_SUBSTEP_SINGLE_BLOCK, i, tf->dims.n_single);
+  flux_substep_callback(FLUX_SUBSTEP_FINAL_LAYER, 0, 1);
+}
+
+float *flux_transformer_forward_with_multi_refs(flux_transformer_t *tf, const float *img_latent, int img_h, int img_w,
+                                                const flux_ref_t *refs, int num_refs, const float *txt_emb,
+                                                int txt_seq, float timestep) {
+  if (!tf || !img_latent || !txt_emb) return NULL;
+  if (!refs) num_refs = 0;
+  flux_cuda_ref cr[16];
+  if (num_refs > 16) return NULL;
+  for (int i = 0; i < num_refs; i++) {
+    cr[i].latent = refs[i].latent;
+    cr[i].h = refs[i].h;
+    cr[i].w = refs[i].w;
+    cr[i].t_offset = refs[i].t_offset;
+  }
+  const size_t n = (size_t)tf->dims.latent_ch * img_h * img_w;
+  float *out = (float *)malloc(n * sizeof(float));
+  if (!out) return NULL;
+  const double t0 = now_ms();
+  if (flux_cuda_forward(tf->model, img_latent, img_h, img_w, cr, num_refs, txt_emb, txt_seq, timestep, out) !=
+      FLUX_CUDA_OK) {
+    fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+    free(out);
+    return NULL;
+  }
+  flux_timing_transformer_total += now_ms() - t0;
+  fire_substeps(tf);
+  return out;
+}
+
+float *flux_transformer_forward(flux_transformer_t *tf, const float *img_latent, int img_h, int img_w,
+                                const float *txt_emb, int txt_seq, float timestep) {
+  return flux_transformer_forward_with_multi_refs(tf, img_latent, img_h, img_w, NULL, 0, txt_emb, txt_seq, timestep);
+}
+
+float *flux_transformer_forward_with_refs(flux_transformer_t *tf, const float *img_latent, int img_h, int img_w,
+                                          const float *ref_latent, int ref_h, int ref_w, int t_offset,
+                                          const float *txt_emb, int txt_seq, float timestep) {
+  flux_ref_t r = {ref_latent, ref_h, ref_w, t_offset};
+  return flux_transformer_forward_with_multi_refs(tf, img_latent, img_h, img_w, ref_latent ? &r : NULL,
+                                                  ref_latent ? 1 : 0, txt_emb, txt_seq, timestep);
+}
+
+/* ------------------------------------------------------------------------------------------ samplers */
+static float *sample_common(flux_transformer_t *tf, const float *z, int batch, int channels, int h, int w,
+                            const flux_ref_t *refs, int num_refs, const float *emb_cond, int seq_cond,
+                            const float *emb_uncond, int seq_uncond, float guidance, const float *schedule,
+                            int num_steps, void (*progress_callback)(int, int)) {
+  if (!tf || !z || !emb_cond || !schedule || num_steps < 1 || batch != 1 || channels != tf->dims.latent_ch ||
+      num_refs > 16 || (emb_uncond && seq_uncond != seq_cond))
+    return NULL;
+  if (!refs) num_refs = 0;
+  flux_cuda_ref_shape shapes[16];
+  const float *lat[16];
+  for (int i = 0; i < num_refs; i++) {
+    shapes[i].h = refs[i].h;
+    shapes[i].w = refs[i].w;
+    shapes[i].t_offset = refs[i].t_offset;
+    lat[i] = refs[i].latent;
+  }
+  const size_t n = (size_t)channels * h * w;
+  float *out = (float *)malloc(n * sizeof(float));
+  flux_cuda_sampler *s = NULL;
+  int rc = out ? FLUX_CUDA_OK : FLUX_CUDA_ERR_NOMEM;
+  if (!rc) rc = flux_cuda_sampler_create(tf->model, h, w, seq_cond, shapes, num_refs, emb_uncond ? 2 : 1, num_steps, &s);
+  if (!rc) rc = flux_cuda_sampler_upload(s, z, emb_cond, emb_uncond, lat);
+
+  flux_reset_timing();
+  const double t_start = now_ms();
+  const int observed = flux_step_callback || progress_callback || flux_substep_callback ||
+                       (flux_step_image_callback && flux_step_image_vae);
+  double step_ms[FLUX_MAX_STEPS];
+  if (!rc && !observed) {
+    /* nobody watches the steps: the whole loop stays on the device */
+    rc = flux_cuda_sampler_run(s, schedule, num_steps, guidance, 0, 1);
+    if (!rc) rc = flux_cuda_sampler_download(s, out, NULL);
+  } else {
+    for (int step = 0; !rc && step < num_steps; step++) {
+      const double t0 = now_ms();
+      if (flux_step_callback) flux_step_callback(step + 1, num_steps);
+      rc = flux_cuda_sampler_run_steps(s, schedule, num_steps, step, 1, guidance, 0);
+      if (!rc) rc = flux_cuda_sampler_download(s, out, NULL); /* waits for the step; out = current latent */
+      if (rc) break;
+      fire_substeps(tf);
+      if (emb_uncond) fire_substeps(tf); /* the reference runs two forwards per guided step */
+      if (step < FLUX_MAX_STEPS) step_ms[step] = now_ms() - t0;
+      if (progress_callback) progress_callback(step + 1, num_steps);
+      if (flux_step_image_callback && flux_step_image_vae && step + 1 < num_steps) {
+        flux_image *img = flux_vae_decode((flux_vae_t *)flux_step_image_vae, out, 1, h, w);
+        if (img) {
+          flux_step_image_callback(step + 1, num_steps, img);
+          flux_image_free(img);
+        }
+      }
+    }
+  }
+  flux_timing_transformer_total = now_ms() - t_start;
+  if (!rc && flux_verbose) {
+    fprintf(stderr, "\nDenoising timing breakdown:\n");
+    if (observed)
+      for (int step = 0; step < num_steps && step < FLUX_MAX_STEPS; step++)
+        fprintf(stderr, "  Step %d: %.1f ms\n", step + 1, step_ms[step]);
+    fprintf(stderr, "  Total denoising: %.1f ms (%.2f s)\n", flux_timing_transformer_total,
+            flux_timing_transformer_total / 1000.0);
+  }
+  flux_cuda_sampler_free(s);
+  if (rc) {
+    fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+    free(out);
+    return NULL;
+  }
+  return out;
+}
+
+float *flux_sample_euler(void *transformer, void *text_encoder, float *z, int batch, int channels, int h, int w,
+                         const float *text_emb, int text_seq, const float *schedule, int num_steps,
+                         void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, NULL, 0, text_emb, text_seq, NULL,
+                       0, 1.0f, schedule, num_steps, progress_callback);
+}
+
+float *flux_sample_euler_with_refs(void *transformer, void *text_encoder, float *z, int batch, int channels, int h,
+                                   int w, const float *ref_latent, int ref_h, int ref_w, int t_offset,
+                                   const float *text_emb, int text_seq, const float *schedule, int num_steps,
+                                   void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  flux_ref_t r = {ref_latent, ref_h, ref_w, t_offset};
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, ref_latent ? &r : NULL,
+                       ref_latent ? 1 : 0, text_emb, text_seq, NULL, 0, 1.0f, schedule, num_steps, progress_callback);
+}
+
+float *flux_sample_euler_with_multi_refs(void *transformer, void *text_encoder, float *z, int batch, int channels,
+                                         int h, int w, const flux_ref_t *refs, int num_refs, const float *text_emb,
+                                         int text_seq, const float *schedule, int num_steps,
+                                         void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, refs, num_refs, text_emb,
+                       text_seq, NULL, 0, 1.0f, schedule, num_steps, progress_callback);
+}
+
+float *flux_sample_euler_cfg(void *transformer, void *text_encoder, float *z, int batch, int channels, int h, int w,
+                             const float *text_emb_cond, int text_seq_cond, const float *text_emb_uncond,
+                             int text_seq_uncond, float guidance_scale, const float *schedule, int num_steps,
+                             void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, NULL, 0, text_emb_cond,
+                       text_seq_cond, text_emb_uncond, text_seq_uncond, guidance_scale, schedule, num_steps,
+                       progress_callback);
+}
+
+float *flux_sample_euler_cfg_with_refs(void *transformer, void *text_encoder, float *z, int batch, int channels, int h,
+                                       int w, const float *ref_latent, int ref_h, int ref_w, int t_offset,
+                                       const float *text_emb_cond, int text_seq_cond, const float *text_emb_uncond,
+                                       int text_seq_uncond, float guidance_scale, const float *schedule,
+                                       int num_steps, void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  flux_ref_t r = {ref_latent, ref_h, ref_w, t_offset};
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, ref_latent ? &r : NULL,
+                       ref_latent ? 1 : 0, text_emb_cond, text_seq_cond, text_emb_uncond, text_seq_uncond,
+                       guidance_scale, schedule, num_steps, progress_callback);
+}
+
+float *flux_sample_euler_cfg_with_multi_refs(void *transformer, void *text_encoder, float *z, int batch, int channels,
+                                             int h, int w, const flux_ref_t *refs, int num_refs,
+                                             const float *text_emb_cond, int text_seq_cond,
+                                             const float *text_emb_uncond, int text_seq_uncond, float guidance_scale,
+                                             const float *schedule, int num_steps,
+                                             void (*progress_callback)(int step, int total)) {
+  (void)text_encoder;
+  return sample_common((flux_transformer_t *)transformer, z, batch, channels, h, w, refs, num_refs, text_emb_cond,
+                       text_seq_cond, text_emb_uncond, text_seq_uncond, guidance_scale, schedule, num_steps,
+                       progress_callback);
+}
+
+/* ------------------------------------------------------------------------------------------ host pieces */
+float *flux_linear_schedule(int num_steps) {
+  float *s = (float *)malloc((num_steps + 1) * sizeof(float));
+  if (s) flux_cuda_linear_schedule(num_steps, s);
+  return s;
+}
+
+float *flux_power_schedule(int num_steps, float alpha) {
+  float *s = (float *)malloc((num_steps + 1) * sizeof(float));
+  if (s) flux_cuda_power_schedule(num_steps, alpha, s);
+  return s;
+}
+
+float *flux_official_schedule(int num_steps, int image_seq_len) {
+  float *s = (float *)malloc((num_steps + 1) * sizeof(float));
+  if (s) flux_cuda_official_schedule(num_steps, image_seq_len, s);
+  return s;
+}
+
+float *flux_init_noise(int batch, int channels, int h, int w, int64_t seed) {
+  if (batch != 1) return NULL; /* every call site of the reference passes 1 */
+  float *n = (float *)malloc((size_t)channels * h * w * sizeof(float));
+  if (!n) return NULL;
+  if (seed < 0) seed = 0;
+  flux_cuda_init_noise(channels, h, w, (long long)seed, n);
+  return n;
+}

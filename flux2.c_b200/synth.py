@@ -135,6 +135,80 @@ def make_latent(seed, ch, h, w):
     return rng.standard_normal((ch, h, w), dtype=np.float32)
 
 
+def vae_tensor_specs():
+    """(name, shape, kind) of the 250 tensors the reference's VAE loader reads (flux_vae.c:1150-1354):
+    kind 'w' = conv/linear weight, 'one' = norm scale, 'zero' = bias / running mean."""
+    specs = []
+
+    def conv(name, cout, cin, k):
+        specs.append((name + ".weight", (cout, cin, k, k), "w"))
+        specs.append((name + ".bias", (cout,), "zero"))
+
+    def norm(name, ch):
+        specs.append((name + ".weight", (ch,), "one"))
+        specs.append((name + ".bias", (ch,), "zero"))
+
+    def resblock(prefix, cin, cout):
+        norm(prefix + ".norm1", cin)
+        conv(prefix + ".conv1", cout, cin, 3)
+        norm(prefix + ".norm2", cout)
+        conv(prefix + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv(prefix + ".conv_shortcut", cout, cin, 1)
+
+    def attn(prefix, ch):
+        norm(prefix + ".group_norm", ch)
+        for n in ("to_q", "to_k", "to_v", "to_out.0"):
+            specs.append((prefix + ".%s.weight" % n, (ch, ch), "w"))
+            specs.append((prefix + ".%s.bias" % n, (ch,), "zero"))
+
+    base, mult = 128, (1, 2, 4, 4)
+    conv("encoder.conv_in", base, 3, 3)
+    for lvl in range(4):
+        ch = base * mult[lvl]
+        prev = base if lvl == 0 else base * mult[lvl - 1]
+        for r in range(2):
+            resblock("encoder.down_blocks.%d.resnets.%d" % (lvl, r), prev if (r == 0 and lvl > 0) else ch, ch)
+        if lvl < 3:
+            conv("encoder.down_blocks.%d.downsamplers.0.conv" % lvl, ch, ch, 3)
+    mid = base * mult[3]
+    for side in ("encoder", "decoder"):
+        resblock(side + ".mid_block.resnets.0", mid, mid)
+        attn(side + ".mid_block.attentions.0", mid)
+        resblock(side + ".mid_block.resnets.1", mid, mid)
+    norm("encoder.conv_norm_out", mid)
+    conv("encoder.conv_out", 64, mid, 3)
+    conv("quant_conv", 64, 64, 1)
+    conv("post_quant_conv", 32, 32, 1)
+    conv("decoder.conv_in", mid, 32, 3)
+    for lvl in range(3, -1, -1):
+        ch = base * mult[lvl]
+        prev = mid if lvl == 3 else base * mult[lvl + 1]
+        for r in range(3):
+            resblock("decoder.up_blocks.%d.resnets.%d" % (3 - lvl, r), prev if r == 0 else ch, ch)
+    for i in range(3):
+        ch = base * mult[3 - i]
+        conv("decoder.up_blocks.%d.upsamplers.0.conv" % i, ch, ch, 3)
+    norm("decoder.conv_norm_out", base)
+    conv("decoder.conv_out", 3, base, 3)
+    specs.append(("bn.running_mean", (128,), "zero"))
+    specs.append(("bn.running_var", (128,), "one"))
+    return specs
+
+
+def make_vae_weights(seed=0, std=0.02):
+    """dict name -> float32 array: conv/linear weights N(0, std^2), norm scales 1, biases and running mean 0,
+    running variance 1. Only used to turn latents into pixels for the decoded-image PSNR check."""
+    out = {}
+    for idx, (name, shape, kind) in enumerate(vae_tensor_specs()):
+        if kind == "w":
+            rng = np.random.Generator(np.random.Philox(key=[np.uint64(seed), np.uint64(0x7A0000 + idx)]))
+            out[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+        else:
+            out[name] = np.full(shape, 1.0 if kind == "one" else 0.0, dtype=np.float32)
+    return out
+
+
 def write_safetensors(path, tensors, dtype="BF16"):
     """Writes name -> array (uint16 bf16 bits for BF16, float32 for F32) in safetensors layout:
     8-byte little-endian header length, JSON header, raw little-endian data (flux_safetensors.c:155-292)."""

@@ -129,6 +129,11 @@ int flux_cuda_sampler_upload(flux_cuda_sampler *s, const float *z0, const float 
  * apply_update = 0 leaves the latent untouched (velocity of the uploaded latent at schedule[i]). */
 int flux_cuda_sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, float guidance,
                           int record_velocities, int apply_update);
+/* Steps [first, first + count) of the same loop, for callers that must observe the latent between steps (the
+ * reference's per-step callbacks, flux_sample.c:240-266). first == 0 starts from the uploaded latent; a later
+ * call with first > 0 continues from where the previous one stopped. */
+int flux_cuda_sampler_run_steps(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count,
+                                float guidance, int record_velocities);
 /* Device -> host copy of the latent (and recorded velocities), then waits and checks for kernel errors. */
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
 /* CUDA-event time of the last flux_cuda_sampler_run in ms (valid after a sync), and its kernel count. */

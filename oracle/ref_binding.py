@@ -18,6 +18,11 @@ OB_DIR = "/opt/prime-rl/.venv/lib/python3.12/site-packages/opencv_python_headles
 c_float_p = ctypes.POINTER(ctypes.c_float)
 
 
+class FluxImage(ctypes.Structure):  # struct flux_image, flux.h:73-78
+    _fields_ = [("width", ctypes.c_int), ("height", ctypes.c_int), ("channels", ctypes.c_int),
+                ("data", ctypes.POINTER(ctypes.c_uint8))]
+
+
 class FluxRefT(ctypes.Structure):  # flux_ref_t, flux.c:68-72
     _fields_ = [("latent", c_float_p), ("h", ctypes.c_int), ("w", ctypes.c_int), ("t_offset", ctypes.c_int)]
 
@@ -91,6 +96,12 @@ class RefLib:
         L.flux_power_schedule.argtypes = [ci, cf]
         L.flux_init_noise.restype = vp
         L.flux_init_noise.argtypes = [ci, ci, ci, ci, ctypes.c_int64]
+        L.flux_vae_load_safetensors.restype = vp
+        L.flux_vae_load_safetensors.argtypes = [vp]
+        L.flux_vae_free.argtypes = [vp]
+        L.flux_vae_decode.restype = ctypes.POINTER(FluxImage)
+        L.flux_vae_decode.argtypes = [vp, c_float_p, ci, ci, ci]
+        L.flux_image_free.argtypes = [ctypes.POINTER(FluxImage)]
         if kind == "blas":
             try:
                 self.blas_threads = L.openblas_get_num_threads()
@@ -118,6 +129,28 @@ class RefLib:
 
     def init_noise(self, channels, h, w, seed):
         return self._take(self.L.flux_init_noise(1, channels, h, w, seed), channels * h * w).reshape(channels, h, w)
+
+    def load_vae(self, safetensors_path):
+        """flux_vae_load_safetensors (flux_vae.c:1232-1386)."""
+        sf = self.L.safetensors_open(safetensors_path.encode())
+        if not sf:
+            raise RuntimeError("reference could not open %s" % safetensors_path)
+        vae = self.L.flux_vae_load_safetensors(sf)
+        self.L.safetensors_close(sf)
+        if not vae:
+            raise RuntimeError("reference could not load the VAE")
+        return vae
+
+    def vae_decode(self, vae, latent):
+        """flux_vae_decode (flux_vae.c:690-837): latent f32 [128, h, w] -> uint8 RGB [16h, 16w, 3]."""
+        lat = np.ascontiguousarray(latent, dtype=np.float32)
+        img = self.L.flux_vae_decode(vae, _fp(lat), 1, lat.shape[1], lat.shape[2])
+        if not img:
+            raise RuntimeError("reference VAE decode failed")
+        i = img.contents
+        out = np.ctypeslib.as_array(i.data, shape=(i.height, i.width, i.channels)).copy()
+        self.L.flux_image_free(img)
+        return out
 
     def load_transformer(self, safetensors_path):
         sf = self.L.safetensors_open(safetensors_path.encode())

@@ -235,3 +235,26 @@ def test_klein_config1_and_2_match_reference(klein, synth, fx):
             assert rel(model.forward(z, h, w, c, float(sch[i])), v) < VEL_TOL
             z = z + np.float32(sch[i + 1] - sch[i]) * v
         assert rel(model.sample(z0, h, w, c, sch), gold[tag + "_final"]) < LATENT_TOL
+
+
+def test_klein_decoded_image_psnr(klein, synth, fx, tmp_path):
+    """Decoded-image gate: the engine's and the reference's final latents of the 256x256 configuration, both
+    decoded by the reference's own CPU VAE (synthetic VAE weights), must agree to PSNR >= 30 dB on the uint8 RGB."""
+    kind, d, model, gold = klein
+    if kind != "base":
+        pytest.skip("decoded once, on the benchmark weights")
+    from oracle import ref_binding as rb
+    ref_kind = rb.best_kind()
+    if ref_kind is None:
+        pytest.skip("the reference build (oracle/_ref) is not present")
+    lib = rb.RefLib(ref_kind)
+    vpath = str(tmp_path / "vae.safetensors")
+    synth.write_safetensors(vpath, synth.make_vae_weights(), dtype="F32")
+    vae = lib.load_vae(vpath)
+    c = synth.make_context(1234, 512, d.text_dim)
+    got = model.sample(fx.init_noise(128, 16, 16, 42), 16, 16, c, gold["cfg1_sched"])
+    a = lib.vae_decode(vae, got).astype(np.float64)
+    b = lib.vae_decode(vae, gold["cfg1_final"]).astype(np.float64)
+    assert b.std() > 10  # a real picture, not a flat field
+    psnr = 10 * np.log10(255.0 ** 2 / max(((a - b) ** 2).mean(), 1e-12))
+    assert psnr >= 30.0, "PSNR %.1f dB" % psnr
