@@ -75,7 +75,7 @@ def test_gemm_gated_residual(fx, ctx):
     ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), h.data_ptr(), M, N, K, fx.EPI_GATED_RES_F32, gate_ptr=gate.data_ptr())
     ctx.sync()
     ref = h0.double() + gate.double() * (x.double() @ w.double().t())
-    assert _rel(h, ref) < 1e-5
+    assert _rel(h, ref) < 3e-5
 
 
 def test_gemm_swiglu(fx, ctx):
