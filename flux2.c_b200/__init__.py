@@ -51,6 +51,9 @@ def _declare(L):
 
 
     fp = ctypes.POINTER(ctypes.c_float)
+    L.flux_cuda_gemm_qkv_norm_rope.restype = c_int
+    L.flux_cuda_gemm_qkv_norm_rope.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_int]
     L.flux_cuda_attention.restype = c_int
     L.flux_cuda_attention.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_int, c_int, c_int, c_int, c_void_p,
                                       c_ll, c_int]
@@ -89,6 +92,12 @@ def _declare(L):
     L.flux_cuda_sampler_run.argtypes = [c_void_p, fp, c_int, ctypes.c_float, c_int, c_int]
     L.flux_cuda_sampler_run_steps.restype = c_int
     L.flux_cuda_sampler_run_steps.argtypes = [c_void_p, fp, c_int, c_int, c_int, ctypes.c_float, c_int]
+    L.flux_cuda_sampler_predict.restype = c_int
+    L.flux_cuda_sampler_predict.argtypes = [c_void_p, fp, c_int, c_int]
+    L.flux_cuda_sampler_velocity.restype = c_int
+    L.flux_cuda_sampler_velocity.argtypes = [c_void_p, c_void_p, ctypes.c_float]
+    L.flux_cuda_sampler_apply_velocity.restype = c_int
+    L.flux_cuda_sampler_apply_velocity.argtypes = [c_void_p, c_void_p, c_int]
     L.flux_cuda_sampler_download.restype = c_int
     L.flux_cuda_sampler_download.argtypes = [c_void_p, c_void_p, c_void_p]
     L.flux_cuda_sampler_last_run.restype = c_int
@@ -167,6 +176,10 @@ class Context:
             ld_out = N // 2 if epilogue == EPI_SWIGLU_BF16 else N
         check(lib().flux_cuda_gemm_bf16(self.handle, x_ptr, w_ptr, out_ptr, M, N, K, epilogue, ld_out, gate_ptr,
                                         tile_n))
+
+    def gemm_qkv_norm_rope(self, x_ptr, w_ptr, out_ptr, M, hidden, K, wq_ptr, wk_ptr, cos_ptr, sin_ptr, seq):
+        check(lib().flux_cuda_gemm_qkv_norm_rope(self.handle, x_ptr, w_ptr, out_ptr, M, hidden, K, wq_ptr, wk_ptr,
+                                                 cos_ptr, sin_ptr, seq))
 
     def attention(self, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr, out_ld, out_col=0):
         check(lib().flux_cuda_attention(self.handle, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr,
@@ -335,6 +348,18 @@ class Sampler:
         sch = np.ascontiguousarray(schedule, dtype=np.float32)
         check(lib().flux_cuda_sampler_run_steps(self.handle, _fp(sch), len(sch) - 1, first, count, guidance,
                                                 int(record_velocities)))
+
+    def predict(self, schedule, step):
+        """Velocity of the current latent at schedule[step]; the latent is left untouched."""
+        np = _np()
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        check(lib().flux_cuda_sampler_predict(self.handle, _fp(sch), len(sch) - 1, step))
+
+    def velocity(self, dst_dev_ptr, scale=1.0):
+        check(lib().flux_cuda_sampler_velocity(self.handle, dst_dev_ptr, scale))
+
+    def apply_velocity(self, v_dev_ptr, step):
+        check(lib().flux_cuda_sampler_apply_velocity(self.handle, v_dev_ptr, step))
 
     def download(self, latent_ptr, velocities_ptr=None):
         check(lib().flux_cuda_sampler_download(self.handle, latent_ptr, velocities_ptr))

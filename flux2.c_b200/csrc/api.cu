@@ -144,6 +144,39 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
 }
 
 
+int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int hidden, int K,
+                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq) {
+  if (!ctx || !x || !w || !out || !wq || !wk || !cos_t || !sin_t || seq <= 0 || hidden % 128) {
+    set_error("gemm_qkv_norm_rope: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  GemmParams P;
+  memset(&P, 0, sizeof(P));
+  int rc = gemm_make_problem(&P.p[0], x, K, w, M, 3 * hidden, K, 256);
+  if (rc) {
+    set_error("gemm_qkv_norm_rope: unsupported shape/alignment M=%d hidden=%d K=%d (rc %d)", M, hidden, K, rc);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  P.nprob = 1;
+  P.err = ctx->err_dev;
+  EpiSeg &sg = P.p[0].seg[0];
+  sg.mode = EPI_QKV_NORM_ROPE;
+  sg.ld = 3 * hidden;
+  sg.out = out;
+  sg.qk.wq_txt = sg.qk.wq_img = wq;
+  sg.qk.wk_txt = sg.qk.wk_img = wk;
+  sg.qk.cos_t = cos_t;
+  sg.qk.sin_t = sin_t;
+  sg.qk.seq = seq;
+  sg.qk.hidden = hidden;
+  rc = gemm_launch(&P, 256, ctx->num_sms, ctx->stream);
+  if (rc) {
+    set_error("gemm_qkv_norm_rope: launch failed (rc %d)", rc);
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
 int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
                         int v_col, int heads, void *out, long long out_ld, int out_col) {
   if (!ctx || !qkv || !out) return FLUX_CUDA_ERR_ARG;
@@ -267,6 +300,36 @@ int flux_cuda_sampler_run_steps(flux_cuda_sampler *s, const float *schedule, int
                                 float guidance, int record_velocities) {
   return sampler_run(s, schedule, num_steps, first, count, guidance, record_velocities, 1);
 }
+int flux_cuda_sampler_predict(flux_cuda_sampler *s, const float *schedule, int num_steps, int step) {
+  return sampler_run(s, schedule, num_steps, step, 1, 1.0f, 0, 0);
+}
+int flux_cuda_sampler_velocity(flux_cuda_sampler *s, float *dst_dev, float scale) {
+  if (!s || !dst_dev) return FLUX_CUDA_ERR_ARG;
+  if (s->ws->B != 1) {
+    set_error("velocity: only for batch-1 samplers (one member of a guidance pair per GPU)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(s->model->ctx->device);
+  const long long n = static_cast<long long>(s->model->d.latent_ch) * s->ws->n_img;
+  if (launch_scale_copy(dst_dev, s->ws->v, scale, n, s->model->ctx->stream)) {
+    set_error("velocity: launch failed");
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+int flux_cuda_sampler_apply_velocity(flux_cuda_sampler *s, const float *v_dev, int step) {
+  if (!s || !v_dev || step < 0 || step >= s->ws->last_steps) {
+    set_error("apply_velocity: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(s->model->ctx->device);
+  const long long n = static_cast<long long>(s->model->d.latent_ch) * s->ws->n_img;
+  if (launch_euler(s->ws->z, v_dev, s->ws->sched, step, n, s->model->ctx->stream)) {
+    set_error("apply_velocity: launch failed");
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
   return sampler_download(s, latent_out, velocities_out);
 }
@@ -305,6 +368,7 @@ static int run_once(flux_cuda_model *m, int h, int w, const flux_cuda_ref *refs,
   flux_cuda_sampler *s = nullptr;
   int rc = sampler_create(m, h, w, txt_seq, rs.data(), num_refs, ctx_uncond ? 2 : 1, num_steps, &s);
   if (rc) return rc;
+  s->ws->use_graphs = false;  // a one-shot sampler would pay the capture for a single replay
   rc = sampler_upload(s, z0, ctx, ctx_uncond, lat.data());
   if (!rc) rc = sampler_run(s, schedule, num_steps, 0, num_steps, guidance, velocities_out != nullptr, apply_update);
   if (!rc) rc = sampler_download(s, latent_out, velocities_out);

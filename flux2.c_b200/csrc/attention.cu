@@ -14,10 +14,12 @@
 //              score buffers, and  T = P V  (A = P from shared memory, B = V as an MN-major operand)
 //              into one of two TMEM output-tile buffers; S(j+1) is issued before P V(j) so that the
 //              tensor pipe works while the softmax warps handle tile j;
-//   warps 2-5  softmax: one thread per query row (its TMEM lane). Online softmax in base 2 with f32
-//              statistics; P is rounded to bf16 and written to shared memory in the swizzled K-major
-//              layout the MMA expects; the running output lives in registers and is rescaled and
-//              updated from the TMEM tile of the previous step (O = O*alpha + T).
+//   warps 2-9  softmax: two threads per query row (its TMEM lane), each owning 64 of the 128 score and
+//              output columns, so that every SM sub-partition runs two softmax warps. Online softmax in
+//              base 2 with f32 statistics (each thread scans the whole row for the maximum but
+//              exponentiates only its half; the partial row sums are combined once at the end); P is rounded to bf16 and written to one of two shared-memory buffers in the
+//              swizzled K-major layout the MMA expects; the running output lives in registers and is
+//              rescaled and updated from the TMEM tile of the previous step (O = O*alpha + T).
 #include "attention.cuh"
 #include "gemm.cuh"
 #include "ptx.cuh"
@@ -26,24 +28,33 @@
 
 namespace fx {
 
-static constexpr int ATT_THREADS = 192;
+static constexpr int ATT_THREADS = 320;    // warp 0 TMA, warp 1 MMA, warps 2..9 softmax
 static constexpr int TILE = 128;           // queries per CTA, keys per step, head dim
 static constexpr int CHUNK_BYTES = 16384;  // 128 rows x 64 bf16
 static constexpr int OFF_Q = 0;
 static constexpr int OFF_KV = 32768;  // stage s: K at OFF_KV + s*65536, V 32768 after it
-static constexpr int OFF_P = OFF_KV + 2 * 65536;
-static constexpr int OFF_BAR = OFF_P + 32768;
-static constexpr int ATT_SMEM = OFF_BAR + 256 + 1024;
+static constexpr int OFF_P = OFF_KV + 2 * 65536;  // two P buffers of 32 KB
+static constexpr int OFF_BAR = OFF_P + 2 * 32768;
+static constexpr int ATT_SMEM = OFF_BAR + 2048 + 1024;
 
 struct AttnBars {
   uint64_t q_full;
   uint64_t k_full[2], v_full[2], kv_empty[2];
   uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, p_empty;
+  uint64_t p_full[2], p_empty[2];
   uint64_t o_full[2], o_empty[2];
   uint32_t tmem_slot;
   int abort_flag;
+  float xchg[2][128];  // [column half][row]: partial row sums exchanged once, at the end, between the two
+                       // threads that share a query row
 };
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnParams P) {
   extern __shared__ uint8_t smem_raw[];
@@ -65,12 +76,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       mbar_init(&B->v_full[i], 1);
       mbar_init(&B->kv_empty[i], 1);
       mbar_init(&B->s_full[i], 1);
-      mbar_init(&B->s_empty[i], 4);
+      mbar_init(&B->s_empty[i], 8);
+      mbar_init(&B->p_full[i], 8);
+      mbar_init(&B->p_empty[i], 1);
       mbar_init(&B->o_full[i], 1);
-      mbar_init(&B->o_empty[i], 4);
+      mbar_init(&B->o_empty[i], 8);
     }
-    mbar_init(&B->p_full, 4);
-    mbar_init(&B->p_empty, 1);
     B->abort_flag = 0;
     mbar_fence_init();
   }
@@ -115,7 +126,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
       const uint32_t sq = smem_u32(smem + OFF_Q);
-      const uint32_t sp = smem_u32(smem + OFF_P);
       auto issue_s = [&](int j) {
         const uint32_t sk = smem_u32(smem + OFF_KV + (j & 1) * 65536);
         const uint32_t d = tmem + (j & 1) * 128;
@@ -144,11 +154,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         }
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(&B->v_full[s], ph, abort_flag) && mbar_wait(&B->p_full, j & 1, abort_flag) &&
+        ok = mbar_wait(&B->v_full[s], ph, abort_flag) && mbar_wait(&B->p_full[s], ph, abort_flag) &&
              mbar_wait(&B->o_empty[s], ph ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t sv = smem_u32(smem + OFF_KV + s * 65536 + 32768);
+        const uint32_t sp = smem_u32(smem + OFF_P + s * 32768);
         const uint32_t d = tmem + 256 + s * 128;
 #pragma unroll
         for (int kc = 0; kc < 2; ++kc) {
@@ -162,24 +173,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         }
         tc_commit(&B->o_full[s]);
         tc_commit(&B->kv_empty[s]);
-        tc_commit(&B->p_empty);
+        tc_commit(&B->p_empty[s]);
       }
       if (!ok) fail();
     }
     __syncwarp();
   } else {
-    // ---------------------------------------------------------------- softmax + output (warps 2..5)
-    const int q = warp & 3;
-    const int row = q * 32 + lane;  // row inside the tile = TMEM lane
+    // ---------------------------------------------------------------- softmax + output (warps 2..9)
+    // Two threads share a query row: thread (q, hf) owns score columns and output columns [64 hf, 64 hf + 64).
+    const int q = warp & 3;          // TMEM lane quarter this warp may read
+    const int hf = (warp - 2) >> 2;  // column half
+    const int row = q * 32 + lane;   // row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
-    uint8_t *sp_row = smem + OFF_P + row * 128;
     const int sw = row & 7;
+    const float scale = P.scale_log2;
 
-    float o[128];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m = -1e30f, l = 0.f, alpha_prev = 1.f;
-    uint32_t r[32];
+    uint32_t s0[32], s1[32];
     bool ok = true;
 
     auto accumulate = [&](int jj, float a) -> bool {
@@ -188,12 +201,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       w = __all_sync(0xffffffffu, w);
       if (!w) return false;
       tc_fence_after_sync();
+      const uint32_t to = tmem + lane_base + 256 + ob * 128 + hf * 64;
+      tc_ld_32x32(to, s0);
+      tc_ld_32x32(to + 32, s1);
+      tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tc_ld_32x32(tmem + lane_base + 256 + ob * 128 + c * 32, r);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], a, __uint_as_float(r[i]));
+      for (int i = 0; i < 32; ++i) {
+        o[i] = fmaf(o[i], a, __uint_as_float(s0[i]));
+        o[32 + i] = fmaf(o[32 + i], a, __uint_as_float(s1[i]));
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -203,71 +218,83 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 
     for (int j = 0; j < T; ++j) {
       const int sb = j & 1;
-      bool w = mbar_wait(&B->s_full[sb], (j >> 1) & 1, abort_flag);
+      const uint32_t ph = (j >> 1) & 1;
+      bool w = mbar_wait(&B->s_full[sb], ph, abort_flag);
       w = __all_sync(0xffffffffu, w);
       if (!w) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      const uint32_t ts = tmem + lane_base + sb * 128;
-      const int valid = P.seq - j * TILE;  // keys of this tile that exist
-      // pass 1: running maximum (scores scaled into base 2)
-      float mx = m;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tc_ld_32x32(ts + c * 32, r);
+      // Row maximum over all 128 columns: the partner's half is read only for its maximum (TMEM reads are
+      // cheap and this keeps the two warps of a row free of any per-tile synchronisation).
+      const uint32_t tb = tmem + lane_base + sb * 128;
+      const int valid_all = P.seq - j * TILE;          // real keys in this tile
+      const int valid = valid_all - hf * 64;           // ... of them in my half
+      const int valid_o = valid_all - (hf ^ 1) * 64;   // ... in the partner's half
+      float mloc = -1e30f;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        tc_ld_32x32(tb + (hf ^ 1) * 64 + c * 32, s0);
         tc_wait_ld();
-        if (valid >= TILE) {
+        if (valid_o >= 64) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * P.scale_log2);
+          for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, __uint_as_float(s0[i]));
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]) * P.scale_log2);
+            if (c * 32 + i < valid_o) mloc = fmaxf(mloc, __uint_as_float(s0[i]));
         }
       }
-      const float alpha = exp2f(m - mx);
-      // the P buffer is free once P V(j-1) has completed
-      w = mbar_wait(&B->p_empty, (j & 1) ^ 1, abort_flag);
+      tc_ld_32x32(tb + hf * 64, s0);
+      tc_ld_32x32(tb + hf * 64 + 32, s1);
+      tc_wait_ld();
+      // the score buffer is in registers now: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&B->s_empty[sb]);
+      if (valid < 64) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i >= valid) s0[i] = __float_as_uint(-1e30f);
+          if (32 + i >= valid) s1[i] = __float_as_uint(-1e30f);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      const float mx = fmaxf(m, mloc * scale);
+      const float alpha = ex2f(m - mx);
+
+      // the P buffer of this parity is free once P V(j-2) has completed
+      w = mbar_wait(&B->p_empty[sb], ph ^ 1, abort_flag);
       w = __all_sync(0xffffffffu, w);
       if (!w) {
         ok = false;
         break;
       }
-      // pass 2: p = 2^(s - max), row sum, bf16 P into shared memory (swizzled K-major, 64 keys per chunk)
+      // p = 2^(s*scale - max); bf16 P into shared memory: my 64 keys are one swizzled 128-byte row of chunk hf
       float rowsum = 0.f;
+      uint8_t *dst = smem + OFF_P + sb * 32768 + hf * CHUNK_BYTES + row * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tc_ld_32x32(ts + c * 32, r);
-        tc_wait_ld();
-        float p[32];
+      for (int t = 0; t < 8; ++t) {
+        float pv[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(fmaf(__uint_as_float(r[i]), P.scale_log2, -mx));
-          if (valid < TILE && c * 32 + i >= valid) e = 0.f;
-          p[i] = e;
-          rowsum += e;
+        for (int e = 0; e < 8; ++e) {
+          const int i = 8 * t + e;
+          const float sv = __uint_as_float(i < 32 ? s0[i] : s1[i - 32]);
+          pv[e] = ex2f(fmaf(sv, scale, -mx));
+          rowsum += pv[e];
         }
-        uint8_t *dst = sp_row + (c >> 1) * CHUNK_BYTES;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int u = (c & 1) * 4 + t;
-          uint4 v;
-          v.x = pack_bf16x2(p[8 * t + 0], p[8 * t + 1]);
-          v.y = pack_bf16x2(p[8 * t + 2], p[8 * t + 3]);
-          v.z = pack_bf16x2(p[8 * t + 4], p[8 * t + 5]);
-          v.w = pack_bf16x2(p[8 * t + 6], p[8 * t + 7]);
-          *reinterpret_cast<uint4 *>(dst + ((u ^ sw) << 4)) = v;
-        }
+        uint4 v;
+        v.x = pack_bf16x2(pv[0], pv[1]);
+        v.y = pack_bf16x2(pv[2], pv[3]);
+        v.z = pack_bf16x2(pv[4], pv[5]);
+        v.w = pack_bf16x2(pv[6], pv[7]);
+        *reinterpret_cast<uint4 *>(dst + ((t ^ sw) << 4)) = v;
       }
-      tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&B->s_empty[sb]);
-        mbar_arrive(&B->p_full);
-      }
+      if (lane == 0) mbar_arrive(&B->p_full[sb]);
       l = fmaf(l, alpha, rowsum);
       if (j > 0) {
         if (!accumulate(j - 1, alpha_prev)) {
@@ -281,13 +308,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     if (ok) ok = accumulate(T - 1, alpha_prev);
     if (!ok) {
       if (lane == 0) fail();
-    } else if (q0 + row < P.seq) {
+    }
+    // total row sum = my half + the partner's half (both halves used the same running maximum)
+    // Every softmax warp passes here exactly once, whatever happened above, so the pair barrier cannot hang.
+    B->xchg[hf][row] = l;
+    pair_sync(1 + q);
+    l += B->xchg[hf ^ 1][row];
+    if (ok && q0 + row < P.seq) {
       const float inv = 1.0f / l;
-      __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(P.out) +
-                           (static_cast<size_t>(batch) * P.seq + q0 + row) * P.out_ld + P.out_col + head * 128;
-      uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+      __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
+                            (static_cast<size_t>(batch) * P.seq + q0 + row) * P.out_ld + P.out_col + head * 128 +
+                            hf * 64;
+      uint4 *d4 = reinterpret_cast<uint4 *>(dstg);
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
+      for (int t = 0; t < 8; ++t) {
         uint4 v;
         v.x = pack_bf16x2(o[8 * t + 0] * inv, o[8 * t + 1] * inv);
         v.y = pack_bf16x2(o[8 * t + 2] * inv, o[8 * t + 3] * inv);

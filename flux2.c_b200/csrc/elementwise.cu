@@ -10,15 +10,16 @@ namespace fx {
 // K3  AdaLN:  out_bf16[r, :] = (1 + scale) * LayerNorm(x_f32[r, :]) + shift      (no affine, eps 1e-6,
 // biased variance, two-pass like the reference: flux_transformer.c:1021-1046). One warp per row; the
 // row stays in registers between the passes (VPL float4 per lane), so HBM sees one read and one write.
+// Four rows per 128-thread block, three blocks per SM: the 1536-row launches of a 512x512 step fit in one wave.
 // ------------------------------------------------------------------------------------------------
 template <int VPL>
-__global__ void __launch_bounds__(256) adaln_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out,
+__global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out,
                                                     int row0, int rows, int hidden, int seq, int n_txt,
                                                     const float *__restrict__ shift_txt,
                                                     const float *__restrict__ scale_txt,
                                                     const float *__restrict__ shift_img,
                                                     const float *__restrict__ scale_img) {
-  const int local = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int local = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (local >= rows) return;
   const int row = row0 + local;
@@ -60,10 +61,10 @@ int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int 
                  const float *shift_txt, const float *scale_txt, const float *shift_img, const float *scale_img,
                  cudaStream_t st) {
   if (rows <= 0) return 0;
-  const int grid = (rows + 7) / 8;
+  const int grid = (rows + 3) / 4;
   __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
 #define FX_ADALN(V)                                                                                               \
-  adaln_kernel<V><<<grid, 256, 0, st>>>(x, o, row0, rows, hidden, seq, n_txt, shift_txt, scale_txt, shift_img, \
+  adaln_kernel<V><<<grid, 128, 0, st>>>(x, o, row0, rows, hidden, seq, n_txt, shift_txt, scale_txt, shift_img, \
                                         scale_img)
   switch (hidden) {
     case 3072: FX_ADALN(24); break;
@@ -273,6 +274,12 @@ __global__ void cfg_euler_kernel(float *__restrict__ z, const float *__restrict_
   }
 }
 
+__global__ void scale_copy_kernel(float *__restrict__ dst, const float *__restrict__ src, float a, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = a * src[i];
+}
+
 static int ew_grid(long long n) {
   long long b = (n + 255) / 256;
   return static_cast<int>(b < 148 * 4 ? (b > 0 ? b : 1) : 148 * 4);
@@ -280,6 +287,11 @@ static int ew_grid(long long n) {
 
 int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st) {
   euler_kernel<<<ew_grid(n), 256, 0, st>>>(z, v, sched, step, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+int launch_scale_copy(float *dst, const float *src, float a, long long n, cudaStream_t st) {
+  scale_copy_kernel<<<ew_grid(n), 256, 0, st>>>(dst, src, a, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

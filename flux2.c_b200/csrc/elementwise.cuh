@@ -20,6 +20,7 @@ int launch_gemv_multi(const void *W_bf16, const float *x, float *y, int R, int K
 int launch_pack_tokens(const float *z, void *tok_bf16, int C, int n, cudaStream_t st);
 int launch_f32_to_bf16(const float *in, void *out_bf16, long long n, cudaStream_t st);
 int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st);
+int launch_scale_copy(float *dst, const float *src, float a, long long n, cudaStream_t st);
 int launch_cfg_euler(float *z, const float *v_cond, const float *v_uncond, float *v_out, float g, const float *sched,
                      int step, long long n, int apply_update, cudaStream_t st);
 

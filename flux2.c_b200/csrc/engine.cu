@@ -329,6 +329,7 @@ void sampler_free(flux_cuda_sampler *s) {
     cudaStreamSynchronize(s->model->ctx->stream);
     for (void *p : s->ws->allocs) cudaFree(p);
     for (cudaEvent_t e : s->ws->prof_events) cudaEventDestroy(e);
+    for (auto &g : s->ws->graphs) cudaGraphExecDestroy(g.exec);
     if (s->ws->ev0) cudaEventDestroy(s->ws->ev0);
     if (s->ws->ev1) cudaEventDestroy(s->ws->ev1);
     delete s->ws;
@@ -492,8 +493,24 @@ struct Launcher {
   }
   bool open = false;
 
+  // [Q|K|V] projection with the per-head RMSNorm and the rotation applied in the epilogue
+  EpiSeg seg_qkv(void *out, int pos0, const float *nq_t, const float *nk_t, const float *nq_i, const float *nk_i) {
+    EpiSeg s = seg(EPI_QKV_NORM_ROPE, out, 3 * m->d.hidden, 0);
+    s.qk.wq_txt = nq_t;
+    s.qk.wk_txt = nk_t;
+    s.qk.wq_img = nq_i;
+    s.qk.wk_img = nk_i;
+    s.qk.cos_t = ws->rope_cos;
+    s.qk.sin_t = ws->rope_sin;
+    s.qk.pos0 = pos0;
+    s.qk.seq = ws->N;
+    s.qk.n_txt = ws->n_txt;
+    s.qk.hidden = m->d.hidden;
+    return s;
+  }
   static EpiSeg seg(int mode, void *out, long long ld, int col0, const float *gate = nullptr) {
     EpiSeg s;
+    memset(&s, 0, sizeof(s));
     s.mode = mode;
     s.col0 = col0;
     s.ld = ld;
@@ -602,10 +619,9 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
     L.adaln(0, B * N, mt + 0 * h, mt + 1 * h, mi + 0 * h, mi + 1 * h);
     int n = per_stream([&](int, int s, size_t row, int M) {
       return Launcher::Prob{ws->norm + row * h, h, w.qkv[s], M, 3 * h, h,
-                            Launcher::seg(EPI_STORE_BF16, ws->qkv + row * 3 * h, 3 * h, 0), 0, {}};
+                            L.seg_qkv(ws->qkv + row * 3 * h, s ? n_txt : 0, w.nq[0], w.nk[0], w.nq[1], w.nk[1]), 0, {}};
     });
     L.gemm(pr, n, 256);
-    L.qknorm(w.nq[0], w.nk[0], w.nq[1], w.nk[1]);
     L.attention();
     n = per_stream([&](int, int s, size_t row, int M) {
       return Launcher::Prob{ws->cat + row * cat_ld, cat_ld, w.out[s], M, h, h,
@@ -630,10 +646,9 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
     const SingleW &w = m->sgl[blk];
     L.adaln(0, B * N, ms, ms + h, ms, ms + h);
     Launcher::Prob p1{ws->norm, h, w.lin1, B * N, 3 * h + 2 * mlp, h,
-                      Launcher::seg(EPI_STORE_BF16, ws->qkv, 3 * h, 0), 3 * h,
+                      L.seg_qkv(ws->qkv, 0, w.nq, w.nk, w.nq, w.nk), 3 * h,
                       Launcher::seg(EPI_SWIGLU_BF16, ws->cat, cat_ld, h)};
     L.gemm(&p1, 1, 256);
-    L.qknorm(w.nq, w.nk, w.nq, w.nk);
     L.attention();
     Launcher::Prob p2{ws->cat, cat_ld, w.lin2, B * N, h, h + mlp,
                       Launcher::seg(EPI_GATED_RES_F32, ws->hs, h, 0, ms + 2 * h), 0, {}};
@@ -695,31 +710,13 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   return L.rc;
 }
 
-int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
-                int record_velocities, int apply_update) {
-  if (!s || !schedule || num_steps < 1 || first < 0 || count < 1 || first + count > num_steps) {
-    set_error("run: bad argument");
-    return FLUX_CUDA_ERR_ARG;
-  }
-  flux_cuda_model *m = s->model;
-  Workspace *ws = s->ws;
-  if (num_steps > ws->max_steps) {
-    set_error("run: %d steps exceed the sampler's capacity of %d", num_steps, ws->max_steps);
-    return FLUX_CUDA_ERR_ARG;
-  }
-  cudaSetDevice(m->ctx->device);
-  cudaStream_t st = m->ctx->stream;
+// Queues steps [first, first + count) on `st` (directly, or into a stream capture).
+static int enqueue_steps(flux_cuda_model *m, Workspace *ws, int num_steps, int first, int count, float guidance,
+                         int record_velocities, int apply_update, cudaStream_t st) {
   const size_t n = static_cast<size_t>(m->d.latent_ch) * ws->n_img;
-  ws->launches = 0;
-  ws->prof_used = 0;
-  ws->last_steps = num_steps;
-  cudaEventRecord(ws->ev0, st);
   int rc = 0;
   if (first == 0) {
-    // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and
-    // no host synchronisation is needed between consecutive runs.
-    rc = check_cuda(cudaMemcpyAsync(ws->sched, schedule, (num_steps + 1) * 4, cudaMemcpyHostToDevice, st), "schedule");
-    if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->z, ws->z_in, n * 4, cudaMemcpyDeviceToDevice, st), "init latent");
+    rc = check_cuda(cudaMemcpyAsync(ws->z, ws->z_in, n * 4, cudaMemcpyDeviceToDevice, st), "init latent");
     if (!rc) rc = prepare(m, ws, num_steps, st);
   }
   for (int i = first; !rc && i < first + count; ++i) {
@@ -740,6 +737,65 @@ int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int 
     if (!rc && record_velocities)
       rc = check_cuda(cudaMemcpyAsync(ws->vel_rec + static_cast<size_t>(i) * n, v, n * 4, cudaMemcpyDeviceToDevice, st),
                       "record velocity");
+  }
+  return rc;
+}
+
+int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
+                int record_velocities, int apply_update) {
+  if (!s || !schedule || num_steps < 1 || first < 0 || count < 1 || first + count > num_steps) {
+    set_error("run: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  flux_cuda_model *m = s->model;
+  Workspace *ws = s->ws;
+  if (num_steps > ws->max_steps) {
+    set_error("run: %d steps exceed the sampler's capacity of %d", num_steps, ws->max_steps);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  cudaSetDevice(m->ctx->device);
+  cudaStream_t st = m->ctx->stream;
+  ws->launches = 0;
+  ws->prof_used = 0;
+  ws->last_steps = num_steps;
+  cudaEventRecord(ws->ev0, st);
+  int rc = 0;
+  if (first == 0)
+    // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and
+    // no host synchronisation is needed between consecutive runs. It stays outside the captured graph because a
+    // graph would bake the caller's pointer in.
+    rc = check_cuda(cudaMemcpyAsync(ws->sched, schedule, (num_steps + 1) * 4, cudaMemcpyHostToDevice, st), "schedule");
+  if (rc) return rc;
+
+  if (ws->profiling || !ws->use_graphs || first != 0 || count != num_steps) {
+    rc = enqueue_steps(m, ws, num_steps, first, count, guidance, record_velocities, apply_update, st);
+  } else {
+    // The loop is ~150 launches per step: replay it as one CUDA graph so that launch gaps do not add up.
+    Workspace::GraphEntry *hit = nullptr;
+    for (auto &g : ws->graphs)
+      if (g.num_steps == num_steps && g.first == first && g.count == count && g.record == record_velocities &&
+          g.apply == apply_update && g.guidance == guidance)
+        hit = &g;
+    if (!hit) {
+      cudaGraph_t graph = nullptr;
+      rc = check_cuda(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "begin capture");
+      if (rc) return rc;
+      rc = enqueue_steps(m, ws, num_steps, first, count, guidance, record_velocities, apply_update, st);
+      cudaError_t e = cudaStreamEndCapture(st, &graph);
+      if (!rc && e != cudaSuccess) rc = check_cuda(e, "end capture");
+      cudaGraphExec_t exec = nullptr;
+      if (!rc) rc = check_cuda(cudaGraphInstantiate(&exec, graph, 0), "graph instantiate");
+      if (graph) cudaGraphDestroy(graph);
+      if (rc) return rc;
+      if (ws->graphs.size() >= 16) {  // bounded cache: drop the oldest
+        cudaGraphExecDestroy(ws->graphs.front().exec);
+        ws->graphs.erase(ws->graphs.begin());
+      }
+      ws->graphs.push_back({num_steps, first, count, record_velocities, apply_update, guidance, exec, ws->launches});
+      hit = &ws->graphs.back();
+    }
+    ws->launches = hit->launches;
+    rc = check_cuda(cudaGraphLaunch(hit->exec, st), "graph launch");
   }
   cudaEventRecord(ws->ev1, st);
   return rc;

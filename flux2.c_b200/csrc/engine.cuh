@@ -79,6 +79,15 @@ struct Workspace {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int last_steps = 0;
   long long launches = 0;  // kernels launched by the last run
+  // captured CUDA graphs of the run loop, one per distinct (steps, range, guidance, flags)
+  struct GraphEntry {
+    int num_steps, first, count, record, apply;
+    float guidance;
+    cudaGraphExec_t exec;
+    long long launches;
+  };
+  std::vector<GraphEntry> graphs;
+  bool use_graphs = true;
   // optional per-kernel-class timing of a run: one CUDA event pair per launch
   bool profiling = false;
   std::vector<cudaEvent_t> prof_events;  // pairs: [2i] before, [2i+1] after launch i

@@ -16,6 +16,17 @@ enum EpiMode : int {
   EPI_GATED_RES_F32 = 2,  // out_f32[row, col] += gate[col] * acc   (reference: gated_add, flux_transformer.c:90-97)
   EPI_SWIGLU_BF16 = 3,    // tile columns [0,128) = gate, [128,256) = up; out_bf16[row, col/2..] = silu(g)*u
   EPI_STORE_F32_T = 4,    // out_f32[col * ld + row] = acc          (token-major -> channel-major, NLC -> NCHW)
+  EPI_QKV_NORM_ROPE = 5,  // fused [Q|K|V] projection: per-head RMSNorm * w and pair rotation on the Q and K columns
+                          // (apply_qk_norm + apply_rope_2d, flux_transformer.c:1052-1106, 719-741), V stored as is; bf16
+};
+
+// Extra operands of EPI_QKV_NORM_ROPE. Segment-relative column c: c < hidden is Q, c < 2*hidden is K, else V.
+// Row r of the problem sits at sequence position (pos0 + r) % seq; positions below n_txt use the text stream's
+// norm weights. cos/sin: f32 [seq, 128], one value per element (pairs share a value).
+struct QkvNormRope {
+  const float *wq_txt, *wk_txt, *wq_img, *wk_img;
+  const float *cos_t, *sin_t;
+  int pos0, seq, n_txt, hidden;
 };
 
 struct EpiSeg {
@@ -24,6 +35,7 @@ struct EpiSeg {
   long long ld;       // destination leading dimension in elements
   void *out;
   const float *gate;  // EPI_GATED_RES_F32 only; indexed by the segment-relative column
+  QkvNormRope qk;     // EPI_QKV_NORM_ROPE only
 };
 
 struct alignas(64) GemmProblem {

@@ -148,6 +148,72 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         }
       }
     } break;
+    case EPI_QKV_NORM_ROPE: {
+      const QkvNormRope &qk = sg.qk;
+      const int pos = (qk.pos0 + row) % qk.seq;
+      __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
+#pragma unroll 1
+      for (int hd = 0; hd < BN / 128; ++hd) {
+        const int col = nrel + hd * 128;  // first column of this head inside the [Q|K|V] segment
+        const uint32_t th = taddr + hd * 128;
+        float rinv = 1.f;
+        const bool rotate = col < 2 * qk.hidden;
+        const float *w = nullptr;
+        if (rotate) {
+          float ss = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tc_ld_32x32(th + c * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ss = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), ss);
+          }
+          rinv = rsqrtf(ss * (1.0f / 128.0f) + 1e-6f);
+          const bool is_k = col >= qk.hidden;
+          w = (pos < qk.n_txt) ? (is_k ? qk.wk_txt : qk.wq_txt) : (is_k ? qk.wk_img : qk.wq_img);
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tc_ld_32x32(th + c * 32, r);
+          tc_wait_ld();
+          if (row_ok) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst + hd * 128 + c * 32);
+            if (rotate) {
+              const float4 *w4 = reinterpret_cast<const float4 *>(w + c * 32);
+              const float4 *c4 = reinterpret_cast<const float4 *>(qk.cos_t + static_cast<size_t>(pos) * 128 + c * 32);
+              const float4 *s4 = reinterpret_cast<const float4 *>(qk.sin_t + static_cast<size_t>(pos) * 128 + c * 32);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const float4 ww = __ldg(w4 + 2 * j + e);
+                  const float4 cc = __ldg(c4 + 2 * j + e);
+                  const float4 sn = __ldg(s4 + 2 * j + e);
+                  const float x0 = __uint_as_float(r[8 * j + 4 * e + 0]) * rinv * ww.x;
+                  const float x1 = __uint_as_float(r[8 * j + 4 * e + 1]) * rinv * ww.y;
+                  const float x2 = __uint_as_float(r[8 * j + 4 * e + 2]) * rinv * ww.z;
+                  const float x3 = __uint_as_float(r[8 * j + 4 * e + 3]) * rinv * ww.w;
+                  o[2 * e + 0] = pack_bf16x2(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x);
+                  o[2 * e + 1] = pack_bf16x2(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z);
+                }
+                d4[j] = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                d4[j] = v;
+              }
+            }
+          }
+        }
+      }
+    } break;
     default:
       break;
   }

@@ -134,6 +134,18 @@ int flux_cuda_sampler_run(flux_cuda_sampler *s, const float *schedule, int num_s
  * call with first > 0 continues from where the previous one stopped. */
 int flux_cuda_sampler_run_steps(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count,
                                 float guidance, int record_velocities);
+/*
+ * Guidance pair split across two GPUs (the reference runs the two passes one after the other on one device,
+ * flux_sample.c:485-499). Each GPU holds a replica and a batch-1 sampler with ITS context (conditional on one
+ * rank, unconditional on the other) and the same latent. Per step: flux_cuda_sampler_predict computes this
+ * rank's velocity without touching the latent; flux_cuda_sampler_velocity writes scale * v to a device buffer
+ * (scale = g on the conditional rank, 1 - g on the other); the caller sums the two buffers across the pair (one
+ * all-reduce of latent_ch*h*w floats over NVLink); flux_cuda_sampler_apply_velocity adds dt * v_sum to the
+ * latent on both ranks, which therefore stay bit-identical. All calls are asynchronous on the context's stream.
+ */
+int flux_cuda_sampler_predict(flux_cuda_sampler *s, const float *schedule, int num_steps, int step);
+int flux_cuda_sampler_velocity(flux_cuda_sampler *s, float *dst_dev, float scale);
+int flux_cuda_sampler_apply_velocity(flux_cuda_sampler *s, const float *v_dev, int step);
 /* Device -> host copy of the latent (and recorded velocities), then waits and checks for kernel errors. */
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
 /* CUDA-event time of the last flux_cuda_sampler_run in ms (valid after a sync), and its kernel count. */
@@ -182,6 +194,16 @@ void flux_cuda_init_noise(int channels, int h, int w, long long seed, float *out
  */
 int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int N, int K,
                         int epilogue, long long ld_out, const float *gate, int tile_n);
+
+/*
+ * The fused [Q|K|V] projection as the engine runs it: out_bf16[M, 3*hidden] = x[M,K] * w[3*hidden,K]^T with the
+ * per-head RMSNorm (weights wq / wk, f32 [128]) and the consecutive-pair rotation (cos/sin f32 [seq,128], row r at
+ * position r % seq) applied to the Q and K thirds inside the GEMM epilogue, V stored unchanged. Replaces the three
+ * flux_linear_nobias calls + apply_qk_norm + apply_rope_2d of flux_transformer.c:1826-1841 / 3051-3079.
+ * hidden % 256 == 0 (two 128-wide heads per output tile), K % 64 == 0.
+ */
+int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int hidden, int K,
+                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq);
 
 /*
  * Joint attention over a fused projection buffer qkv[batch*seq, ld] (bf16): for every head,

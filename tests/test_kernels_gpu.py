@@ -79,3 +79,35 @@ def test_qk_norm_rope_matches_torch(fx, ctx, batch, seq, heads):
     assert _rel(work[:, :hid].float(), ref_one(qkv[:, :hid], wq)) < 4e-3
     assert _rel(work[:, hid:2 * hid].float(), ref_one(qkv[:, hid:2 * hid], wk)) < 4e-3
     assert torch.equal(work[:, 2 * hid:], qkv[:, 2 * hid:])  # V untouched
+
+
+@pytest.mark.parametrize("M,heads,K,seq", [(100, 2, 256, 50), (1536, 24, 3072, 1536), (300, 4, 128, 300)])
+def test_fused_qkv_projection_norm_rope(fx, ctx, M, heads, K, seq):
+    """GEMM epilogue variant: projection + per-head RMSNorm + rotation on Q, K; V untouched."""
+    hid = heads * 128
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(3 * hid, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wq = torch.randn(128, device="cuda", generator=g)
+    wk = torch.randn(128, device="cuda", generator=g)
+    ang = torch.rand(seq, 64, device="cuda", generator=g) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, dim=1).contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, dim=1).contiguous()
+    out = torch.zeros(M, 3 * hid, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.gemm_qkv_norm_rope(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, hid, K, wq.data_ptr(), wk.data_ptr(),
+                           cos.data_ptr(), sin.data_ptr(), seq)
+    ctx.sync()
+    y = x.float() @ w.float().t()
+    pos = torch.arange(M, device="cuda") % seq
+
+    def ref_one(t, wv):
+        t = t.reshape(M, heads, 128)
+        t = t * torch.rsqrt((t * t).mean(-1, keepdim=True) + 1e-6) * wv
+        t0, t1 = t[..., 0::2], t[..., 1::2]
+        c, s = cos[pos][:, None, 0::2], sin[pos][:, None, 0::2]
+        return torch.stack([t0 * c - t1 * s, t1 * c + t0 * s], dim=-1).reshape(M, hid)
+
+    assert _rel(out[:, :hid].float(), ref_one(y[:, :hid], wq)) < 4e-3
+    assert _rel(out[:, hid:2 * hid].float(), ref_one(y[:, hid:2 * hid], wk)) < 4e-3
+    assert _rel(out[:, 2 * hid:].float(), y[:, 2 * hid:]) < 4e-3
