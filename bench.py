@@ -204,9 +204,9 @@ def run_micro(args):
         w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
         out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
         torch.cuda.synchronize()
-        ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K))
+        ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, tile_n=args.tile_n))
         tf = 2.0 * M * N * K / ms / 1e9
-        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "ms": ms, "tflops": tf, "frac_of_burst_peak":
+        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "ms": ms, "tflops": tf, "frac_of_burst_peak":
                           tf / peaks["bf16"], "peak_source": peaks["source"]}))
     elif args.micro == "attn":
         seq, heads = args.seq, 24
@@ -404,6 +404,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
+    ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -45,6 +45,8 @@ def _declare(L):
     L.flux_cuda_ctx_sync.argtypes = [c_void_p]
     L.flux_cuda_ctx_stream.restype = c_void_p
     L.flux_cuda_ctx_stream.argtypes = [c_void_p]
+    L.flux_cuda_ctx_set_gemm_pair.restype = c_int
+    L.flux_cuda_ctx_set_gemm_pair.argtypes = [c_void_p, c_int]
     L.flux_cuda_gemm_bf16.restype = c_int
     L.flux_cuda_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll,
                                       c_void_p, c_int]
@@ -153,6 +155,9 @@ class Context:
 
     def sync(self):
         check(lib().flux_cuda_ctx_sync(self.handle))
+
+    def set_gemm_pair(self, on):
+        check(lib().flux_cuda_ctx_set_gemm_pair(self.handle, int(on)))
 
     @property
     def stream(self):

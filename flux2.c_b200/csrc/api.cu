@@ -4,6 +4,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -81,7 +82,8 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
     flux_cuda_ctx_destroy(c);
     return rc;
   }
-  if (gemm_init() != 0 || attn_init() != 0 || elementwise_init() != 0) {
+  if (const char *e = getenv("FLUX_CUDA_GEMM_PAIR")) c->gemm_pair = atoi(e) != 0;
+  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || elementwise_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
     flux_cuda_ctx_destroy(c);
     return FLUX_CUDA_ERR_CUDA;
@@ -109,6 +111,12 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx) {
 
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
+int flux_cuda_ctx_set_gemm_pair(flux_cuda_ctx *ctx, int on) {
+  if (!ctx) return FLUX_CUDA_ERR_ARG;
+  ctx->gemm_pair = on != 0;
+  return FLUX_CUDA_OK;
+}
+
 int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int N, int K,
                         int epilogue, long long ld_out, const float *gate, int tile_n) {
   if (!ctx || !x || !w || !out) {
@@ -121,9 +129,10 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
   }
   int bn = tile_n;
   if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  const bool pair = bn == 512;  // 256-wide tiles computed by CTA pairs
   GemmParams P;
   memset(&P, 0, sizeof(P));
-  int rc = gemm_make_problem(&P.p[0], x, K, w, M, N, K, bn);
+  int rc = pair ? gemm_make_problem_pair(&P.p[0], x, K, w, M, N, K) : gemm_make_problem(&P.p[0], x, K, w, M, N, K, bn);
   if (rc) {
     set_error("gemm: unsupported shape/alignment M=%d N=%d K=%d tile_n=%d (rc %d)", M, N, K, bn, rc);
     return FLUX_CUDA_ERR_ARG;
@@ -135,7 +144,7 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
   P.p[0].seg[0].ld = ld_out;
   P.p[0].seg[0].out = out;
   P.p[0].seg[0].gate = gate;
-  rc = gemm_launch(&P, bn, ctx->num_sms, ctx->stream);
+  rc = pair ? gemm2_launch(&P, ctx->num_sms, ctx->stream) : gemm_launch(&P, bn, ctx->num_sms, ctx->stream);
   if (rc) {
     set_error("gemm: launch failed (rc %d: %s)", rc, cudaGetErrorString(cudaGetLastError()));
     return rc <= -8 ? FLUX_CUDA_ERR_CUDA : FLUX_CUDA_ERR_ARG;

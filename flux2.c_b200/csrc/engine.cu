@@ -534,8 +534,10 @@ struct Launcher {
     memset(&P, 0, sizeof(P));
     P.nprob = n;
     P.err = m->ctx->err_dev;
+    const bool pair = bn == 256 && m->ctx->gemm_pair;
     for (int i = 0; i < n; ++i) {
-      int r = gemm_make_problem(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K, bn);
+      int r = pair ? gemm_make_problem_pair(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K)
+                   : gemm_make_problem(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K, bn);
       if (r) return fail("gemm_make_problem", r);
       P.p[i].seg[0] = pr[i].s0;
       if (pr[i].n_split > 0 && pr[i].n_split < pr[i].N) {
@@ -544,7 +546,7 @@ struct Launcher {
       }
     }
     begin(KC_GEMM);
-    int r = gemm_launch(&P, bn, m->ctx->num_sms, st);
+    int r = pair ? gemm2_launch(&P, m->ctx->num_sms, st) : gemm_launch(&P, bn, m->ctx->num_sms, st);
     count();
     if (r) return fail("gemm_launch", r);
   }

@@ -63,6 +63,10 @@ struct alignas(64) GemmParams {
 int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn);
 // Launches the persistent kernel over P.nprob problems. bn must match gemm_make_problem.
 int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream);
+// Paired variant (gemm2_tcgen05.cu): two CTAs per 256 x 256 tile, tile width fixed at 256.
+int gemm2_init();
+int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K);
+int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream);
 int gemm_init();  // resolves cuTensorMapEncodeTiled and opts the kernels into large shared memory
 
 // Tensor-map helper shared with the attention kernel: rank-2 bf16 tensor [rows, cols], cols contiguous,

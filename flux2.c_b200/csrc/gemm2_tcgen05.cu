@@ -1,0 +1,234 @@
+// K1 (paired variant): the same GEMM as gemm_tcgen05.cu, computed by PAIRS of CTAs on neighbouring SMs
+// (a cluster of two, tcgen05 cta_group::2). A pair owns a 256 x 256 output tile: each CTA stages its own 128
+// rows of X and only HALF of the W tile (128 of the 256 output columns' rows); one thread of the leader CTA
+// issues tcgen05.mma M256 N256 K16, which reads both CTAs' shared memory and writes each CTA's half of the
+// accumulator into that CTA's TMEM. Per k-slice a CTA therefore pulls 32 KB through L2 instead of 48 KB for the
+// same 128 x 256 x 64 of work, which matters because the single-CTA kernel is limited by operand delivery
+// (~16 TB/s of L2->SM traffic), not by the tensor pipe. No multicast is used: every CTA issues its own loads.
+//
+// Synchronisation: "full" barriers live in the leader (both CTAs' TMA loads complete bytes on them); "empty"
+// and "accumulator full" barriers exist in both CTAs and are signalled by one multicast tcgen05.commit;
+// "accumulator drained" lives in the leader and collects the arrivals of all eight epilogue warps of the pair.
+#include <cudaTypedefs.h>
+
+#include "gemm.cuh"
+#include "gemm_epilogue.cuh"
+#include "ptx.cuh"
+
+namespace fx {
+
+static constexpr int P_BM = 128;  // rows per CTA (256 per pair)
+static constexpr int P_BN = 256;
+static constexpr int P_BK = 64;
+static constexpr int P_STAGES = 6;
+static constexpr int P_A_BYTES = P_BM * P_BK * 2;        // 16 KB
+static constexpr int P_B_BYTES = (P_BN / 2) * P_BK * 2;  // 16 KB: this CTA's half of the W tile
+static constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+static constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 256 + 1024;
+static constexpr int P_THREADS = 192;
+
+__global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __grid_constant__ GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t *full = bars;                  // used in the leader only
+  uint64_t *empty = bars + P_STAGES;      // both CTAs
+  uint64_t *tfull = bars + 2 * P_STAGES;  // both CTAs
+  uint64_t *tempty = tfull + 2;           // leader only, 8 arrivals
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything can arrive on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    atomicCAS(P.err, 0, code);
+  };
+  // pair-level tile -> (problem, first row of the PAIR's tile, first column)
+  auto decode = [&](int tile, int &prob, int &m0, int &n0) {
+    prob = 0;
+    while (prob + 1 < P.nprob && tile >= P.tile_end[prob]) ++prob;
+    const int local = tile - (prob ? P.tile_end[prob - 1] : 0);
+    const int tm = P.p[prob].tiles_m;
+    m0 = (local % tm) * (2 * P_BM);
+    n0 = (local / tm) * P_BN;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      for (int i = 0; i < P.nprob; ++i) {
+        tma_prefetch_desc(&P.p[i].tmA);
+        tma_prefetch_desc(&P.p[i].tmB);
+      }
+      uint32_t kiter = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < P.total_tiles; tile += num_pairs) {
+        int prob, m0, n0;
+        decode(tile, prob, m0, n0);
+        const GemmProblem &pb = P.p[prob];
+        const int KB = pb.K / P_BK;
+        for (int kb = 0; kb < KB; ++kb, ++kiter) {
+          const int s = kiter % P_STAGES;
+          const uint32_t ph = (kiter / P_STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+            fail(KERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t *sa = smem + s * P_STAGE_BYTES;
+          uint8_t *sb = sa + P_A_BYTES;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
+          tma_load_2d_pair(sa, &pb.tmA, full_leader, kb * P_BK, m0 + rank * P_BM);
+          tma_load_2d_pair(sb, &pb.tmB, full_leader, kb * P_BK, n0 + rank * (P_BN / 2));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * P_BM, P_BN, 0, 0);
+      uint32_t kiter = 0, it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < P.total_tiles; tile += num_pairs, ++it) {
+        int prob, m0, n0;
+        decode(tile, prob, m0, n0);
+        const int KB = P.p[prob].K / P_BK;
+        const int acc = it & 1;
+        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          fail(KERR_WAIT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + acc * P_BN;
+        for (int kb = 0; kb < KB; ++kb, ++kiter) {
+          const int s = kiter % P_STAGES;
+          const uint32_t ph = (kiter / P_STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag)) {
+            fail(KERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * P_STAGE_BYTES);
+          const uint64_t ad = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(sa + P_A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < P_BK / 16; ++k) tc_mma_ss_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          tc_commit_pair(&empty[s], 3);  // frees the stage in both CTAs
+        }
+        if (ok) tc_commit_pair(&tfull[acc], 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;
+    uint32_t it = 0;
+    for (int tile = pair; tile < P.total_tiles; tile += num_pairs, ++it) {
+      int prob, m0, n0;
+      decode(tile, prob, m0, n0);
+      const int acc = it & 1;
+      bool ok = mbar_wait(&tfull[acc], (it >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) fail(KERR_WAIT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * P_BN + (static_cast<uint32_t>(q * 32) << 16);
+      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+int gemm2_init() {
+  cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+  return e == cudaSuccess ? 0 : -2;
+}
+
+// Same contract as gemm_launch for bn = 256, but problems must have been made with gemm_make_problem_pair.
+int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
+  if (P->nprob < 1 || P->nprob > GEMM_MAX_PROBLEMS) return -5;
+  int acc = 0;
+  for (int i = 0; i < P->nprob; ++i) {
+    const GemmProblem &pb = P->p[i];
+    if (pb.n_split % P_BN) return -6;
+    acc += pb.tiles_m * pb.tiles_n;
+    P->tile_end[i] = acc;
+  }
+  P->total_tiles = acc;
+  int pairs = num_sms / 2;
+  if (acc < pairs) pairs = acc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(P_THREADS);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm2_bf16_tn_kernel, *P) == cudaSuccess ? 0 : -8;
+}
+
+int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % P_BK) || (N % P_BN) || ldx < K) return -5;
+  int rc = make_tmap_2d_bf16(&p->tmA, X, M, K, ldx, P_BM, P_BK);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&p->tmB, W, N, K, K, P_BN / 2, P_BK);
+  if (rc) return rc;
+  p->M = M;
+  p->N = N;
+  p->K = K;
+  p->n_split = N;
+  p->tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
+  p->tiles_n = N / P_BN;
+  return 0;
+}
+
+}  // namespace fx

@@ -17,6 +17,7 @@
 // [Q|K|V|gate|up] split of the single-stream block (flux_transformer.c:3051-3058) and the final
 // NLC -> NCHW transpose (flux_transformer.c:3547-3552).
 #include "gemm.cuh"
+#include "gemm_epilogue.cuh"
 #include "ptx.cuh"
 
 #include <cudaTypedefs.h>
@@ -38,186 +39,6 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
   static constexpr int TMEM_COLS = 2 * BN;
 };
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
-
-template <int BN>
-__device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row) {
-  const bool second = n0 >= pb.n_split;
-  const EpiSeg &sg = second ? pb.seg[1] : pb.seg[0];
-  const int nrel = n0 - (second ? pb.n_split : 0);  // segment-relative first column of this tile
-  const int row = m0 + lane_row;
-  const bool row_ok = row < pb.M;
-  uint32_t r[32];
-
-  switch (sg.mode) {
-    case EPI_STORE_BF16: {
-      __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tc_ld_32x32(taddr + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-          uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 32);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            d4[j] = v;
-          }
-        }
-      }
-    } break;
-    case EPI_STORE_F32: {
-      float *dst = reinterpret_cast<float *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tc_ld_32x32(taddr + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-          uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) d4[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        }
-      }
-    } break;
-    case EPI_GATED_RES_F32: {
-      float *dst = reinterpret_cast<float *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
-      const float *gate = sg.gate + nrel;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tc_ld_32x32(taddr + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-          float4 *d4 = reinterpret_cast<float4 *>(dst + c * 32);
-          const float4 *g4 = reinterpret_cast<const float4 *>(gate + c * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 h = d4[j];
-            const float4 g = __ldg(g4 + j);
-            h.x = fmaf(g.x, __uint_as_float(r[4 * j + 0]), h.x);
-            h.y = fmaf(g.y, __uint_as_float(r[4 * j + 1]), h.y);
-            h.z = fmaf(g.z, __uint_as_float(r[4 * j + 2]), h.z);
-            h.w = fmaf(g.w, __uint_as_float(r[4 * j + 3]), h.w);
-            d4[j] = h;
-          }
-        }
-      }
-    } break;
-    case EPI_SWIGLU_BF16: {
-      if constexpr (BN == 256) {
-        __nv_bfloat16 *dst =
-            reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel / 2;
-        uint32_t u[32];
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tc_ld_32x32(taddr + c * 32, r);
-          tc_ld_32x32(taddr + 128 + c * 32, u);
-          tc_wait_ld();
-          if (row_ok) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 32);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float o[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                o[e] = silu_f(__uint_as_float(r[8 * j + e])) * __uint_as_float(u[8 * j + e]);
-              uint4 v;
-              v.x = pack_bf16x2(o[0], o[1]);
-              v.y = pack_bf16x2(o[2], o[3]);
-              v.z = pack_bf16x2(o[4], o[5]);
-              v.w = pack_bf16x2(o[6], o[7]);
-              d4[j] = v;
-            }
-          }
-        }
-      }
-    } break;
-    case EPI_STORE_F32_T: {
-      float *dst = reinterpret_cast<float *>(sg.out) + static_cast<size_t>(sg.col0 + nrel) * sg.ld + row;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tc_ld_32x32(taddr + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) dst[static_cast<size_t>(c * 32 + j) * sg.ld] = __uint_as_float(r[j]);
-        }
-      }
-    } break;
-    case EPI_QKV_NORM_ROPE: {
-      const QkvNormRope &qk = sg.qk;
-      const int pos = (qk.pos0 + row) % qk.seq;
-      __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
-#pragma unroll 1
-      for (int hd = 0; hd < BN / 128; ++hd) {
-        const int col = nrel + hd * 128;  // first column of this head inside the [Q|K|V] segment
-        const uint32_t th = taddr + hd * 128;
-        float rinv = 1.f;
-        const bool rotate = col < 2 * qk.hidden;
-        const float *w = nullptr;
-        if (rotate) {
-          float ss = 0.f;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tc_ld_32x32(th + c * 32, r);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) ss = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), ss);
-          }
-          rinv = rsqrtf(ss * (1.0f / 128.0f) + 1e-6f);
-          const bool is_k = col >= qk.hidden;
-          w = (pos < qk.n_txt) ? (is_k ? qk.wk_txt : qk.wq_txt) : (is_k ? qk.wk_img : qk.wq_img);
-        }
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tc_ld_32x32(th + c * 32, r);
-          tc_wait_ld();
-          if (row_ok) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst + hd * 128 + c * 32);
-            if (rotate) {
-              const float4 *w4 = reinterpret_cast<const float4 *>(w + c * 32);
-              const float4 *c4 = reinterpret_cast<const float4 *>(qk.cos_t + static_cast<size_t>(pos) * 128 + c * 32);
-              const float4 *s4 = reinterpret_cast<const float4 *>(qk.sin_t + static_cast<size_t>(pos) * 128 + c * 32);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint32_t o[4];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const float4 ww = __ldg(w4 + 2 * j + e);
-                  const float4 cc = __ldg(c4 + 2 * j + e);
-                  const float4 sn = __ldg(s4 + 2 * j + e);
-                  const float x0 = __uint_as_float(r[8 * j + 4 * e + 0]) * rinv * ww.x;
-                  const float x1 = __uint_as_float(r[8 * j + 4 * e + 1]) * rinv * ww.y;
-                  const float x2 = __uint_as_float(r[8 * j + 4 * e + 2]) * rinv * ww.z;
-                  const float x3 = __uint_as_float(r[8 * j + 4 * e + 3]) * rinv * ww.w;
-                  o[2 * e + 0] = pack_bf16x2(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x);
-                  o[2 * e + 1] = pack_bf16x2(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z);
-                }
-                d4[j] = make_uint4(o[0], o[1], o[2], o[3]);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-                d4[j] = v;
-              }
-            }
-          }
-        }
-      }
-    } break;
-    default:
-      break;
-  }
-}
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __grid_constant__ GemmParams P) {

@@ -36,6 +36,11 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx);
 /* The context's cudaStream_t, for callers that time with their own CUDA events. */
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx);
 
+/* Chooses how the 256-column GEMM tiles are computed: 0 = one CTA per 128 x 256 tile, 1 = a pair of CTAs on
+ * neighbouring SMs per 256 x 256 tile (tcgen05 cta_group::2; each CTA stages half of the weight tile). Also
+ * settable with the environment variable FLUX_CUDA_GEMM_PAIR before the context is created. */
+int flux_cuda_ctx_set_gemm_pair(flux_cuda_ctx *ctx, int on);
+
 /* ------------------------------------------------------------------------------------------------
  * Model: the FLUX.2-klein diffusion transformer resident on one GPU (bf16 weights).
  * ---------------------------------------------------------------------------------------------- */
@@ -190,7 +195,8 @@ void flux_cuda_init_noise(int channels, int h, int w, long long seed, float *out
  *   SWIGLU_BF16              w rows interleaved per 256 as [128 gate rows | 128 up rows];
  *                            out_bf16[M, N/2] = silu(gate) * up   (flux_transformer.c:1737-1763);
  *   STORE_F32_T              out_f32[c * ld_out + r] = acc        (flux_transformer.c:3547-3552).
- * K % 64 == 0, N % tile_n == 0, tile_n in {128, 256} (0 = choose).
+ * K % 64 == 0, N % tile_n == 0, tile_n in {128, 256} (0 = choose); tile_n = 512 selects the paired kernel
+ * (256-column tiles, two CTAs per 256 x 256 tile, N % 256 == 0).
  */
 int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int N, int K,
                         int epilogue, long long ld_out, const float *gate, int tile_n);

@@ -109,3 +109,49 @@ def test_gemm_rejects_bad_shape(fx, ctx):
     out = torch.zeros(128, 256, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(fx.FluxCudaError):
         ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), 128, 256, 48, fx.EPI_STORE_BF16)  # K % 64 != 0
+
+
+# ---- paired kernel (two CTAs per 256 x 256 tile, tcgen05 cta_group::2): tile_n = 512 selects it
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 256), (1536, 9216, 3072), (1536, 3072, 12288),
+                                   (48, 3072, 3072), (300, 768, 128), (129, 256, 192)])
+def test_gemm_pair_store_f32(fx, ctx, M, N, K):
+    x, w = _inputs(M, N, K, seed=11)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_F32, tile_n=512)
+    ctx.sync()
+    assert torch.isfinite(out).all()
+    assert _rel(out, x.double() @ w.double().t()) < 3e-5
+
+
+def test_gemm_pair_agrees_with_single_cta_kernel(fx, ctx):
+    M, N, K = 1000, 2048, 1024
+    x, w = _inputs(M, N, K, seed=12)
+    a = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), a.data_ptr(), M, N, K, fx.EPI_STORE_BF16, tile_n=256)
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), b.data_ptr(), M, N, K, fx.EPI_STORE_BF16, tile_n=512)
+    ctx.sync()
+    assert torch.equal(a, b)  # same k order, same accumulation: bit-identical
+
+
+def test_gemm_pair_swiglu_and_gated(fx, ctx):
+    M, Nh, K = 1024, 1024, 512
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    wg = (torch.randn(Nh, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(Nh, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    w = torch.stack([wg.view(Nh // 128, 128, K), wu.view(Nh // 128, 128, K)], dim=1).reshape(2 * Nh, K).contiguous()
+    out = torch.zeros(M, Nh, device="cuda", dtype=torch.bfloat16)
+    h0 = torch.randn(M, Nh, device="cuda", generator=g)
+    gate = torch.randn(Nh, device="cuda", generator=g)
+    h = h0.clone()
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, 2 * Nh, K, fx.EPI_SWIGLU_BF16, tile_n=512)
+    ctx.gemm_bf16(x.data_ptr(), wg.data_ptr(), h.data_ptr(), M, Nh, K, fx.EPI_GATED_RES_F32, gate_ptr=gate.data_ptr(),
+                  tile_n=512)
+    ctx.sync()
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert _rel(out.float(), ref) < 4e-3
+    assert _rel(h, h0.double() + gate.double() * (x.double() @ wg.double().t())) < 3e-5
