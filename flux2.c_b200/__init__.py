@@ -108,6 +108,8 @@ def _declare(L):
     L.flux_cuda_sampler_set_profiling.argtypes = [c_void_p, c_int]
     L.flux_cuda_sampler_profile.restype = c_int
     L.flux_cuda_sampler_profile.argtypes = [c_void_p, fp, ctypes.POINTER(c_ll)]
+    L.flux_cuda_sampler_profile_launches.restype = c_int
+    L.flux_cuda_sampler_profile_launches.argtypes = [c_void_p, fp, ctypes.POINTER(c_int), c_int, ctypes.POINTER(c_int)]
     L.flux_cuda_official_schedule.restype = None
     L.flux_cuda_official_schedule.argtypes = [c_int, c_int, fp]
     L.flux_cuda_linear_schedule.restype = None
@@ -384,6 +386,14 @@ class Sampler:
         n = (ctypes.c_longlong * 5)()
         check(lib().flux_cuda_sampler_profile(self.handle, ms, n))
         return {k: {"ms": ms[i], "n": n[i]} for i, k in enumerate(("gemm", "attn", "adaln", "qknorm", "other"))}
+
+    def profile_launches(self, capacity=8192):
+        """[(ms, class index)] of the last profiled run, in launch order."""
+        ms = (ctypes.c_float * capacity)()
+        cls = (ctypes.c_int * capacity)()
+        n = ctypes.c_int()
+        check(lib().flux_cuda_sampler_profile_launches(self.handle, ms, cls, capacity, ctypes.byref(n)))
+        return [(ms[i], cls[i]) for i in range(n.value)]
 
     def close(self):
         if self.handle:

@@ -361,6 +361,21 @@ int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long lon
   return sampler_profile(s, ms_by_class, launches_by_class);
 }
 
+int flux_cuda_sampler_profile_launches(flux_cuda_sampler *s, float *ms, int *kernel_class, int capacity, int *count) {
+  if (!s || !ms || !kernel_class || !count) return FLUX_CUDA_ERR_ARG;
+  Workspace *ws = s->ws;
+  int n = 0;
+  for (size_t i = 0; i < ws->prof_used && n < capacity; ++i, ++n) {
+    if (cudaEventElapsedTime(&ms[n], ws->prof_events[2 * i], ws->prof_events[2 * i + 1]) != cudaSuccess) {
+      set_error("profile: events not complete (synchronize first)");
+      return FLUX_CUDA_ERR_CUDA;
+    }
+    kernel_class[n] = ws->prof_class[i];
+  }
+  *count = n;
+  return FLUX_CUDA_OK;
+}
+
 static int run_once(flux_cuda_model *m, int h, int w, const flux_cuda_ref *refs, int num_refs, const float *ctx,
                     const float *ctx_uncond, int txt_seq, const float *schedule, int num_steps, float guidance,
                     const float *z0, float *latent_out, float *velocities_out, int apply_update) {

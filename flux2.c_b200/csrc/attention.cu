@@ -22,20 +22,21 @@
 //              rescaled and updated from the TMEM tile of the previous step (O = O*alpha + T).
 #include "attention.cuh"
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cudaTypedefs.h>
 
 namespace fx {
 
-static constexpr int ATT_THREADS = 320;    // warp 0 TMA, warp 1 MMA, warps 2..9 softmax
+static constexpr int ATT_THREADS = 576;    // warp 0 TMA, warp 1 MMA, warps 2..17 softmax
 static constexpr int TILE = 128;           // queries per CTA, keys per step, head dim
 static constexpr int CHUNK_BYTES = 16384;  // 128 rows x 64 bf16
 static constexpr int OFF_Q = 0;
 static constexpr int OFF_KV = 32768;  // stage s: K at OFF_KV + s*65536, V 32768 after it
 static constexpr int OFF_P = OFF_KV + 2 * 65536;  // two P buffers of 32 KB
 static constexpr int OFF_BAR = OFF_P + 2 * 32768;
-static constexpr int ATT_SMEM = OFF_BAR + 2048 + 1024;
+static constexpr int ATT_SMEM = OFF_BAR + 2560;  // no alignment slack: the kernel checks the base instead
 
 struct AttnBars {
   uint64_t q_full;
@@ -45,8 +46,9 @@ struct AttnBars {
   uint64_t o_full[2], o_empty[2];
   uint32_t tmem_slot;
   int abort_flag;
-  float xchg[2][128];  // [column half][row]: partial row sums exchanged once, at the end, between the two
-                       // threads that share a query row
+  uint64_t mx_full[2][4];  // [tile parity][lane quarter]: the four warps of a quarter published their maxima
+  __nv_bfloat16 xchg[2][4][128];  // [tile parity][column quarter][row]: partial row maxima, rounded UP to bf16
+                                  // (any common upper bound stabilises the softmax; shared memory is full)
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -54,12 +56,16 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnParams P) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles; never observed, but checked
+    if (threadIdx.x == 0) atomicCAS(P.err, 0, KERR_BAD_SHAPE);
+    return;
+  }
   AttnBars *B = reinterpret_cast<AttnBars *>(smem + OFF_BAR);
+  static_assert(sizeof(AttnBars) <= 2560, "barrier block does not fit");
   volatile int *abort_flag = &B->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -76,11 +82,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       mbar_init(&B->v_full[i], 1);
       mbar_init(&B->kv_empty[i], 1);
       mbar_init(&B->s_full[i], 1);
-      mbar_init(&B->s_empty[i], 8);
-      mbar_init(&B->p_full[i], 8);
+      mbar_init(&B->s_empty[i], 16);
+      mbar_init(&B->p_full[i], 16);
       mbar_init(&B->p_empty[i], 1);
       mbar_init(&B->o_full[i], 1);
-      mbar_init(&B->o_empty[i], 8);
+      mbar_init(&B->o_empty[i], 16);
+      for (int qq = 0; qq < 4; ++qq) mbar_init(&B->mx_full[i][qq], 4);
     }
     B->abort_flag = 0;
     mbar_fence_init();
@@ -90,6 +97,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = B->tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above touched only shared memory and TMEM
 
   auto fail = [&]() {
     *abort_flag = 1;
@@ -179,110 +188,92 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     }
     __syncwarp();
   } else {
-    // ---------------------------------------------------------------- softmax + output (warps 2..9)
-    // Two threads share a query row: thread (q, hf) owns score columns and output columns [64 hf, 64 hf + 64).
+    // ---------------------------------------------------------------- softmax + output (warps 2..17)
+    // Four threads share a query row: thread (q, cq) owns score columns and output columns [32 cq, 32 cq + 32).
     const int q = warp & 3;          // TMEM lane quarter this warp may read
-    const int hf = (warp - 2) >> 2;  // column half
+    const int cq = (warp - 2) >> 2;  // column quarter
     const int row = q * 32 + lane;   // row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const int sw = row & 7;
     const float scale = P.scale_log2;
 
-    float o[64];
+    float o[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
     float m = -1e30f, l = 0.f, alpha_prev = 1.f;
-    uint32_t s0[32], s1[32];
+    uint32_t s0[32], t0[32];
     bool ok = true;
 
     auto accumulate = [&](int jj, float a) -> bool {
       const int ob = jj & 1;
-      bool w = mbar_wait(&B->o_full[ob], (jj >> 1) & 1, abort_flag);
-      w = __all_sync(0xffffffffu, w);
+      bool w = mbar_wait_warp(&B->o_full[ob], (jj >> 1) & 1, abort_flag);
       if (!w) return false;
       tc_fence_after_sync();
-      const uint32_t to = tmem + lane_base + 256 + ob * 128 + hf * 64;
-      tc_ld_32x32(to, s0);
-      tc_ld_32x32(to + 32, s1);
+      tc_ld_32x32(tmem + lane_base + 256 + ob * 128 + cq * 32, t0);
       tc_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        o[i] = fmaf(o[i], a, __uint_as_float(s0[i]));
-        o[32 + i] = fmaf(o[32 + i], a, __uint_as_float(s1[i]));
-      }
+      for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], a, __uint_as_float(t0[i]));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&B->o_empty[ob]);
       return true;
     };
 
-    for (int j = 0; j < T; ++j) {
+    int j = 0;
+    for (; j < T; ++j) {
       const int sb = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      bool w = mbar_wait(&B->s_full[sb], ph, abort_flag);
-      w = __all_sync(0xffffffffu, w);
+      bool w = mbar_wait_warp(&B->s_full[sb], ph, abort_flag);
       if (!w) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      // Row maximum over all 128 columns: the partner's half is read only for its maximum (TMEM reads are
-      // cheap and this keeps the two warps of a row free of any per-tile synchronisation).
-      const uint32_t tb = tmem + lane_base + sb * 128;
-      const int valid_all = P.seq - j * TILE;          // real keys in this tile
-      const int valid = valid_all - hf * 64;           // ... of them in my half
-      const int valid_o = valid_all - (hf ^ 1) * 64;   // ... in the partner's half
-      float mloc = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        tc_ld_32x32(tb + (hf ^ 1) * 64 + c * 32, s0);
-        tc_wait_ld();
-        if (valid_o >= 64) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, __uint_as_float(s0[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid_o) mloc = fmaxf(mloc, __uint_as_float(s0[i]));
-        }
-      }
-      tc_ld_32x32(tb + hf * 64, s0);
-      tc_ld_32x32(tb + hf * 64 + 32, s1);
+      tc_ld_32x32(tmem + lane_base + sb * 128 + cq * 32, s0);
       tc_wait_ld();
-      // the score buffer is in registers now: hand it back to the MMA warp
+      // the scores are in registers now: hand the TMEM buffer back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&B->s_empty[sb]);
-      if (valid < 64) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i >= valid) s0[i] = __float_as_uint(-1e30f);
-          if (32 + i >= valid) s1[i] = __float_as_uint(-1e30f);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
-      const float mx = fmaxf(m, mloc * scale);
-      const float alpha = ex2f(m - mx);
 
-      // the P buffer of this parity is free once P V(j-2) has completed
-      w = mbar_wait(&B->p_empty[sb], ph ^ 1, abort_flag);
-      w = __all_sync(0xffffffffu, w);
+      const int valid = P.seq - j * TILE - cq * 32;  // columns of my quarter that are real keys
+      if (valid < 32) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i >= valid) s0[i] = __float_as_uint(-1e30f);
+      }
+      float mloc = -1e30f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, __uint_as_float(s0[i]));
+      // publish my partial maximum, wait (bounded) for the three other quarters of this row
+      B->xchg[sb][cq][row] = __float2bfloat16_ru(mloc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&B->mx_full[sb][q]);
+      w = mbar_wait_warp(&B->mx_full[sb][q], ph, abort_flag);
       if (!w) {
         ok = false;
         break;
       }
-      // p = 2^(s*scale - max); bf16 P into shared memory: my 64 keys are one swizzled 128-byte row of chunk hf
+      mloc = fmaxf(fmaxf(__bfloat162float(B->xchg[sb][0][row]), __bfloat162float(B->xchg[sb][1][row])),
+                   fmaxf(__bfloat162float(B->xchg[sb][2][row]), __bfloat162float(B->xchg[sb][3][row])));
+      const float mx = fmaxf(m, mloc * scale);
+      const float alpha = ex2f(m - mx);
+
+      // the P buffer of this parity is free once P V(j-2) has completed
+      w = mbar_wait_warp(&B->p_empty[sb], ph ^ 1, abort_flag);
+      if (!w) {
+        ok = false;
+        break;
+      }
+      // p = 2^(s*scale - max); bf16 P into shared memory: my 32 keys are half of a swizzled 128-byte row
       float rowsum = 0.f;
-      uint8_t *dst = smem + OFF_P + sb * 32768 + hf * CHUNK_BYTES + row * 128;
+      uint8_t *dst = smem + OFF_P + sb * 32768 + (cq >> 1) * CHUNK_BYTES + row * 128;
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
+      for (int t = 0; t < 4; ++t) {
         float pv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int i = 8 * t + e;
-          const float sv = __uint_as_float(i < 32 ? s0[i] : s1[i - 32]);
-          pv[e] = ex2f(fmaf(sv, scale, -mx));
+          pv[e] = ex2f(fmaf(__uint_as_float(s0[8 * t + e]), scale, -mx));
           rowsum += pv[e];
         }
         uint4 v;
@@ -290,7 +281,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         v.y = pack_bf16x2(pv[2], pv[3]);
         v.z = pack_bf16x2(pv[4], pv[5]);
         v.w = pack_bf16x2(pv[6], pv[7]);
-        *reinterpret_cast<uint4 *>(dst + ((t ^ sw) << 4)) = v;
+        const int u = (cq & 1) * 4 + t;  // 16-byte unit inside the 128-byte row
+        *reinterpret_cast<uint4 *>(dst + ((u ^ sw) << 4)) = v;
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -308,26 +300,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     if (ok) ok = accumulate(T - 1, alpha_prev);
     if (!ok) {
       if (lane == 0) fail();
-    }
-    // total row sum = my half + the partner's half (both halves used the same running maximum)
-    // Every softmax warp passes here exactly once, whatever happened above, so the pair barrier cannot hang.
-    B->xchg[hf][row] = l;
-    pair_sync(1 + q);
-    l += B->xchg[hf ^ 1][row];
-    if (ok && q0 + row < P.seq) {
-      const float inv = 1.0f / l;
-      __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
-                            (static_cast<size_t>(batch) * P.seq + q0 + row) * P.out_ld + P.out_col + head * 128 +
-                            hf * 64;
-      uint4 *d4 = reinterpret_cast<uint4 *>(dstg);
+    } else {
+      // total row sum = the four quarters' partial sums (all used the same running maximum). They are exchanged
+      // in f32 through the first P buffer, which the last P V has finished reading, behind the same bounded
+      // barrier as the maxima (next phase of the parity the loop did not use last).
+      const int sb = T & 1;
+      const uint32_t ph = (T >> 1) & 1;
+      float *lsum = reinterpret_cast<float *>(smem + OFF_P);  // [4][128]
+      lsum[cq * 128 + row] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&B->mx_full[sb][q]);
+      bool w = mbar_wait_warp(&B->mx_full[sb][q], ph, abort_flag);
+      if (!w) {
+        if (lane == 0) fail();
+      } else if (q0 + row < P.seq) {
+        l = (lsum[row] + lsum[128 + row]) + (lsum[256 + row] + lsum[384 + row]);
+        const float inv = 1.0f / l;
+        __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
+                              (static_cast<size_t>(batch) * P.seq + q0 + row) * P.out_ld + P.out_col + head * 128 +
+                              cq * 32;
+        uint4 *d4 = reinterpret_cast<uint4 *>(dstg);
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        uint4 v;
-        v.x = pack_bf16x2(o[8 * t + 0] * inv, o[8 * t + 1] * inv);
-        v.y = pack_bf16x2(o[8 * t + 2] * inv, o[8 * t + 3] * inv);
-        v.z = pack_bf16x2(o[8 * t + 4] * inv, o[8 * t + 5] * inv);
-        v.w = pack_bf16x2(o[8 * t + 6] * inv, o[8 * t + 7] * inv);
-        d4[t] = v;
+        for (int t = 0; t < 4; ++t) {
+          uint4 v;
+          v.x = pack_bf16x2(o[8 * t + 0] * inv, o[8 * t + 1] * inv);
+          v.y = pack_bf16x2(o[8 * t + 2] * inv, o[8 * t + 3] * inv);
+          v.z = pack_bf16x2(o[8 * t + 4] * inv, o[8 * t + 5] * inv);
+          v.w = pack_bf16x2(o[8 * t + 6] * inv, o[8 * t + 7] * inv);
+          d4[t] = v;
+        }
       }
     }
   }
@@ -391,8 +392,7 @@ int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long lo
 
 int attn_launch(const AttnParams *p, cudaStream_t stream) {
   dim3 grid((p->seq + TILE - 1) / TILE, p->heads, p->batch);
-  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(*p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  return launch_kernel(attn_fwd_kernel, grid, dim3(ATT_THREADS), ATT_SMEM, stream, 1, *p) == cudaSuccess ? 0 : -8;
 }
 
 }  // namespace fx

@@ -11,7 +11,7 @@ struct flux_cuda_ctx {
   cudaStream_t stream = nullptr;  // owned
   int *err_dev = nullptr;         // device word, 0 = no kernel reported a failed wait
   int *err_host = nullptr;        // pinned mirror
-  bool gemm_pair = false;         // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
+  bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
 };
 
 namespace fx {

@@ -2,6 +2,7 @@
 // QK-RMSNorm + 2-axis RoPE (K5), sampler updates (K6), layout/dtype changes at the edges (K7).
 // All are bandwidth-bound: 128-bit accesses, warp-shuffle reductions, f32 statistics.
 #include "elementwise.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace fx {
@@ -19,6 +20,8 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
                                                     const float *__restrict__ scale_txt,
                                                     const float *__restrict__ shift_img,
                                                     const float *__restrict__ scale_img) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int local = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (local >= rows) return;
@@ -63,9 +66,9 @@ int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int 
   if (rows <= 0) return 0;
   const int grid = (rows + 3) / 4;
   __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
-#define FX_ADALN(V)                                                                                               \
-  adaln_kernel<V><<<grid, 128, 0, st>>>(x, o, row0, rows, hidden, seq, n_txt, shift_txt, scale_txt, shift_img, \
-                                        scale_img)
+#define FX_ADALN(V)                                                                                             \
+  launch_kernel(adaln_kernel<V>, dim3(grid), dim3(128), 0, st, 1, x, o, row0, rows, hidden, seq, n_txt, shift_txt, \
+                scale_txt, shift_img, scale_img)
   switch (hidden) {
     case 3072: FX_ADALN(24); break;
     case 256: FX_ADALN(2); break;
@@ -213,6 +216,8 @@ int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int
 // ------------------------------------------------------------------------------------------------
 __global__ void pack_tokens_kernel(const float *__restrict__ z, __nv_bfloat16 *__restrict__ tok, int C, int n) {
   __shared__ float tile[32][33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
   for (int i = ty; i < 32; i += 8) {
@@ -228,8 +233,10 @@ __global__ void pack_tokens_kernel(const float *__restrict__ z, __nv_bfloat16 *_
 
 int launch_pack_tokens(const float *z, void *tok, int C, int n, cudaStream_t st) {
   dim3 grid((n + 31) / 32, (C + 31) / 32);
-  pack_tokens_kernel<<<grid, dim3(32, 8), 0, st>>>(z, reinterpret_cast<__nv_bfloat16 *>(tok), C, n);
-  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  return launch_kernel(pack_tokens_kernel, grid, dim3(32, 8), 0, st, 1, z, reinterpret_cast<__nv_bfloat16 *>(tok), C,
+                       n) == cudaSuccess
+             ? 0
+             : -8;
 }
 
 __global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4) {
@@ -255,6 +262,8 @@ int launch_f32_to_bf16(const float *in, void *out, long long n, cudaStream_t st)
 // ------------------------------------------------------------------------------------------------
 __global__ void euler_kernel(float *__restrict__ z, const float *__restrict__ v, const float *__restrict__ sched,
                              int step, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float dt = sched[step + 1] - sched[step];
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
@@ -286,8 +295,8 @@ static int ew_grid(long long n) {
 }
 
 int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st) {
-  euler_kernel<<<ew_grid(n), 256, 0, st>>>(z, v, sched, step, n);
-  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  return launch_kernel(euler_kernel, dim3(ew_grid(n)), dim3(256), 0, st, 1, z, v, sched, step, n) == cudaSuccess ? 0
+                                                                                                                   : -8;
 }
 
 int launch_scale_copy(float *dst, const float *src, float a, long long n, cudaStream_t st) {

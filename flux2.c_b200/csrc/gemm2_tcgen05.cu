@@ -13,6 +13,7 @@
 
 #include "gemm.cuh"
 #include "gemm_epilogue.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace fx {
@@ -62,6 +63,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
   cluster_sync_all();  // the partner's barriers exist before anything can arrive on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above touched only shared memory and TMEM
 
   auto fail = [&](int code) {
     *abort_flag = 1;
@@ -154,8 +157,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
       int prob, m0, n0;
       decode(tile, prob, m0, n0);
       const int acc = it & 1;
-      bool ok = mbar_wait(&tfull[acc], (it >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
+      const bool ok = mbar_wait_warp(&tfull[acc], (it >> 1) & 1, abort_flag);
       if (!ok) {
         if (lane == 0) fail(KERR_WAIT_TMEM_FULL);
         break;
@@ -201,19 +203,9 @@ int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
   P->total_tiles = acc;
   int pairs = num_sms / 2;
   if (acc < pairs) pairs = acc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(P_THREADS);
-  cfg.dynamicSmemBytes = P_SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm2_bf16_tn_kernel, *P) == cudaSuccess ? 0 : -8;
+  return launch_kernel(gemm2_bf16_tn_kernel, dim3(2 * pairs), dim3(P_THREADS), P_SMEM, stream, 2, *P) == cudaSuccess
+             ? 0
+             : -8;
 }
 
 int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K) {

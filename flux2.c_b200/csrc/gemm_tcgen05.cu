@@ -18,6 +18,7 @@
 // NLC -> NCHW transpose (flux_transformer.c:3547-3552).
 #include "gemm.cuh"
 #include "gemm_epilogue.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cudaTypedefs.h>
@@ -74,6 +75,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above touched only shared memory and TMEM
 
   auto fail = [&](int code) {
     *abort_flag = 1;
@@ -165,8 +168,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
       int prob, m0, n0;
       decode(tile, prob, m0, n0);
       const int acc = it & 1;
-      bool ok = mbar_wait(&tfull[acc], (it >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
+      const bool ok = mbar_wait_warp(&tfull[acc], (it >> 1) & 1, abort_flag);
       if (!ok) {
         if (lane == 0) fail(KERR_WAIT_TMEM_FULL);
         break;
@@ -257,11 +259,12 @@ int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream) {
       if (pb.seg[s].mode == EPI_SWIGLU_BF16 && bn != 256) return -7;
   }
   const int grid = P->total_tiles < num_sms ? P->total_tiles : num_sms;
-  if (bn == 256)
-    gemm_bf16_tn_kernel<256><<<grid, GEMM_THREADS, GemmCfg<256>::SMEM_BYTES, stream>>>(*P);
-  else
-    gemm_bf16_tn_kernel<128><<<grid, GEMM_THREADS, GemmCfg<128>::SMEM_BYTES, stream>>>(*P);
-  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  cudaError_t e =
+      bn == 256 ? launch_kernel(gemm_bf16_tn_kernel<256>, dim3(grid), dim3(GEMM_THREADS), GemmCfg<256>::SMEM_BYTES,
+                                stream, 1, *P)
+                : launch_kernel(gemm_bf16_tn_kernel<128>, dim3(grid), dim3(GEMM_THREADS), GemmCfg<128>::SMEM_BYTES,
+                                stream, 1, *P);
+  return e == cudaSuccess ? 0 : -8;
 }
 
 }  // namespace fx

@@ -83,6 +83,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
 }
 
+// Whole-warp bounded wait with a warp-uniform result: lane 0 polls the barrier, the other lanes wait at a warp
+// barrier instead of hammering the shared-memory pipe with 32 polls per warp. __syncwarp orders the other
+// lanes' later accesses after lane 0's acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// pdl_launch_dependents: the next kernel in the stream may start being scheduled. pdl_wait: blocks until the
+// previous kernel has completed and its memory is visible; nothing produced or still read by the previous kernel
+// may be touched before it. Both are no-ops when the launch did not ask for programmatic serialization.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -162,6 +162,8 @@ int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kerne
 #define FLUX_CUDA_KERNEL_CLASSES 5
 int flux_cuda_sampler_set_profiling(flux_cuda_sampler *s, int on);
 int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
+/* The same per launch, in launch order: ms[i] and kernel_class[i] for up to `capacity` launches. */
+int flux_cuda_sampler_profile_launches(flux_cuda_sampler *s, float *ms, int *kernel_class, int capacity, int *count);
 
 /* ------------------------------------------------------------------------------------------------
  * Host-side pieces of the sampler (plain C, no GPU involved).

@@ -1,0 +1,76 @@
+"""Further fixtures from the REFERENCE implementation (see make_golden.py): the two heavier BASELINE shapes.
+
+  guided_256 : 256x256, 512 text tokens, 10 Euler steps with classifier-free guidance 4.0 (the base-model
+               configuration at a step count the CPU reference finishes in minutes), "sharp" weights: combined
+               velocities along the reference's own trajectory and the final latent.
+  img2img_1024 : one forward of the 1024x1024 img2img shape (4096 target + 4096 reference tokens + 512 text
+               tokens = 8704), benchmark weights; the velocity is stored subsampled (every 2nd latent row / column).
+
+    python tests/golden/make_golden_extra.py
+"""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+from conftest import load_package  # noqa: E402
+
+load_package()
+import flux2_c_b200.synth as synth  # noqa: E402
+from oracle import ref_binding as rb  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+D = synth.Dims.klein4b()
+
+
+def model(kind, lib):
+    path = "/tmp/synth_%s.safetensors" % kind
+    if not os.path.exists(path):
+        synth.write_safetensors(path, synth.make_transformer_weights(D, seed=0, sharp=kind == "sharp"))
+    return lib.load_transformer(path)
+
+
+def main():
+    lib = rb.RefLib(rb.best_kind())
+    out = {"ref_build": lib.kind}
+    t0 = time.time()
+
+    tf = model("sharp", lib)
+    h = w = 16
+    steps, g = 10, 4.0
+    z = lib.init_noise(128, h, w, 42)
+    cc = synth.make_context(1234, 512, D.text_dim)
+    cu = synth.make_context(4321, 512, D.text_dim)
+    sch = lib.official_schedule(steps, h * w)
+    vs = []
+    for i in range(steps):
+        vu = tf.forward(z, h, w, cu, float(sch[i]))
+        vc = tf.forward(z, h, w, cc, float(sch[i]))
+        v = vu + np.float32(g) * (vc - vu)  # flux_sample.c:495-499
+        vs.append(v)
+        z = z + np.float32(sch[i + 1] - sch[i]) * v
+        print("guided step", i, time.time() - t0, flush=True)
+    out["guided_256_sched"] = sch
+    out["guided_256_v"] = np.stack(vs)
+    out["guided_256_final"] = z
+    tf.close()
+
+    tf = model("base", lib)
+    h = w = 64
+    z = lib.init_noise(128, h, w, 42)
+    ref = synth.make_latent(7, 128, 64, 64)
+    c = synth.make_context(1234, 512, D.text_dim)
+    v = tf.forward(z, h, w, c, 1.0, refs=[(ref, 10)])
+    out["img2img_1024_v_sub"] = v[:, ::2, ::2].copy()
+    out["img2img_1024_v_rms"] = np.float64(np.sqrt((v.astype(np.float64) ** 2).mean()))
+    print("img2img forward", time.time() - t0, flush=True)
+    tf.close()
+    np.savez_compressed(os.path.join(HERE, "reference_extra.npz"), **out)
+
+
+if __name__ == "__main__":
+    main()

@@ -258,3 +258,50 @@ def test_klein_decoded_image_psnr(klein, synth, fx, tmp_path):
     assert b.std() > 10  # a real picture, not a flat field
     psnr = 10 * np.log10(255.0 ** 2 / max(((a - b) ** 2).mean(), 1e-12))
     assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+
+
+def _extra():
+    path = os.path.join(GOLDEN, "reference_extra.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_extra.npz missing")
+    return np.load(path)
+
+
+def test_klein_guided_loop_matches_reference(klein, synth, fx):
+    """Base-model configuration: guidance 4.0, conditional + unconditional pass per step (run as a batch of two),
+    256x256, 10 steps, on the weights that make attention sharp. Guidance multiplies per-pass errors by up to
+    g + |1 - g| = 7, so this is the tightest case for the per-step tolerance."""
+    kind, d, model, gold = klein
+    if kind != "sharp":
+        pytest.skip("stored for the sharp weights")
+    ex = _extra()
+    h = w = 16
+    g = 4.0
+    sch = ex["guided_256_sched"]
+    cc = synth.make_context(1234, 512, d.text_dim)
+    cu = synth.make_context(4321, 512, d.text_dim)
+    z0 = fx.init_noise(128, h, w, 42)
+    z = z0.copy()
+    worst = 0.0
+    for i in range(len(sch) - 1):  # the reference's own trajectory
+        vu = model.forward(z, h, w, cu, float(sch[i]))
+        vc = model.forward(z, h, w, cc, float(sch[i]))
+        worst = max(worst, rel(vu + np.float32(g) * (vc - vu), ex["guided_256_v"][i]))
+        z = z + np.float32(sch[i + 1] - sch[i]) * ex["guided_256_v"][i]
+    assert worst < VEL_TOL, worst
+    got = model.sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=g)
+    assert rel(got, ex["guided_256_final"]) < LATENT_TOL
+
+
+def test_klein_img2img_1024_forward_matches_reference(klein, synth, fx):
+    """1024x1024 img2img shape: 4096 target + 4096 reference tokens (T offset 10) + 512 text tokens = 8704."""
+    kind, d, model, gold = klein
+    if kind != "base":
+        pytest.skip("stored for the benchmark weights")
+    ex = _extra()
+    z = fx.init_noise(128, 64, 64, 42)
+    ref = synth.make_latent(7, 128, 64, 64)
+    c = synth.make_context(1234, 512, d.text_dim)
+    v = model.forward(z, 64, 64, c, 1.0, [(ref, 10)])
+    assert rel(v[:, ::2, ::2], ex["img2img_1024_v_sub"]) < VEL_TOL
+    assert abs(np.sqrt((v.astype(np.float64) ** 2).mean()) / float(ex["img2img_1024_v_rms"]) - 1.0) < 1e-2
