@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflux_cuda.so")
 
 EPI_STORE_BF16, EPI_STORE_F32, EPI_GATED_RES_F32, EPI_SWIGLU_BF16, EPI_STORE_F32_T = range(5)
+EPI_X_F16, EPI_OUT_F16 = 0x100, 0x200  # or-ed into the epilogue: f16 activations in / out
 
 _lib = None
 
@@ -45,6 +46,8 @@ def _declare(L):
     L.flux_cuda_ctx_sync.argtypes = [c_void_p]
     L.flux_cuda_ctx_stream.restype = c_void_p
     L.flux_cuda_ctx_stream.argtypes = [c_void_p]
+    L.flux_cuda_ctx_set_half_format.restype = c_int
+    L.flux_cuda_ctx_set_half_format.argtypes = [c_void_p, c_int]
     L.flux_cuda_ctx_set_gemm_pair.restype = c_int
     L.flux_cuda_ctx_set_gemm_pair.argtypes = [c_void_p, c_int]
     L.flux_cuda_gemm_bf16.restype = c_int
@@ -55,12 +58,12 @@ def _declare(L):
     fp = ctypes.POINTER(ctypes.c_float)
     L.flux_cuda_gemm_qkv_norm_rope.restype = c_int
     L.flux_cuda_gemm_qkv_norm_rope.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                                               c_void_p, c_void_p, c_void_p, c_int]
+                                               c_void_p, c_void_p, c_void_p, c_int, c_int]
     L.flux_cuda_attention.restype = c_int
     L.flux_cuda_attention.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_int, c_int, c_int, c_int, c_void_p,
-                                      c_ll, c_int]
+                                      c_ll, c_int, c_int]
     L.flux_cuda_adaln.restype = c_int
-    L.flux_cuda_adaln.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    L.flux_cuda_adaln.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int]
     L.flux_cuda_qk_norm_rope.restype = c_int
     L.flux_cuda_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p, c_void_p, c_void_p]
@@ -158,6 +161,10 @@ class Context:
     def sync(self):
         check(lib().flux_cuda_ctx_sync(self.handle))
 
+    def set_half_format(self, name):
+        """'f16' (default) or 'bf16': storage format of models created afterwards."""
+        check(lib().flux_cuda_ctx_set_half_format(self.handle, {"f16": 1, "bf16": 2}[name]))
+
     def set_gemm_pair(self, on):
         check(lib().flux_cuda_ctx_set_gemm_pair(self.handle, int(on)))
 
@@ -180,20 +187,21 @@ class Context:
     def gemm_bf16(self, x_ptr, w_ptr, out_ptr, M, N, K, epilogue=EPI_STORE_BF16, ld_out=None, gate_ptr=None,
                   tile_n=0):
         if ld_out is None:
-            ld_out = N // 2 if epilogue == EPI_SWIGLU_BF16 else N
+            ld_out = N // 2 if (epilogue & 0xFF) == EPI_SWIGLU_BF16 else N
         check(lib().flux_cuda_gemm_bf16(self.handle, x_ptr, w_ptr, out_ptr, M, N, K, epilogue, ld_out, gate_ptr,
                                         tile_n))
 
-    def gemm_qkv_norm_rope(self, x_ptr, w_ptr, out_ptr, M, hidden, K, wq_ptr, wk_ptr, cos_ptr, sin_ptr, seq):
+    def gemm_qkv_norm_rope(self, x_ptr, w_ptr, out_ptr, M, hidden, K, wq_ptr, wk_ptr, cos_ptr, sin_ptr, seq,
+                           f16=False):
         check(lib().flux_cuda_gemm_qkv_norm_rope(self.handle, x_ptr, w_ptr, out_ptr, M, hidden, K, wq_ptr, wk_ptr,
-                                                 cos_ptr, sin_ptr, seq))
+                                                 cos_ptr, sin_ptr, seq, int(f16)))
 
-    def attention(self, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr, out_ld, out_col=0):
+    def attention(self, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr, out_ld, out_col=0, f16=False):
         check(lib().flux_cuda_attention(self.handle, qkv_ptr, batch, seq, ld, q_col, k_col, v_col, heads, out_ptr,
-                                        out_ld, out_col))
+                                        out_ld, out_col, int(f16)))
 
-    def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr):
-        check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr))
+    def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, f16=False):
+        check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, int(f16)))
 
     def qk_norm_rope(self, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr, cos_ptr, sin_ptr):
         check(lib().flux_cuda_qk_norm_rope(self.handle, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr,

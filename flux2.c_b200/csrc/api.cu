@@ -83,7 +83,9 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
     return rc;
   }
   if (const char *e = getenv("FLUX_CUDA_GEMM_PAIR")) c->gemm_pair = atoi(e) != 0;
-  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || elementwise_init() != 0) {
+  if (const char *e = getenv("FLUX_CUDA_BF16")) c->f16 = atoi(e) == 0;
+  if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 1 ? 1 : 2;
+  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || attn2_init() != 0 || elementwise_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
     flux_cuda_ctx_destroy(c);
     return FLUX_CUDA_ERR_CUDA;
@@ -111,6 +113,12 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx) {
 
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
+int flux_cuda_ctx_set_half_format(flux_cuda_ctx *ctx, int dtype) {
+  if (!ctx || (dtype != FLUX_CUDA_F16 && dtype != FLUX_CUDA_BF16)) return FLUX_CUDA_ERR_ARG;
+  ctx->f16 = dtype == FLUX_CUDA_F16;
+  return FLUX_CUDA_OK;
+}
+
 int flux_cuda_ctx_set_gemm_pair(flux_cuda_ctx *ctx, int on) {
   if (!ctx) return FLUX_CUDA_ERR_ARG;
   ctx->gemm_pair = on != 0;
@@ -123,6 +131,8 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
     set_error("gemm: null argument");
     return FLUX_CUDA_ERR_ARG;
   }
+  const int x_f16 = (epilogue & FLUX_CUDA_EPI_X_F16) != 0, out_f16 = (epilogue & FLUX_CUDA_EPI_OUT_F16) != 0;
+  epilogue &= 0xFF;
   if (epilogue < 0 || epilogue > 4 || (epilogue == EPI_GATED_RES_F32 && !gate)) {
     set_error("gemm: bad epilogue %d", epilogue);
     return FLUX_CUDA_ERR_ARG;
@@ -139,6 +149,8 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
   }
   P.nprob = 1;
   P.err = ctx->err_dev;
+  P.p[0].x_f16 = x_f16;
+  P.p[0].seg[0].out_f16 = out_f16;
   P.p[0].seg[0].mode = epilogue;
   P.p[0].seg[0].col0 = 0;
   P.p[0].seg[0].ld = ld_out;
@@ -154,7 +166,8 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
 
 
 int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int hidden, int K,
-                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq) {
+                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq,
+                                 int f16) {
   if (!ctx || !x || !w || !out || !wq || !wk || !cos_t || !sin_t || seq <= 0 || hidden % 128) {
     set_error("gemm_qkv_norm_rope: bad argument");
     return FLUX_CUDA_ERR_ARG;
@@ -168,7 +181,9 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   }
   P.nprob = 1;
   P.err = ctx->err_dev;
+  P.p[0].x_f16 = f16 != 0;
   EpiSeg &sg = P.p[0].seg[0];
+  sg.out_f16 = f16 != 0;
   sg.mode = EPI_QKV_NORM_ROPE;
   sg.ld = 3 * hidden;
   sg.out = out;
@@ -187,15 +202,17 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
 }
 
 int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
-                        int v_col, int heads, void *out, long long out_ld, int out_col) {
+                        int v_col, int heads, void *out, long long out_ld, int out_col, int f16) {
   if (!ctx || !qkv || !out) return FLUX_CUDA_ERR_ARG;
   AttnParams A;
-  int rc = attn_make_params(&A, qkv, batch, seq, ld, q_col, k_col, v_col, out, out_ld, out_col, heads, ctx->err_dev);
+  const bool v2 = ctx->attn_version == 2;
+  int rc = (v2 ? attn2_make_params : attn_make_params)(&A, qkv, batch, seq, ld, q_col, k_col, v_col, out, out_ld,
+                                                        out_col, heads, f16, ctx->err_dev);
   if (rc) {
     set_error("attention: unsupported shape/alignment (rc %d)", rc);
     return FLUX_CUDA_ERR_ARG;
   }
-  rc = attn_launch(&A, ctx->stream);
+  rc = v2 ? attn2_launch(&A, ctx->stream) : attn_launch(&A, ctx->stream);
   if (rc) {
     set_error("attention: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return FLUX_CUDA_ERR_CUDA;
@@ -204,9 +221,9 @@ int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq,
 }
 
 int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
-                    const float *scale) {
+                    const float *scale, int f16) {
   if (!ctx || !x || !out || !shift || !scale) return FLUX_CUDA_ERR_ARG;
-  int rc = launch_adaln(x, out, 0, rows, hidden, rows > 0 ? rows : 1, 0, shift, scale, shift, scale, ctx->stream);
+  int rc = launch_adaln(x, out, 0, rows, hidden, rows > 0 ? rows : 1, 0, f16, shift, scale, shift, scale, ctx->stream);
   if (rc) {
     set_error("adaln: unsupported hidden size %d or launch failure", hidden);
     return rc == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;

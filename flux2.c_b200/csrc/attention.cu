@@ -132,8 +132,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
-      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
+      const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
+      const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
+      const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (K-major) x V (MN-major)
       const uint32_t sq = smem_u32(smem + OFF_Q);
       auto issue_s = [&](int j) {
         const uint32_t sk = smem_u32(smem + OFF_KV + (j & 1) * 65536);
@@ -196,6 +197,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const int sw = row & 7;
     const float scale = P.scale_log2;
+    const bool f16 = P.f16 != 0;
 
     float o[32];
 #pragma unroll
@@ -277,10 +279,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           rowsum += pv[e];
         }
         uint4 v;
-        v.x = pack_bf16x2(pv[0], pv[1]);
-        v.y = pack_bf16x2(pv[2], pv[3]);
-        v.z = pack_bf16x2(pv[4], pv[5]);
-        v.w = pack_bf16x2(pv[6], pv[7]);
+        v.x = pack_16x2(pv[0], pv[1], f16);
+        v.y = pack_16x2(pv[2], pv[3], f16);
+        v.z = pack_16x2(pv[4], pv[5], f16);
+        v.w = pack_16x2(pv[6], pv[7], f16);
         const int u = (cq & 1) * 4 + t;  // 16-byte unit inside the 128-byte row
         *reinterpret_cast<uint4 *>(dst + ((u ^ sw) << 4)) = v;
       }
@@ -323,10 +325,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           uint4 v;
-          v.x = pack_bf16x2(o[8 * t + 0] * inv, o[8 * t + 1] * inv);
-          v.y = pack_bf16x2(o[8 * t + 2] * inv, o[8 * t + 3] * inv);
-          v.z = pack_bf16x2(o[8 * t + 4] * inv, o[8 * t + 5] * inv);
-          v.w = pack_bf16x2(o[8 * t + 6] * inv, o[8 * t + 7] * inv);
+          v.x = pack_16x2(o[8 * t + 0] * inv, o[8 * t + 1] * inv, f16);
+          v.y = pack_16x2(o[8 * t + 2] * inv, o[8 * t + 3] * inv, f16);
+          v.z = pack_16x2(o[8 * t + 4] * inv, o[8 * t + 5] * inv, f16);
+          v.w = pack_16x2(o[8 * t + 6] * inv, o[8 * t + 7] * inv, f16);
           d4[t] = v;
         }
       }
@@ -362,7 +364,7 @@ int attn_init() {
 }
 
 int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col, int v_col,
-                     void *out, long long out_ld, int out_col, int heads, int *err) {
+                     void *out, long long out_ld, int out_col, int heads, int f16, int *err) {
   if (!g_encode3 && attn_init() != 0) return -1;
   if (seq <= 0 || batch <= 0 || heads <= 0 || (ld % 8) || (q_col % 64) || (k_col % 64) || (v_col % 64) ||
       (out_ld % 8) || (out_col % 8) || (reinterpret_cast<uintptr_t>(qkv) & 15) ||
@@ -386,6 +388,7 @@ int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long lo
   p->out_ld = out_ld;
   p->out_col = out_col;
   p->scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
+  p->f16 = f16 != 0;
   p->err = err;
   return 0;
 }

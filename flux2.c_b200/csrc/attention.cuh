@@ -13,12 +13,19 @@ struct alignas(64) AttnParams {
   long long out_ld;
   int out_col;
   float scale_log2;        // log2(e) / sqrt(head_dim)
+  int f16;                 // Q, K, V, P and the output are f16 instead of bf16
   int *err;
 };
 
 int attn_init();
 int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col, int v_col,
-                     void *out, long long out_ld, int out_col, int heads, int *err);
+                     void *out, long long out_ld, int out_col, int heads, int f16, int *err);
 int attn_launch(const AttnParams *p, cudaStream_t stream);
+
+// Second-generation kernel (attention2.cu): two query tiles per CTA, P and the output accumulator in TMEM.
+int attn2_init();
+int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col, int v_col,
+                      void *out, long long out_ld, int out_col, int heads, int f16, int *err);
+int attn2_launch(const AttnParams *p, cudaStream_t stream);
 
 }  // namespace fx

@@ -1,0 +1,383 @@
+// K2: joint text+image attention, flash style, on tcgen05.
+//
+//   O[q, head] = softmax(Q[q, head] . K[:, head]^T / sqrt(128)) . V[:, head]      no mask, all N keys
+//
+// replaces the reference's mha_forward / joint_attention (flux_transformer.c:1249-1330, 1335-1460;
+// flash variant flux_kernels.c:700-969). Text and image tokens live in ONE [txt ; img ; refs] sequence
+// in this engine, so the double-stream blocks' joint attention (both streams' queries against the
+// concatenated keys) and the single-stream blocks' attention are the same launch.
+//
+// One CTA = TWO tiles of 128 queries of one head (of one batch element) that share every K/V tile and
+// alternate on the tensor pipe, so that while the softmax warps of one tile exponentiate, the pipe
+// works for the other. Q, K, V are read by TMA straight out of the fused projection output
+// [B, N, ld] (16-bit, 128-byte swizzle, 64-column boxes). TMEM (512 columns): scores S_a, S_b (f32,
+// 128 columns each; the 16-bit probabilities P overwrite the first 64 columns of their S) and the two
+// output accumulators O_a, O_b (f32, 128 columns each). Roles:
+//   warp 0      TMA producer: both Q tiles once, then a two-stage ring of K/V tiles (128 keys each);
+//   warp 1      MMA issuer: S_t = Q_t K^T (both operands K-major in shared memory) and
+//               O_t += P_t V (A = P_t from TMEM, B = V as an MN-major shared-memory operand);
+//   warps 2-5   softmax of tile a, warps 6-9 of tile b: one thread per query row (its TMEM lane).
+//               Online softmax in base 2 with f32 statistics. The running maximum is only raised when a
+//               tile exceeds it by more than 8 (p stays below 2^8), so the accumulator in TMEM rarely has
+//               to be rescaled; when it does, the row's thread multiplies its O row in place
+//               (tcgen05.ld / tcgen05.st) before it releases P for the next P V.
+#include "attention.cuh"
+#include "gemm.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace fx {
+
+static constexpr int ATT_THREADS = 320;
+static constexpr int TILE = 128;           // queries per tile, keys per step, head dim
+static constexpr int QTILES = 2;           // query tiles per CTA
+static constexpr int CHUNK_BYTES = 16384;  // 128 rows x 64 16-bit elements
+static constexpr int OFF_Q = 0;            // tile t at t * 32768
+static constexpr int OFF_KV = QTILES * 32768;  // stage s: K at OFF_KV + s*65536, V 32768 after it
+static constexpr int OFF_BAR = OFF_KV + 2 * 65536;
+static constexpr int ATT_SMEM = OFF_BAR + 256 + 1024;
+static constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct Attn2Bars {
+  uint64_t q_full;
+  uint64_t k_full[2], v_full[2], kv_empty[2];
+  uint64_t s_ready[QTILES], p_ready[QTILES], o_done[QTILES];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2f_(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 lanes x 32 consecutive 32-bit columns, registers -> TMEM.
+__device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]: A is a 128-lane x K tile of 16-bit values, two per 32-bit column.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_constant__ AttnParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Attn2Bars *B = reinterpret_cast<Attn2Bars *>(smem + OFF_BAR);
+  volatile int *abort_flag = &B->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * (QTILES * TILE);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int T = (P.seq + TILE - 1) / TILE;  // key tiles
+
+  if (threadIdx.x == 0) {
+    mbar_init(&B->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&B->k_full[i], 1);
+      mbar_init(&B->v_full[i], 1);
+      mbar_init(&B->kv_empty[i], 1);
+      mbar_init(&B->s_ready[i], 1);
+      mbar_init(&B->p_ready[i], 4);
+      mbar_init(&B->o_done[i], 1);
+    }
+    B->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&B->tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = B->tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above touched only shared memory and TMEM
+
+  auto fail = [&]() {
+    *abort_flag = 1;
+    atomicCAS(P.err, 0, KERR_WAIT_ATTN);
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&P.tm);
+      mbar_arrive_expect_tx(&B->q_full, QTILES * 2 * CHUNK_BYTES);
+      for (int t = 0; t < QTILES; ++t) {
+        uint8_t *sq = smem + OFF_Q + t * 32768;
+        tma_load_3d(sq, &P.tm, &B->q_full, P.q_col + head * 128, q0 + t * TILE, batch);
+        tma_load_3d(sq + CHUNK_BYTES, &P.tm, &B->q_full, P.q_col + head * 128 + 64, q0 + t * TILE, batch);
+      }
+      for (int j = 0; j < T; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&B->kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) {
+          fail();
+          break;
+        }
+        uint8_t *sk = smem + OFF_KV + s * 65536;
+        uint8_t *sv = sk + 32768;
+        mbar_arrive_expect_tx(&B->k_full[s], 2 * CHUNK_BYTES);
+        tma_load_3d(sk, &P.tm, &B->k_full[s], P.k_col + head * 128, j * TILE, batch);
+        tma_load_3d(sk + CHUNK_BYTES, &P.tm, &B->k_full[s], P.k_col + head * 128 + 64, j * TILE, batch);
+        mbar_arrive_expect_tx(&B->v_full[s], 2 * CHUNK_BYTES);
+        tma_load_3d(sv, &P.tm, &B->v_full[s], P.v_col + head * 128, j * TILE, batch);
+        tma_load_3d(sv + CHUNK_BYTES, &P.tm, &B->v_full[s], P.v_col + head * 128 + 64, j * TILE, batch);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
+      const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
+      const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (TMEM)   x V (MN-major)
+      auto issue_s = [&](int t, int j) {
+        const uint32_t sq = smem_u32(smem + OFF_Q + t * 32768);
+        const uint32_t sk = smem_u32(smem + OFF_KV + (j & 1) * 65536);
+        const uint32_t d = tmem + t * 128;
+#pragma unroll
+        for (int kc = 0; kc < 2; ++kc) {
+          const uint64_t ad = make_smem_desc_sw128(sq + kc * CHUNK_BYTES, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(sk + kc * CHUNK_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc_s, (kc | k) ? 1u : 0u);
+        }
+        tc_commit(&B->s_ready[t]);
+      };
+      bool ok = mbar_wait(&B->q_full, 0, abort_flag) && mbar_wait(&B->k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0, 0);
+        issue_s(1, 0);
+      }
+      for (int j = 0; ok && j < T; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&B->v_full[st], (j >> 1) & 1, abort_flag);
+        const uint32_t sv = smem_u32(smem + OFF_KV + st * 65536 + 32768);
+        for (int t = 0; ok && t < QTILES; ++t) {
+          ok = mbar_wait(&B->p_ready[t], j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          // O_t (+)= P_t V: P_t sits in the first 64 columns of S_t, 16 keys = 8 columns per MMA
+          const uint32_t d = tmem + 256 + t * 128;
+          const uint32_t pa = tmem + t * 128;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // V tile: rows = keys (128 B each, one 64-wide half of d per chunk); 16 keys per MMA.
+            const uint64_t bd = make_smem_desc_sw128(sv + k * 16 * 128, CHUNK_BYTES, 1024);
+            tc_mma_ts(d, pa + k * 8, bd, idesc_o, (j | k) ? 1u : 0u);
+          }
+          tc_commit(&B->o_done[t]);
+          if (t == QTILES - 1) tc_commit(&B->kv_empty[st]);
+          if (j + 1 < T) {
+            if (t == 0) {
+              ok = mbar_wait(&B->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
+          }
+        }
+      }
+      if (!ok) fail();
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax + output (warps 2..9)
+    const int t = (warp - 2) >> 2;  // query tile
+    const int q = warp & 3;         // TMEM lane quarter this warp may access
+    const int row = q * 32 + lane;  // row inside the tile = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + t * 128;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * 128;
+    const float scale = P.scale_log2;
+    const bool f16 = P.f16 != 0;
+
+    float m_ref = -1e30f, l = 0.f;
+    uint32_t s[4][32];
+    bool ok = true;
+
+    for (int j = 0; j < T; ++j) {
+      ok = mbar_wait_warp(&B->s_ready[t], j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld_32x32(s_addr + c * 32, s[c]);
+      tc_wait_ld();
+      const int valid = P.seq - j * TILE;
+      if (valid < TILE) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-1e30f);
+      }
+      float mloc = -1e30f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, __uint_as_float(s[c][i]));
+      mloc *= scale;
+      // Raise the reference maximum only when this tile exceeds it by more than the threshold.
+      const bool raise = mloc > m_ref + RESCALE_THRESHOLD;
+      if (j == 0) {
+        m_ref = mloc;
+      } else if (__any_sync(0xffffffffu, raise)) {
+        // rescale the accumulator row in TMEM once P V(j-1) has completed
+        ok = mbar_wait_warp(&B->o_done[t], (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const float alpha = raise ? ex2f_(m_ref - mloc) : 1.0f;
+        uint32_t o[32];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tc_ld_32x32(o_addr + c * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc_st_32x32(o_addr + c * 32, o);
+        }
+        tc_wait_st();
+        if (raise) {
+          l *= alpha;
+          m_ref = mloc;
+        }
+      }
+      // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
+      float rowsum = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i]), scale, -m_ref));
+            const float p1 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i + 1]), scale, -m_ref));
+            rowsum += p0 + p1;
+            pk[c * 16 + i] = pack_16x2(p0, p1, f16);
+          }
+        tc_st_32x32(s_addr + h * 32, pk);
+      }
+      l += rowsum;
+      tc_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&B->p_ready[t]);
+    }
+    if (ok) ok = mbar_wait_warp(&B->o_done[t], (T - 1) & 1, abort_flag);
+    if (!ok) {
+      if (lane == 0) fail();
+    } else {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l;
+      const int grow = q0 + t * TILE + row;
+      __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
+                            (static_cast<size_t>(batch) * P.seq + grow) * P.out_ld + P.out_col + head * 128;
+      uint32_t o[32];
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tc_ld_32x32(o_addr + c * 32, o);
+        tc_wait_ld();
+        if (grow < P.seq) {
+          uint4 *d4 = reinterpret_cast<uint4 *>(dstg + c * 32);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 v;
+            v.x = pack_16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv, f16);
+            v.y = pack_16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv, f16);
+            v.z = pack_16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv, f16);
+            v.w = pack_16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv, f16);
+            d4[u] = v;
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode4 = nullptr;
+
+int attn2_init() {
+  if (!g_encode4) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return -1;
+    g_encode4 = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  return cudaFuncSetAttribute(attn2_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) == cudaSuccess
+             ? 0
+             : -2;
+}
+
+int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col, int v_col,
+                     void *out, long long out_ld, int out_col, int heads, int f16, int *err) {
+  if (!g_encode4 && attn2_init() != 0) return -1;
+  if (seq <= 0 || batch <= 0 || heads <= 0 || (ld % 8) || (q_col % 64) || (k_col % 64) || (v_col % 64) ||
+      (out_ld % 8) || (out_col % 8) || (reinterpret_cast<uintptr_t>(qkv) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return -3;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(ld) * 2 * seq};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode4(&p->tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(qkv), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -4;
+  p->seq = seq;
+  p->batch = batch;
+  p->heads = heads;
+  p->q_col = q_col;
+  p->k_col = k_col;
+  p->v_col = v_col;
+  p->out = out;
+  p->out_ld = out_ld;
+  p->out_col = out_col;
+  p->scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
+  p->f16 = f16 != 0;
+  p->err = err;
+  return 0;
+}
+
+int attn2_launch(const AttnParams *p, cudaStream_t stream) {
+  dim3 grid((p->seq + QTILES * TILE - 1) / (QTILES * TILE), p->heads, p->batch);
+  return launch_kernel(attn2_fwd_kernel, grid, dim3(ATT_THREADS), ATT_SMEM, stream, 1, *p) == cudaSuccess ? 0 : -8;
+}
+
+}  // namespace fx

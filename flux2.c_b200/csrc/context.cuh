@@ -11,6 +11,8 @@ struct flux_cuda_ctx {
   cudaStream_t stream = nullptr;  // owned
   int *err_dev = nullptr;         // device word, 0 = no kernel reported a failed wait
   int *err_host = nullptr;        // pinned mirror
+  bool f16 = true;                // 16-bit tensors (weights and activations) are f16; false: bf16
+  int attn_version = 2;           // 1: attention.cu, 2: attention2.cu
   bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
 };
 

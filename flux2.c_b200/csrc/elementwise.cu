@@ -5,6 +5,8 @@
 #include "launch.cuh"
 #include "ptx.cuh"
 
+#include <cuda_fp16.h>
+
 namespace fx {
 
 // ------------------------------------------------------------------------------------------------
@@ -15,7 +17,7 @@ namespace fx {
 // ------------------------------------------------------------------------------------------------
 template <int VPL>
 __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out,
-                                                    int row0, int rows, int hidden, int seq, int n_txt,
+                                                    int row0, int rows, int hidden, int seq, int n_txt, int f16,
                                                     const float *__restrict__ shift_txt,
                                                     const float *__restrict__ scale_txt,
                                                     const float *__restrict__ shift_img,
@@ -56,19 +58,19 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
     const float b = fmaf((v[i].y - mean) * rstd, 1.f + sc.y, sh.y);
     const float c = fmaf((v[i].z - mean) * rstd, 1.f + sc.z, sh.z);
     const float d = fmaf((v[i].w - mean) * rstd, 1.f + sc.w, sh.w);
-    o2[i * 32 + lane] = make_uint2(pack_bf16x2(a, b), pack_bf16x2(c, d));
+    o2[i * 32 + lane] = make_uint2(pack_16x2(a, b, f16 != 0), pack_16x2(c, d, f16 != 0));
   }
 }
 
-int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int seq, int n_txt,
+int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int seq, int n_txt, int f16,
                  const float *shift_txt, const float *scale_txt, const float *shift_img, const float *scale_img,
                  cudaStream_t st) {
   if (rows <= 0) return 0;
   const int grid = (rows + 3) / 4;
   __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
 #define FX_ADALN(V)                                                                                             \
-  launch_kernel(adaln_kernel<V>, dim3(grid), dim3(128), 0, st, 1, x, o, row0, rows, hidden, seq, n_txt, shift_txt, \
-                scale_txt, shift_img, scale_img)
+  launch_kernel(adaln_kernel<V>, dim3(grid), dim3(128), 0, st, 1, x, o, row0, rows, hidden, seq, n_txt, f16, \
+                shift_txt, scale_txt, shift_img, scale_img)
   switch (hidden) {
     case 3072: FX_ADALN(24); break;
     case 256: FX_ADALN(2); break;
@@ -158,7 +160,7 @@ __global__ void timestep_sincos_kernel(const float *__restrict__ t, int S, int d
 template <int S>
 __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__restrict__ W,
                                                          const float *__restrict__ x, float *__restrict__ y, int R,
-                                                         int K, int silu_out) {
+                                                         int K, int silu_out, int f16) {
   extern __shared__ float xs[];  // [S, K]
   for (int i = threadIdx.x; i < S * K / 4; i += blockDim.x)
     reinterpret_cast<float4 *>(xs)[i] = reinterpret_cast<const float4 *>(x)[i];
@@ -172,8 +174,17 @@ __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__
   for (int s = 0; s < S; ++s) acc[s] = 0.f;
   for (int i = lane; i < K / 8; i += 32) {
     const uint4 w = __ldg(wr + i);
-    const float wf[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
-                         bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
+    float wf[8];
+    if (f16) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&w.y));
+      const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&w.z));
+      const float2 d = __half22float2(*reinterpret_cast<const __half2 *>(&w.w));
+      wf[0] = a.x, wf[1] = a.y, wf[2] = b.x, wf[3] = b.y, wf[4] = c.x, wf[5] = c.y, wf[6] = d.x, wf[7] = d.y;
+    } else {
+      wf[0] = bf16_lo(w.x), wf[1] = bf16_hi(w.x), wf[2] = bf16_lo(w.y), wf[3] = bf16_hi(w.y);
+      wf[4] = bf16_lo(w.z), wf[5] = bf16_hi(w.z), wf[6] = bf16_lo(w.w), wf[7] = bf16_hi(w.w);
+    }
 #pragma unroll
     for (int s = 0; s < S; ++s) {
       const float4 a = *reinterpret_cast<const float4 *>(xs + s * K + i * 8);
@@ -202,11 +213,11 @@ int elementwise_init() {
 }
 
 // x [S, K] f32 (S <= GEMV_S; unused rows are read as zero padding by the caller's buffer), y [S, R] f32.
-int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int silu_out, cudaStream_t st) {
+int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int silu_out, int f16, cudaStream_t st) {
   if (K % 8 || K > 12288) return -1;
   const size_t smem = static_cast<size_t>(GEMV_S) * K * 4;
   gemv_multi_kernel<GEMV_S><<<(R + 7) / 8, 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
-                                                             silu_out);
+                                                             silu_out, f16);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
@@ -214,7 +225,7 @@ int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int
 // K7  edges: channel-major f32 latents -> token-major bf16 (the NCHW -> NLC transpose of
 // flux_transformer.c:3156-3161 / 3650-3664 fused with the cast), and f32 -> bf16 for the context.
 // ------------------------------------------------------------------------------------------------
-__global__ void pack_tokens_kernel(const float *__restrict__ z, __nv_bfloat16 *__restrict__ tok, int C, int n) {
+__global__ void pack_tokens_kernel(const float *__restrict__ z, uint16_t *__restrict__ tok, int C, int n, int f16) {
   __shared__ float tile[32][33];
   pdl_launch_dependents();
   pdl_wait();
@@ -227,31 +238,35 @@ __global__ void pack_tokens_kernel(const float *__restrict__ z, __nv_bfloat16 *_
   __syncthreads();
   for (int i = ty; i < 32; i += 8) {
     const int p = p0 + i, c = c0 + tx;
-    if (p < n && c < C) tok[static_cast<size_t>(p) * C + c] = __float2bfloat16_rn(tile[tx][i]);
+    if (p < n && c < C) {
+      const float v = tile[tx][i];
+      tok[static_cast<size_t>(p) * C + c] = static_cast<uint16_t>(pack_16x2(v, 0.f, f16 != 0) & 0xFFFFu);
+    }
   }
 }
 
-int launch_pack_tokens(const float *z, void *tok, int C, int n, cudaStream_t st) {
+int launch_pack_tokens(const float *z, void *tok, int C, int n, int f16, cudaStream_t st) {
   dim3 grid((n + 31) / 32, (C + 31) / 32);
-  return launch_kernel(pack_tokens_kernel, grid, dim3(32, 8), 0, st, 1, z, reinterpret_cast<__nv_bfloat16 *>(tok), C,
-                       n) == cudaSuccess
+  return launch_kernel(pack_tokens_kernel, grid, dim3(32, 8), 0, st, 1, z, reinterpret_cast<uint16_t *>(tok), C, n,
+                       f16) == cudaSuccess
              ? 0
              : -8;
 }
 
-__global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4) {
+__global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4, int f16) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float4 v = in[i];
-    out[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    out[i] = make_uint2(pack_16x2(v.x, v.y, f16 != 0), pack_16x2(v.z, v.w, f16 != 0));
   }
 }
 
-int launch_f32_to_bf16(const float *in, void *out, long long n, cudaStream_t st) {
+int launch_f32_to_bf16(const float *in, void *out, long long n, int f16, cudaStream_t st) {
   if (n % 4) return -1;
   const long long n4 = n / 4;
   const int grid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
-  f32_to_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float4 *>(in), reinterpret_cast<uint2 *>(out), n4);
+  f32_to_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float4 *>(in), reinterpret_cast<uint2 *>(out), n4,
+                                           f16);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

@@ -35,6 +35,32 @@ static float bf16_to_f32_host(uint16_t b) {
   memcpy(&f, &u, 4);
   return f;
 }
+// f32 -> f16 bits, round to nearest even, saturating at +-65504, subnormals handled.
+static uint16_t f32_to_f16_host(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  const uint16_t sign = static_cast<uint16_t>((u >> 16) & 0x8000u);
+  const uint32_t a = u & 0x7FFFFFFFu;
+  if (a >= 0x7F800000u) return static_cast<uint16_t>(sign | (a > 0x7F800000u ? 0x7E00u : 0x7BFFu));
+  if (a >= 0x477FF000u) return static_cast<uint16_t>(sign | 0x7BFFu);  // rounds to >= 65520: saturate
+  if (a < 0x33000001u) return sign;                                   // below half of the smallest subnormal
+  int exp = static_cast<int>(a >> 23) - 127;
+  uint32_t man = (a & 0x7FFFFFu) | 0x800000u;  // 24-bit significand
+  int shift;                                   // bits to drop
+  uint32_t base;
+  if (exp < -14) {  // subnormal result: value = man * 2^(exp-23), unit 2^-24
+    shift = -exp - 14 + 13;  // = 23 - (exp + 24)
+    base = 0;
+  } else {
+    shift = 13;
+    base = static_cast<uint32_t>(exp + 15) << 10;
+    man &= 0x7FFFFFu;
+  }
+  uint32_t q = man >> shift;
+  const uint32_t rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+  if (rem > half || (rem == half && (q & 1u))) ++q;  // may carry into the exponent: still correct
+  return static_cast<uint16_t>(sign | (base + q));
+}
 static float f16_to_f32_host(uint16_t h) {
   const uint32_t sign = (h & 0x8000u) << 16;
   int exp = (h >> 10) & 0x1F;
@@ -90,6 +116,7 @@ int model_create(flux_cuda_ctx *ctx, const ModelDims &d, flux_cuda_model **out) 
   flux_cuda_model *m = new flux_cuda_model();
   m->ctx = ctx;
   m->d = d;
+  m->f16 = ctx->f16;
   const size_t h = d.hidden, mlp = d.mlp;
   int rc = 0;
   auto A = [&](bf16 **p, size_t n) {
@@ -147,16 +174,18 @@ void model_free(flux_cuda_model *m) {
   delete m;
 }
 
-// Converts `count` elements of the source dtype (0 = F32, 1 = F16, 2 = BF16) to bf16 bits on the host.
-static const uint16_t *to_bf16_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp) {
-  if (dtype == 2) return reinterpret_cast<const uint16_t *>(data);
+// Converts `count` elements of the source dtype (0 = F32, 1 = F16, 2 = BF16) to the model's 16-bit weight format
+// on the host. bf16 -> f16 is exact for 6.1e-5 <= |w| <= 65504 (bf16 has fewer mantissa bits); smaller weights
+// land on f16 subnormals with an absolute error below 3e-8.
+static const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp,
+                                    bool want_f16) {
+  if ((dtype == 2 && !want_f16) || (dtype == 1 && want_f16)) return reinterpret_cast<const uint16_t *>(data);
   tmp.resize(count);
-  if (dtype == 0) {
-    const float *f = reinterpret_cast<const float *>(data);
-    for (size_t i = 0; i < count; ++i) tmp[i] = f32_to_bf16_host(f[i]);
-  } else {
-    const uint16_t *hh = reinterpret_cast<const uint16_t *>(data);
-    for (size_t i = 0; i < count; ++i) tmp[i] = f32_to_bf16_host(f16_to_f32_host(hh[i]));
+  const float *f = reinterpret_cast<const float *>(data);
+  const uint16_t *hh = reinterpret_cast<const uint16_t *>(data);
+  for (size_t i = 0; i < count; ++i) {
+    const float v = dtype == 0 ? f[i] : dtype == 1 ? f16_to_f32_host(hh[i]) : bf16_to_f32_host(hh[i]);
+    tmp[i] = want_f16 ? f32_to_f16_host(v) : f32_to_bf16_host(v);
   }
   return tmp.data();
 }
@@ -201,7 +230,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
   auto plain = [&](bf16 *dst, long long er, long long ec) -> int {
     int rc = want(er, ec);
     if (rc) return rc;
-    const uint16_t *src = to_bf16_host(data, dtype, count, tmp);
+    const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
     return check_cuda(cudaMemcpy(dst, src, count * 2, cudaMemcpyHostToDevice), "upload weights");
   };
   auto vec_f32 = [&](float *dst) -> int {
@@ -250,7 +279,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
     else if (t == "ff.linear_in.weight" || t == "ff_context.linear_in.weight") {
       // rows [0, mlp) = gate, [mlp, 2 mlp) = up (flux_transformer.c:4503-4523)
       if (!(rc = want(2 * mlp, h)))
-        rc = upload_interleaved(m, b.ffin[t == "ff.linear_in.weight" ? 1 : 0], to_bf16_host(data, dtype, count, tmp),
+        rc = upload_interleaved(m, b.ffin[t == "ff.linear_in.weight" ? 1 : 0], to_half_host(data, dtype, count, tmp, m->f16),
                                 mlp, h);
     } else {
       set_error("unknown tensor %s", name);
@@ -264,7 +293,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
     else if (t == "attn.to_qkv_mlp_proj.weight") {
       // rows [Q | K | V | gate | up] (flux_transformer.c:3051-3058): Q, K, V stay; gate/up are interleaved
       if (!(rc = want(3 * h + 2 * mlp, h))) {
-        const uint16_t *src = to_bf16_host(data, dtype, count, tmp);
+        const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
         rc = check_cuda(cudaMemcpy(b.lin1, src, 3 * h * h * 2, cudaMemcpyHostToDevice), "upload weights");
         if (!rc) rc = upload_interleaved(m, b.lin1 + 3 * h * h, src + 3 * h * h, mlp, h);
       }
@@ -457,6 +486,11 @@ int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, con
 }
 
 // ------------------------------------------------------------------------------------------------ forward
+// 16-bit tensors are f16 by default (model->f16): same tensor-core rate as bf16, 3 more mantissa bits where the
+// rounding error of the step comes from (the GEMM A operands). The guidance pair needs them:
+// v_u + g (v_c - v_u) multiplies per-pass errors by up to g + |1 - g|.
+#define ACT_F16 (m->f16 ? 1 : 0)
+
 struct Launcher {
   flux_cuda_model *m;
   Workspace *ws;
@@ -496,6 +530,7 @@ struct Launcher {
   // [Q|K|V] projection with the per-head RMSNorm and the rotation applied in the epilogue
   EpiSeg seg_qkv(void *out, int pos0, const float *nq_t, const float *nk_t, const float *nq_i, const float *nk_i) {
     EpiSeg s = seg(EPI_QKV_NORM_ROPE, out, 3 * m->d.hidden, 0);
+    s.out_f16 = ACT_F16;
     s.qk.wq_txt = nq_t;
     s.qk.wk_txt = nk_t;
     s.qk.wq_img = nq_i;
@@ -508,9 +543,10 @@ struct Launcher {
     s.qk.hidden = m->d.hidden;
     return s;
   }
-  static EpiSeg seg(int mode, void *out, long long ld, int col0, const float *gate = nullptr) {
+  EpiSeg seg(int mode, void *out, long long ld, int col0, const float *gate = nullptr) {
     EpiSeg s;
     memset(&s, 0, sizeof(s));
+    s.out_f16 = ACT_F16;
     s.mode = mode;
     s.col0 = col0;
     s.ld = ld;
@@ -539,6 +575,7 @@ struct Launcher {
       int r = pair ? gemm_make_problem_pair(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K)
                    : gemm_make_problem(&P.p[i], pr[i].X, pr[i].ldx, pr[i].W, pr[i].M, pr[i].N, pr[i].K, bn);
       if (r) return fail("gemm_make_problem", r);
+      P.p[i].x_f16 = ACT_F16;
       P.p[i].seg[0] = pr[i].s0;
       if (pr[i].n_split > 0 && pr[i].n_split < pr[i].N) {
         P.p[i].n_split = pr[i].n_split;
@@ -553,7 +590,8 @@ struct Launcher {
   void adaln(int row0, int rows, const float *sh_t, const float *sc_t, const float *sh_i, const float *sc_i) {
     if (rc) return;
     begin(KC_ADALN);
-    int r = launch_adaln(ws->hs, ws->norm, row0, rows, m->d.hidden, ws->N, ws->n_txt, sh_t, sc_t, sh_i, sc_i, st);
+    int r = launch_adaln(ws->hs, ws->norm, row0, rows, m->d.hidden, ws->N, ws->n_txt, ACT_F16, sh_t, sc_t, sh_i, sc_i,
+                         st);
     count();
     if (r) return fail("adaln", r);
   }
@@ -570,11 +608,12 @@ struct Launcher {
     if (rc) return;
     const int h = m->d.hidden;
     AttnParams A;
-    int r = attn_make_params(&A, ws->qkv, ws->B, ws->N, 3 * h, 0, h, 2 * h, ws->cat, h + m->d.mlp, 0, m->d.heads,
-                             m->ctx->err_dev);
+    const bool v2 = m->ctx->attn_version == 2;
+    int r = (v2 ? attn2_make_params : attn_make_params)(&A, ws->qkv, ws->B, ws->N, 3 * h, 0, h, 2 * h, ws->cat,
+                                                        h + m->d.mlp, 0, m->d.heads, ACT_F16, m->ctx->err_dev);
     if (r) return fail("attn_make_params", r);
     begin(KC_ATTN);
-    r = attn_launch(&A, st);
+    r = v2 ? attn2_launch(&A, st) : attn_launch(&A, st);
     count();
     if (r) return fail("attn_launch", r);
   }
@@ -593,14 +632,14 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
 
   // target tokens of the current latent: NCHW f32 -> NLC bf16 (reference tokens were packed once per sample)
   L.begin(KC_OTHER);
-  if (launch_pack_tokens(ws->z, ws->tok, C, ws->n_img, st)) L.fail("pack_tokens", -8);
+  if (launch_pack_tokens(ws->z, ws->tok, C, ws->n_img, ACT_F16, st)) L.fail("pack_tokens", -8);
   L.count();
   // embedders: image tokens every step; the text projection is step-invariant and was computed once
   {
     Launcher::Prob pr[2];
     for (int b = 0; b < B; ++b)
       pr[b] = {ws->tok, C, m->x_emb, n_it, h, C,
-               Launcher::seg(EPI_STORE_F32, ws->hs + (static_cast<size_t>(b) * N + n_txt) * h, h, 0), 0, {}};
+               L.seg(EPI_STORE_F32, ws->hs + (static_cast<size_t>(b) * N + n_txt) * h, h, 0), 0, {}};
     L.gemm(pr, B, 256);
     if (!L.rc &&
         cudaMemcpy2DAsync(ws->hs, static_cast<size_t>(N) * h * 4, ws->txt0, static_cast<size_t>(n_txt) * h * 4,
@@ -627,18 +666,18 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
     L.attention();
     n = per_stream([&](int, int s, size_t row, int M) {
       return Launcher::Prob{ws->cat + row * cat_ld, cat_ld, w.out[s], M, h, h,
-                            Launcher::seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 2 * h), 0, {}};
+                            L.seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 2 * h), 0, {}};
     });
     L.gemm(pr, n, 256);
     L.adaln(0, B * N, mt + 3 * h, mt + 4 * h, mi + 3 * h, mi + 4 * h);
     n = per_stream([&](int, int s, size_t row, int M) {
       return Launcher::Prob{ws->norm + row * h, h, w.ffin[s], M, 2 * mlp, h,
-                            Launcher::seg(EPI_SWIGLU_BF16, ws->cat + row * cat_ld, cat_ld, h), 0, {}};
+                            L.seg(EPI_SWIGLU_BF16, ws->cat + row * cat_ld, cat_ld, h), 0, {}};
     });
     L.gemm(pr, n, 256);
     n = per_stream([&](int, int s, size_t row, int M) {
       return Launcher::Prob{ws->cat + row * cat_ld + h, cat_ld, w.ffout[s], M, h, mlp,
-                            Launcher::seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 5 * h), 0, {}};
+                            L.seg(EPI_GATED_RES_F32, ws->hs + row * h, h, 0, (s ? mi : mt) + 5 * h), 0, {}};
     });
     L.gemm(pr, n, 256);
   }
@@ -649,11 +688,11 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
     L.adaln(0, B * N, ms, ms + h, ms, ms + h);
     Launcher::Prob p1{ws->norm, h, w.lin1, B * N, 3 * h + 2 * mlp, h,
                       L.seg_qkv(ws->qkv, 0, w.nq, w.nk, w.nq, w.nk), 3 * h,
-                      Launcher::seg(EPI_SWIGLU_BF16, ws->cat, cat_ld, h)};
+                      L.seg(EPI_SWIGLU_BF16, ws->cat, cat_ld, h)};
     L.gemm(&p1, 1, 256);
     L.attention();
     Launcher::Prob p2{ws->cat, cat_ld, w.lin2, B * N, h, h + mlp,
-                      Launcher::seg(EPI_GATED_RES_F32, ws->hs, h, 0, ms + 2 * h), 0, {}};
+                      L.seg(EPI_GATED_RES_F32, ws->hs, h, 0, ms + 2 * h), 0, {}};
     L.gemm(&p2, 1, 256);
   }
 
@@ -664,7 +703,7 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
       const size_t row = static_cast<size_t>(b) * N + n_txt;
       L.adaln(static_cast<int>(row), ws->n_img, mf + h, mf, mf + h, mf);
       pr[b] = {ws->norm + row * h, h, m->proj_out, ws->n_img, C, h,
-               Launcher::seg(EPI_STORE_F32_T, ws->v + static_cast<size_t>(b) * C * ws->n_img, ws->n_img, 0), 0, {}};
+               L.seg(EPI_STORE_F32_T, ws->v + static_cast<size_t>(b) * C * ws->n_img, ws->n_img, 0), 0, {}};
     }
     L.gemm(pr, B, 128);
   }
@@ -679,16 +718,17 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   Launcher L{m, ws, st};
   const long long ctx_n = static_cast<long long>(ws->B) * ws->n_txt * d.text_dim;
   L.begin(KC_OTHER);
-  if (launch_f32_to_bf16(ws->ctx_in, ws->ctx_bf, ctx_n, st)) L.fail("f32_to_bf16", -8);
+  if (launch_f32_to_bf16(ws->ctx_in, ws->ctx_bf, ctx_n, ACT_F16, st)) L.fail("f32_to_bf16", -8);
   L.count();
   Launcher::Prob pc{ws->ctx_bf, d.text_dim, m->ctx_emb, ws->B * ws->n_txt, h, d.text_dim,
-                    Launcher::seg(EPI_STORE_F32, ws->txt0, h, 0), 0, {}};
+                    L.seg(EPI_STORE_F32, ws->txt0, h, 0), 0, {}};
   L.gemm(&pc, 1, 256);
   size_t off = 0;
   for (const RefSpec &r : ws->refs) {
     const int n = r.h * r.w;
     L.begin(KC_OTHER);
-    if (launch_pack_tokens(ws->ref_in + off * C, ws->tok + (ws->n_img + off) * C, C, n, st)) L.fail("pack refs", -8);
+    if (launch_pack_tokens(ws->ref_in + off * C, ws->tok + (ws->n_img + off) * C, C, n, ACT_F16, st))
+      L.fail("pack refs", -8);
     L.count();
     off += n;
   }
@@ -698,13 +738,13 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   for (int s0 = 0; s0 < num_steps && !L.rc; s0 += GEMV_S) {
     L.begin(KC_OTHER);  // the three projections of this group of steps share one event pair
     int r = launch_gemv_multi(m->t1, ws->tsin + static_cast<size_t>(s0) * d.time_dim,
-                              ws->th + static_cast<size_t>(s0) * h, h, d.time_dim, 1, st);
+                              ws->th + static_cast<size_t>(s0) * h, h, d.time_dim, 1, ACT_F16, st);
     if (!r)  // svec = silu(t_emb): every consumer of t_emb applies SiLU first (flux_transformer.c:3227-3230)
       r = launch_gemv_multi(m->t2, ws->th + static_cast<size_t>(s0) * h, ws->svec + static_cast<size_t>(s0) * h, h, h,
-                            1, st);
+                            1, ACT_F16, st);
     if (!r)
       r = launch_gemv_multi(m->mod_all, ws->svec + static_cast<size_t>(s0) * h,
-                            ws->mod + static_cast<size_t>(s0) * 17 * h, 17 * h, h, 0, st);
+                            ws->mod + static_cast<size_t>(s0) * 17 * h, 17 * h, h, 0, ACT_F16, st);
     L.count();
     if (r) L.fail("modulation gemv", r);
     ws->launches += 2;

@@ -56,6 +56,7 @@ struct flux_cuda_model {
   std::set<std::string> seen;
   size_t expected = 0;
   bool finalized = false;
+  bool f16 = true;  // weights were converted to f16 at upload (else kept bf16); activations follow
   size_t weight_bytes = 0;
 };
 

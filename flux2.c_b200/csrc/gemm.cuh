@@ -31,6 +31,7 @@ struct QkvNormRope {
 
 struct EpiSeg {
   int mode;
+  int out_f16;        // 16-bit outputs are written as f16 (saturating) instead of bf16
   int col0;           // first destination column of this segment
   long long ld;       // destination leading dimension in elements
   void *out;
@@ -42,6 +43,7 @@ struct alignas(64) GemmProblem {
   CUtensorMap tmA;  // X  [M, K] bf16, box 64 x 128, 128B swizzle
   CUtensorMap tmB;  // W  [N, K] bf16, box 64 x BN,  128B swizzle
   int M, N, K;
+  int x_f16;        // X and W hold f16 instead of bf16 (tcgen05 kind::f16 needs both operands in one format)
   int n_split;      // output columns [0, n_split) go to seg[0], [n_split, N) to seg[1]
   EpiSeg seg[2];
   int tiles_m, tiles_n;

@@ -115,13 +115,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * P_BM, P_BN, 0, 0);
+      constexpr uint32_t idesc_bf16 = make_idesc_16(2 * P_BM, P_BN, FMT_BF16, FMT_BF16, 0, 0);
+      constexpr uint32_t idesc_f16 = make_idesc_16(2 * P_BM, P_BN, FMT_F16, FMT_F16, 0, 0);
       uint32_t kiter = 0, it = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < P.total_tiles; tile += num_pairs, ++it) {
         int prob, m0, n0;
         decode(tile, prob, m0, n0);
         const int KB = P.p[prob].K / P_BK;
+        const uint32_t idesc = P.p[prob].x_f16 ? idesc_f16 : idesc_bf16;
         const int acc = it & 1;
         if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
           fail(KERR_WAIT_TMEM_EMPTY);
@@ -217,6 +219,7 @@ int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const v
   p->M = M;
   p->N = N;
   p->K = K;
+  p->x_f16 = 0;
   p->n_split = N;
   p->tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
   p->tiles_n = N / P_BN;

@@ -15,6 +15,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
   const int nrel = n0 - (second ? pb.n_split : 0);  // segment-relative first column of this tile
   const int row = m0 + lane_row;
   const bool row_ok = row < pb.M;
+  const bool f16 = sg.out_f16 != 0;
   uint32_t r[32];
 
   switch (sg.mode) {
@@ -29,10 +30,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            v.x = pack_16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16);
+            v.y = pack_16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16);
+            v.z = pack_16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16);
+            v.w = pack_16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16);
             d4[j] = v;
           }
         }
@@ -93,10 +94,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
               for (int e = 0; e < 8; ++e)
                 o[e] = silu_f(__uint_as_float(r[8 * j + e])) * __uint_as_float(u[8 * j + e]);
               uint4 v;
-              v.x = pack_bf16x2(o[0], o[1]);
-              v.y = pack_bf16x2(o[2], o[3]);
-              v.z = pack_bf16x2(o[4], o[5]);
-              v.w = pack_bf16x2(o[6], o[7]);
+              v.x = pack_16x2(o[0], o[1], f16);
+              v.y = pack_16x2(o[2], o[3], f16);
+              v.z = pack_16x2(o[4], o[5], f16);
+              v.w = pack_16x2(o[6], o[7], f16);
               d4[j] = v;
             }
           }
@@ -161,8 +162,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
                   const float x1 = __uint_as_float(r[8 * j + 4 * e + 1]) * rinv * ww.y;
                   const float x2 = __uint_as_float(r[8 * j + 4 * e + 2]) * rinv * ww.z;
                   const float x3 = __uint_as_float(r[8 * j + 4 * e + 3]) * rinv * ww.w;
-                  o[2 * e + 0] = pack_bf16x2(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x);
-                  o[2 * e + 1] = pack_bf16x2(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z);
+                  o[2 * e + 0] = pack_16x2(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x, f16);
+                  o[2 * e + 1] = pack_16x2(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z, f16);
                 }
                 d4[j] = make_uint4(o[0], o[1], o[2], o[3]);
               }
@@ -170,10 +171,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                v.x = pack_16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16);
+                v.y = pack_16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16);
+                v.z = pack_16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16);
+                v.w = pack_16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16);
                 d4[j] = v;
               }
             }

@@ -159,13 +159,19 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
-// Instruction descriptor for tcgen05.mma kind::f16 with bf16 inputs and f32 accumulation.
-// Bits: [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format, 15 A major
-// (0 = K), 16 B major, [17,23) N>>3, [24,29) M>>4.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+// Instruction descriptor for tcgen05.mma kind::f16 with 16-bit inputs and f32 accumulation.
+// Bits: [4,6) D format (1 = f32), [7,10) A format (0 = f16, 1 = bf16), [10,13) B format, 15 A major
+// (0 = K), 16 B major, [17,23) N>>3, [24,29) M>>4. Both operands must use the same format: an f16 x bf16
+// descriptor raises "illegal instruction" on sm_100a.
+static constexpr uint32_t FMT_F16 = 0, FMT_BF16 = 1;
+__host__ __device__ constexpr uint32_t make_idesc_16(int M, int N, uint32_t a_fmt, uint32_t b_fmt, int a_mn_major,
+                                                     int b_mn_major) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
+  return make_idesc_16(M, N, FMT_BF16, FMT_BF16, a_mn_major, b_mn_major);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
@@ -205,6 +211,16 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&v);
+}
+// Two f32 -> packed f16x2, round to nearest, saturating to +-65504 instead of overflowing to infinity.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// 16-bit pair in the requested activation format.
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi, bool f16) {
+  return f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }

@@ -36,6 +36,15 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx);
 /* The context's cudaStream_t, for callers that time with their own CUDA events. */
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx);
 
+/*
+ * 16-bit storage format of models created afterwards from this context: FLUX_CUDA_F16 (default) or FLUX_CUDA_BF16
+ * (also: environment variable FLUX_CUDA_BF16=1 before the context is created). Weights arrive as bf16 in the
+ * file and are converted once at upload (exact for 6.1e-5 <= |w| <= 65504, absolute error below 3e-8 under
+ * that); activations use the same format because tcgen05 kind::f16 needs both operands in one format. f16 has
+ * three more mantissa bits than bf16 at the same tensor-core rate; every 16-bit store saturates at +-65504.
+ */
+int flux_cuda_ctx_set_half_format(flux_cuda_ctx *ctx, int dtype);
+
 /* Chooses how the 256-column GEMM tiles are computed: 0 = one CTA per 128 x 256 tile, 1 = a pair of CTAs on
  * neighbouring SMs per 256 x 256 tile (tcgen05 cta_group::2; each CTA stages half of the weight tile). Also
  * settable with the environment variable FLUX_CUDA_GEMM_PAIR before the context is created. */
@@ -187,6 +196,10 @@ void flux_cuda_init_noise(int channels, int h, int w, long long seed, float *out
 #define FLUX_CUDA_EPI_GATED_RES_F32 2
 #define FLUX_CUDA_EPI_SWIGLU_BF16 3
 #define FLUX_CUDA_EPI_STORE_F32_T 4
+/* or-ed into `epilogue`: x AND w hold f16 instead of bf16 / 16-bit outputs are written as f16 (saturating at
+ * +-65504) instead of bf16. */
+#define FLUX_CUDA_EPI_X_F16 0x100
+#define FLUX_CUDA_EPI_OUT_F16 0x200
 
 /*
  * out = epilogue(x[M,K] * w[N,K]^T), x and w bf16 row-major, f32 accumulation.
@@ -211,7 +224,8 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
  * hidden % 256 == 0 (two 128-wide heads per output tile), K % 64 == 0.
  */
 int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *w, void *out, int M, int hidden, int K,
-                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq);
+                                 const float *wq, const float *wk, const float *cos_t, const float *sin_t, int seq,
+                                 int f16 /* x and out in f16 instead of bf16 */);
 
 /*
  * Joint attention over a fused projection buffer qkv[batch*seq, ld] (bf16): for every head,
@@ -219,10 +233,11 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
  * (+128*head). Replaces mha_forward / joint_attention (flux_transformer.c:1249-1330, 1335-1460).
  */
 int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
-                        int v_col, int heads, void *out, long long out_ld, int out_col);
-/* apply_adaln (flux_transformer.c:979-1048): out_bf16 = (1 + scale) * LayerNorm(x_f32) + shift, rows x hidden. */
+                        int v_col, int heads, void *out, long long out_ld, int out_col,
+                        int f16 /* qkv and out hold f16 instead of bf16 */);
+/* apply_adaln (flux_transformer.c:979-1048): out_16 = (1 + scale) * LayerNorm(x_f32) + shift, rows x hidden. */
 int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
-                    const float *scale);
+                    const float *scale, int f16 /* out in f16 instead of bf16 */);
 /* apply_qk_norm + apply_rope_2d (flux_transformer.c:1052-1106, 719-741) in place on bf16 Q and K. */
 int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
                            int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t);

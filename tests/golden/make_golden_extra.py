@@ -72,5 +72,33 @@ def main():
     np.savez_compressed(os.path.join(HERE, "reference_extra.npz"), **out)
 
 
+def guided_512():
+    """BASELINE config 3 in full: benchmark weights, 512x512, 50 Euler steps, guidance 4.0, separate conditional /
+    unconditional 512-token contexts. 100 reference forwards (about half an hour on 8 cores). Stored: the final
+    latent and, for three probe steps, the reference's state and combined velocity."""
+    lib = rb.RefLib(rb.best_kind())
+    tf = model("base", lib)
+    h = w = 32
+    steps, g = 50, 4.0
+    z = lib.init_noise(128, h, w, 42)
+    cc = synth.make_context(1234, 512, D.text_dim)
+    cu = synth.make_context(4321, 512, D.text_dim)
+    sch = lib.official_schedule(steps, h * w)
+    out = {"sched": sch, "ref_build": lib.kind}
+    t0 = time.time()
+    for i in range(steps):
+        vu = tf.forward(z, h, w, cu, float(sch[i]))
+        vc = tf.forward(z, h, w, cc, float(sch[i]))
+        v = vu + np.float32(g) * (vc - vu)
+        if i in (0, 24, 49):
+            out["z_%d" % i] = z.copy()
+            out["v_%d" % i] = v.copy()
+        z = z + np.float32(sch[i + 1] - sch[i]) * v
+        print("guided 512 step", i, time.time() - t0, flush=True)
+    out["final"] = z
+    tf.close()
+    np.savez_compressed(os.path.join(HERE, "reference_guided512.npz"), **out)
+
+
 if __name__ == "__main__":
-    main()
+    guided_512() if sys.argv[1:] == ["guided512"] else main()

@@ -155,3 +155,34 @@ def test_gemm_pair_swiglu_and_gated(fx, ctx):
     ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
     assert _rel(out.float(), ref) < 4e-3
     assert _rel(h, h0.double() + gate.double() * (x.double() @ wg.double().t())) < 3e-5
+
+
+# ---- f16 operands (what the engine runs by default): same kernels, other operand format.
+# tcgen05 kind::f16 wants both operands in ONE format: an f16 x bf16 descriptor is an illegal instruction.
+@pytest.mark.parametrize("tile_n", [256, 512, 128])
+@pytest.mark.parametrize("M,N,K", [(1536, 3072, 3072), (200, 768, 128)])
+def test_gemm_f16_operands(fx, ctx, M, N, K, tile_n):
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.float16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.float16)
+    out32 = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    out16 = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out32.data_ptr(), M, N, K, fx.EPI_STORE_F32 | fx.EPI_X_F16, tile_n=tile_n)
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out16.data_ptr(), M, N, K,
+                  fx.EPI_STORE_BF16 | fx.EPI_X_F16 | fx.EPI_OUT_F16, tile_n=tile_n)
+    ctx.sync()
+    ref = x.double() @ w.double().t()
+    assert _rel(out32, ref) < 3e-5
+    assert _rel(out16.float(), ref) < 5e-4  # f16 output rounding
+
+
+def test_gemm_f16_output_saturates_instead_of_overflowing(fx, ctx):
+    M, N, K = 128, 256, 64
+    x = torch.full((M, K), 200.0, device="cuda", dtype=torch.float16)
+    w = torch.full((N, K), 8.0, device="cuda", dtype=torch.float16)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, fx.EPI_STORE_BF16 | fx.EPI_X_F16 | fx.EPI_OUT_F16)
+    ctx.sync()
+    assert torch.isfinite(out).all() and (out == 65504).all()  # 200 * 8 * 64 = 102400 > f16 max

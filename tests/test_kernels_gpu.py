@@ -11,39 +11,43 @@ def _rel(a, b):
     return ((a.double() - b.double()).norm() / b.double().norm()).item()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("batch,seq,heads,sharp", [
     (1, 128, 1, 1.0), (1, 256, 2, 1.0), (1, 48, 2, 1.0), (1, 300, 3, 3.0), (1, 1536, 24, 1.0), (2, 200, 2, 2.0),
     (1, 768, 24, 0.02),
 ])
-def test_attention_matches_torch(fx, ctx, batch, seq, heads, sharp):
+def test_attention_matches_torch(fx, ctx, batch, seq, heads, sharp, dtype):
     hid = heads * 128
     g = torch.Generator(device="cuda").manual_seed(seq + heads)
-    qkv = (torch.randn(batch * seq, 3 * hid, device="cuda", generator=g) * sharp).to(torch.bfloat16)
+    qkv = (torch.randn(batch * seq, 3 * hid, device="cuda", generator=g) * sharp).to(dtype)
     out_ld = hid + 256  # output lands inside a wider [attention | mlp] buffer
-    out = torch.zeros(batch * seq, out_ld, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(batch * seq, out_ld, device="cuda", dtype=dtype)
     torch.cuda.synchronize()
-    ctx.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), out_ld, 0)
+    ctx.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), out_ld, 0,
+                  f16=dtype == torch.float16)
     ctx.sync()
     q, k, v = [t.float().reshape(batch, seq, heads, 128).transpose(1, 2) for t in qkv.split(hid, dim=1)]
     s = (q @ k.transpose(-1, -2)) / math.sqrt(128.0)
     ref = (torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(batch * seq, hid)
     assert torch.isfinite(out.float()).all()
     assert (out[:, hid:] == 0).all()
-    assert _rel(out[:, :hid].float(), ref) < 1e-2  # bf16 P and bf16 output
+    assert _rel(out[:, :hid].float(), ref) < (2e-3 if dtype == torch.float16 else 1e-2)  # 16-bit P and output
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,hidden", [(1, 256), (37, 256), (1536, 3072), (1000, 1024)])
-def test_adaln_matches_torch(fx, ctx, rows, hidden):
+def test_adaln_matches_torch(fx, ctx, rows, hidden, dtype):
     g = torch.Generator(device="cuda").manual_seed(rows)
     x = torch.randn(rows, hidden, device="cuda", generator=g) * 3 + 0.5
     shift = torch.randn(hidden, device="cuda", generator=g)
     scale = torch.randn(hidden, device="cuda", generator=g)
-    out = torch.zeros(rows, hidden, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(rows, hidden, device="cuda", dtype=dtype)
     torch.cuda.synchronize()
-    ctx.adaln(x.data_ptr(), out.data_ptr(), rows, hidden, shift.data_ptr(), scale.data_ptr())
+    ctx.adaln(x.data_ptr(), out.data_ptr(), rows, hidden, shift.data_ptr(), scale.data_ptr(),
+              f16=dtype == torch.float16)
     ctx.sync()
     ref = torch.nn.functional.layer_norm(x, (hidden,), eps=1e-6) * (1 + scale) + shift
-    assert _rel(out.float(), ref) < 4e-3
+    assert _rel(out.float(), ref) < (5e-4 if dtype == torch.float16 else 4e-3)
 
 
 def test_adaln_rejects_unsupported_hidden(fx, ctx):
@@ -81,22 +85,23 @@ def test_qk_norm_rope_matches_torch(fx, ctx, batch, seq, heads):
     assert torch.equal(work[:, 2 * hid:], qkv[:, 2 * hid:])  # V untouched
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,heads,K,seq", [(100, 2, 256, 50), (1536, 24, 3072, 1536), (300, 4, 128, 300)])
-def test_fused_qkv_projection_norm_rope(fx, ctx, M, heads, K, seq):
+def test_fused_qkv_projection_norm_rope(fx, ctx, M, heads, K, seq, dtype):
     """GEMM epilogue variant: projection + per-head RMSNorm + rotation on Q, K; V untouched."""
     hid = heads * 128
     g = torch.Generator(device="cuda").manual_seed(M)
-    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
-    w = (torch.randn(3 * hid, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(3 * hid, K, device="cuda", generator=g) * 0.05).to(dtype)  # both operands in one format
     wq = torch.randn(128, device="cuda", generator=g)
     wk = torch.randn(128, device="cuda", generator=g)
     ang = torch.rand(seq, 64, device="cuda", generator=g) * 6.28
     cos = torch.cos(ang).repeat_interleave(2, dim=1).contiguous()
     sin = torch.sin(ang).repeat_interleave(2, dim=1).contiguous()
-    out = torch.zeros(M, 3 * hid, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(M, 3 * hid, device="cuda", dtype=dtype)
     torch.cuda.synchronize()
     ctx.gemm_qkv_norm_rope(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, hid, K, wq.data_ptr(), wk.data_ptr(),
-                           cos.data_ptr(), sin.data_ptr(), seq)
+                           cos.data_ptr(), sin.data_ptr(), seq, f16=dtype == torch.float16)
     ctx.sync()
     y = x.float() @ w.float().t()
     pos = torch.arange(M, device="cuda") % seq
@@ -108,6 +113,7 @@ def test_fused_qkv_projection_norm_rope(fx, ctx, M, heads, K, seq):
         c, s = cos[pos][:, None, 0::2], sin[pos][:, None, 0::2]
         return torch.stack([t0 * c - t1 * s, t1 * c + t0 * s], dim=-1).reshape(M, hid)
 
-    assert _rel(out[:, :hid].float(), ref_one(y[:, :hid], wq)) < 4e-3
-    assert _rel(out[:, hid:2 * hid].float(), ref_one(y[:, hid:2 * hid], wk)) < 4e-3
-    assert _rel(out[:, 2 * hid:].float(), y[:, 2 * hid:]) < 4e-3
+    tol = 5e-4 if dtype == torch.float16 else 4e-3
+    assert _rel(out[:, :hid].float(), ref_one(y[:, :hid], wq)) < tol
+    assert _rel(out[:, hid:2 * hid].float(), ref_one(y[:, hid:2 * hid], wk)) < tol
+    assert _rel(out[:, 2 * hid:].float(), y[:, 2 * hid:]) < tol

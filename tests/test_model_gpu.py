@@ -121,6 +121,26 @@ def test_tiny_sampler_with_reference(tiny, synth, fx):
     assert rel(model.sample(z0, h, w, c, sch, refs=refs), om.sample_euler(z0, h, w, c, sch, refs=refs)) < LATENT_TOL
 
 
+def test_tiny_forward_in_bf16_mode(tiny, synth, fx):
+    """The same kernels with bf16 storage (FLUX_CUDA_BF16 / flux_cuda_ctx_set_half_format): still inside the
+    per-step tolerance, and measurably less accurate than the default f16 storage."""
+    d, W, model, om = tiny
+    c2 = fx.Context(0)
+    c2.set_half_format("bf16")
+    m2 = fx.Model.from_tensors(c2, d, W)
+    try:
+        z = synth.make_latent(11, d.latent_ch, 8, 8)
+        c = synth.make_context(12, 64, d.text_dim)
+        want = om.forward(z, 8, 8, c, 0.5)
+        e_bf16 = rel(m2.forward(z, 8, 8, c, 0.5), want)
+        e_f16 = rel(model.forward(z, 8, 8, c, 0.5), want)
+        assert e_bf16 < VEL_TOL
+        assert e_f16 < 0.5 * e_bf16
+    finally:
+        m2.close()
+        c2.close()
+
+
 def test_forward_is_deterministic(tiny, synth):
     d, W, model, om = tiny
     z = synth.make_latent(61, d.latent_ch, 8, 8)
@@ -305,3 +325,31 @@ def test_klein_img2img_1024_forward_matches_reference(klein, synth, fx):
     v = model.forward(z, 64, 64, c, 1.0, [(ref, 10)])
     assert rel(v[:, ::2, ::2], ex["img2img_1024_v_sub"]) < VEL_TOL
     assert abs(np.sqrt((v.astype(np.float64) ** 2).mean()) / float(ex["img2img_1024_v_rms"]) - 1.0) < 1e-2
+
+
+def test_klein_config3_guided_512_matches_reference(klein, synth, fx):
+    """The base-model benchmark configuration in full: 512x512, 50 Euler steps, guidance 4.0, the conditional and
+    unconditional passes run as one batch of two. Per-step tolerance on the combined velocity at three probe steps
+    of the reference's own trajectory; final-latent tolerance on the engine's free-running 50-step loop."""
+    kind, d, model, gold = klein
+    if kind != "base":
+        pytest.skip("stored for the benchmark weights")
+    path = os.path.join(GOLDEN, "reference_guided512.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_guided512.npz missing")
+    ex = np.load(path)
+    h = w = 32
+    g = 4.0
+    sch = ex["sched"]
+    assert len(sch) == 51
+    cc = synth.make_context(1234, 512, d.text_dim)
+    cu = synth.make_context(4321, 512, d.text_dim)
+    for i in (0, 24, 49):
+        z = ex["z_%d" % i]
+        vu = model.forward(z, h, w, cu, float(sch[i]))
+        vc = model.forward(z, h, w, cc, float(sch[i]))
+        assert rel(vu + np.float32(g) * (vc - vu), ex["v_%d" % i]) < VEL_TOL
+    z0 = fx.init_noise(128, h, w, 42)
+    assert np.allclose(z0, ex["z_0"], atol=2e-6)
+    got = model.sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=g)
+    assert rel(got, ex["final"]) < LATENT_TOL
