@@ -385,7 +385,7 @@ def run_ours(args):
             f1 = 2.0 * n_tok * dims.hidden * (3 * dims.hidden + 2 * dims.mlp)
             ms1 = sum(lin1) / len(lin1)
             a1 = f1 / (ms1 * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": "gemm2_bf16_tn_kernel on the single-stream linear1 shape "
+            roof = {"bound": "tensor", "kernel": "gemm2_bf16_tn_kernel (f16 operands, CTA pairs) on the single-stream linear1 shape "
                     "[%d x %d] . [%d x %d]" % (n_tok, dims.hidden, dims.hidden, 3 * dims.hidden + 2 * dims.mlp),
                     "achieved": a1, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                     "frac": a1 / peaks["bf16_sustained"],

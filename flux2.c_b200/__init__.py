@@ -67,6 +67,10 @@ def _declare(L):
     L.flux_cuda_qk_norm_rope.restype = c_int
     L.flux_cuda_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p, c_void_p, c_void_p]
+    L.flux_cuda_patchify.restype = c_int
+    L.flux_cuda_patchify.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
+    L.flux_cuda_unpatchify.restype = c_int
+    L.flux_cuda_unpatchify.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
     L.flux_cuda_dims_klein4b.restype = None
     L.flux_cuda_dims_klein4b.argtypes = [ctypes.POINTER(CDims)]
     L.flux_cuda_model_load_safetensors.restype = c_int
@@ -202,6 +206,12 @@ class Context:
 
     def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, f16=False):
         check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, int(f16)))
+
+    def patchify(self, out_ptr, in_ptr, batch, channels, H, W, patch):
+        check(lib().flux_cuda_patchify(self.handle, out_ptr, in_ptr, batch, channels, H, W, patch))
+
+    def unpatchify(self, out_ptr, in_ptr, batch, channels, H, W, patch):
+        check(lib().flux_cuda_unpatchify(self.handle, out_ptr, in_ptr, batch, channels, H, W, patch))
 
     def qk_norm_rope(self, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr, cos_ptr, sin_ptr):
         check(lib().flux_cuda_qk_norm_rope(self.handle, qkv_ptr, ld, q_col, k_col, seq, batch, heads, wq_ptr, wk_ptr,

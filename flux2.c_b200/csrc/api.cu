@@ -201,6 +201,24 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   return FLUX_CUDA_OK;
 }
 
+int flux_cuda_patchify(flux_cuda_ctx *ctx, float *out, const float *in, int batch, int channels, int H, int W,
+                       int patch_size) {
+  if (!ctx || !out || !in || batch <= 0 || channels <= 0 || H <= 0 || W <= 0) return FLUX_CUDA_ERR_ARG;
+  int rc = launch_patchify(out, const_cast<float *>(in), batch, channels, H, W, patch_size, 1, ctx->stream);
+  if (rc) set_error("patchify: H and W must be multiples of the patch size");
+  return rc == 0 ? FLUX_CUDA_OK : rc == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
+}
+int flux_cuda_unpatchify(flux_cuda_ctx *ctx, float *out, const float *in, int batch, int channels, int H, int W,
+                         int patch_size) {
+  if (!ctx || !out || !in || batch <= 0 || channels <= 0 || H <= 0 || W <= 0 || patch_size <= 0)
+    return FLUX_CUDA_ERR_ARG;
+  // the reference passes the PACKED height and width here; the kernel wants the plain ones
+  int rc = launch_patchify(const_cast<float *>(in), out, batch, channels, H * patch_size, W * patch_size, patch_size, 0,
+                           ctx->stream);
+  if (rc) set_error("unpatchify: launch failed");
+  return rc == 0 ? FLUX_CUDA_OK : FLUX_CUDA_ERR_CUDA;
+}
+
 int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq, long long ld, int q_col, int k_col,
                         int v_col, int heads, void *out, long long out_ld, int out_col, int f16) {
   if (!ctx || !qkv || !out) return FLUX_CUDA_ERR_ARG;

@@ -271,6 +271,40 @@ int launch_f32_to_bf16(const float *in, void *out, long long n, int f16, cudaStr
 }
 
 // ------------------------------------------------------------------------------------------------
+// K7b  patchify / unpatchify: space-to-depth of p x p pixel blocks, [B, C, H, W] <-> [B, C p p, H/p, W/p] with the
+// new channel index c p p + pi p + pj (flux_patchify / flux_unpatchify, flux_kernels.c:1038-1094). This is the
+// layout change between VAE latents (32 channels) and the DiT's 128-channel latents. One thread per element of
+// the PACKED tensor, so the packed side is read or written fully coalesced.
+// ------------------------------------------------------------------------------------------------
+__global__ void patchify_kernel(float *__restrict__ packed, float *__restrict__ plain, int C, int H, int W, int p,
+                                long long total, int to_packed) {
+  const int oh = H / p, ow = W / p;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pw = static_cast<int>(i % ow);
+    long long r = i / ow;
+    const int ph = static_cast<int>(r % oh);
+    r /= oh;
+    const int oc = static_cast<int>(r % (C * p * p));
+    const long long b = r / (C * p * p);
+    const int c = oc / (p * p), pi = (oc / p) % p, pj = oc % p;
+    const long long j = ((b * C + c) * H + (ph * p + pi)) * W + (pw * p + pj);
+    if (to_packed) packed[i] = plain[j];
+    else plain[j] = packed[i];
+  }
+}
+
+int launch_patchify(float *packed, float *plain, int batch, int C, int H, int W, int p, int to_packed, cudaStream_t st) {
+  if (p <= 0 || H % p || W % p) return -1;
+  const long long total = static_cast<long long>(batch) * C * H * W;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  patchify_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(packed, plain, C, H, W, p, total, to_packed);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// ------------------------------------------------------------------------------------------------
 // K6  sampler updates: Euler  z += dt * v  (flux_axpy, flux_kernels.c:126-130; flux_sample.c:248) and
 // the classifier-free-guidance combine  v = v_u + g (v_c - v_u); z += dt * v  (flux_sample.c:495-499).
 // dt is read from the device-resident schedule so that a captured launch works for every step.

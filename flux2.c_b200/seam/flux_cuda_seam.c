@@ -15,6 +15,7 @@
  * step but the last), timing globals. Difference: there is no CPU fallback - a CUDA failure returns NULL
  * with the reason on stderr.
  */
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -40,6 +41,14 @@ typedef struct { /* flux.c:68-72 */
   int h, w;
   int t_offset;
 } flux_ref_t;
+
+float *flux_linear_schedule(int num_steps);
+float *flux_init_noise(int batch, int channels, int h, int w, int64_t seed);
+float *flux_transformer_forward(flux_transformer_t *tf, const float *img_latent, int img_h, int img_w,
+                                const float *txt_emb, int txt_seq, float timestep);
+float *flux_sample_euler(void *transformer, void *text_encoder, float *z, int batch, int channels, int h, int w,
+                         const float *text_emb, int text_seq, const float *schedule, int num_steps,
+                         void (*progress_callback)(int step, int total));
 
 double flux_timing_transformer_total = 0.0;
 double flux_timing_transformer_double = 0.0;
@@ -288,6 +297,137 @@ float *flux_sample_euler_cfg_with_multi_refs(void *transformer, void *text_encod
                        text_seq_cond, text_emb_uncond, text_seq_uncond, guidance_scale, schedule, num_steps,
                        progress_callback);
 }
+
+/* ------------------------------------------------------------------------------------------ other samplers
+ * Exported by flux_sample.c but called from nowhere in the reference (flux_sample.c:697-821, 891-930). They are
+ * host loops over single forwards, kept for symbol completeness; the latent visits the host between steps. */
+static void after_step(int step, int num_steps, const float *z, int h, int w, void (*progress_callback)(int, int)) {
+  if (progress_callback) progress_callback(step + 1, num_steps);
+  if (flux_step_image_callback && flux_step_image_vae && step + 1 < num_steps) {
+    flux_image *img = flux_vae_decode((flux_vae_t *)flux_step_image_vae, z, 1, h, w);
+    if (img) {
+      flux_step_image_callback(step + 1, num_steps, img);
+      flux_image_free(img);
+    }
+  }
+}
+
+/* Euler steps with fresh Gaussian noise of scale eta * sqrt(|dt|) added after every step but the last. */
+float *flux_sample_euler_ancestral(void *transformer, float *z, int batch, int channels, int h, int w,
+                                   const float *text_emb, int text_seq, const float *schedule, int num_steps,
+                                   float eta, void (*progress_callback)(int step, int total)) {
+  flux_transformer_t *tf = (flux_transformer_t *)transformer;
+  if (!tf || !z || batch != 1) return NULL;
+  const int n = channels * h * w;
+  float *cur = (float *)malloc((size_t)n * sizeof(float));
+  float *noise = (float *)malloc((size_t)n * sizeof(float));
+  if (!cur || !noise) {
+    free(cur);
+    free(noise);
+    return NULL;
+  }
+  memcpy(cur, z, (size_t)n * sizeof(float));
+  for (int step = 0; step < num_steps; step++) {
+    const float dt = schedule[step + 1] - schedule[step];
+    float *v = flux_transformer_forward(tf, cur, h, w, text_emb, text_seq, schedule[step]);
+    if (!v) {
+      free(cur);
+      free(noise);
+      return NULL;
+    }
+    for (int i = 0; i < n; i++) cur[i] += dt * v[i];
+    free(v);
+    if (eta > 0.0f && step < num_steps - 1) {
+      const float sigma = eta * sqrtf(fabsf(dt));
+      flux_randn(noise, n);
+      for (int i = 0; i < n; i++) cur[i] += sigma * noise[i];
+    }
+    after_step(step, num_steps, cur, h, w, progress_callback);
+  }
+  free(noise);
+  return cur;
+}
+
+/* Heun (second order): predictor z + dt v(z, t), corrector with the mean of the two velocities; the last step
+ * is a plain Euler step. */
+float *flux_sample_heun(void *transformer, float *z, int batch, int channels, int h, int w, const float *text_emb,
+                        int text_seq, const float *schedule, int num_steps,
+                        void (*progress_callback)(int step, int total)) {
+  flux_transformer_t *tf = (flux_transformer_t *)transformer;
+  if (!tf || !z || batch != 1) return NULL;
+  const int n = channels * h * w;
+  float *cur = (float *)malloc((size_t)n * sizeof(float));
+  float *pred = (float *)malloc((size_t)n * sizeof(float));
+  if (!cur || !pred) {
+    free(cur);
+    free(pred);
+    return NULL;
+  }
+  memcpy(cur, z, (size_t)n * sizeof(float));
+  for (int step = 0; step < num_steps; step++) {
+    const float dt = schedule[step + 1] - schedule[step];
+    float *v1 = flux_transformer_forward(tf, cur, h, w, text_emb, text_seq, schedule[step]);
+    float *v2 = NULL;
+    if (v1 && step < num_steps - 1) {
+      for (int i = 0; i < n; i++) pred[i] = cur[i] + dt * v1[i];
+      v2 = flux_transformer_forward(tf, pred, h, w, text_emb, text_seq, schedule[step + 1]);
+    }
+    if (!v1 || (step < num_steps - 1 && !v2)) {
+      free(v1);
+      free(cur);
+      free(pred);
+      return NULL;
+    }
+    if (v2)
+      for (int i = 0; i < n; i++) cur[i] += 0.5f * dt * (v1[i] + v2[i]);
+    else
+      for (int i = 0; i < n; i++) cur[i] += dt * v1[i];
+    free(v1);
+    free(v2);
+    after_step(step, num_steps, cur, h, w, progress_callback);
+  }
+  free(pred);
+  return cur;
+}
+
+/* Shifted-sigmoid and resolution-dependent schedules (flux_sample.c:75-116). */
+float *flux_sigmoid_schedule(int num_steps, float shift) {
+  float *s = (float *)malloc((num_steps + 1) * sizeof(float));
+  if (!s) return NULL;
+  for (int i = 0; i <= num_steps; i++) {
+    const float x = ((float)i / (float)num_steps - 0.5f) * 10.0f + shift;
+    s[i] = 1.0f - 1.0f / (1.0f + expf(-x));
+  }
+  s[0] = 1.0f;
+  s[num_steps] = 0.0f;
+  return s;
+}
+
+float *flux_resolution_schedule(int num_steps, int height, int width) {
+  float *s = (float *)malloc((num_steps + 1) * sizeof(float));
+  if (!s) return NULL;
+  const long pixels = (long)height * width;
+  const float shift = pixels >= 1024L * 1024L ? 1.0f : pixels >= 512L * 512L ? 0.5f : 0.0f;
+  for (int i = 0; i <= num_steps; i++) s[i] = 1.0f - powf((float)i / (float)num_steps, 1.0f + 0.5f * shift);
+  return s;
+}
+
+/* flux_generate_latent (flux_sample.c:891-919): noise from the seed, LINEAR schedule, plain Euler loop. */
+float *flux_generate_latent(void *ctx_ptr, const float *text_emb, int text_seq, int height, int width, int num_steps,
+                            int64_t seed, void (*progress_callback)(int step, int total)) {
+  const int lh = height / 16, lw = width / 16;
+  float *z = flux_init_noise(1, FLUX_LATENT_CHANNELS, lh, lw, seed);
+  float *sched = flux_linear_schedule(num_steps);
+  float *out = (z && sched) ? flux_sample_euler(ctx_ptr, NULL, z, 1, FLUX_LATENT_CHANNELS, lh, lw, text_emb, text_seq,
+                                                sched, num_steps, progress_callback)
+                            : NULL;
+  free(z);
+  free(sched);
+  return out;
+}
+
+void (*flux_progress_callback)(int, int) = NULL;
+void flux_set_progress_callback(void (*callback)(int, int)) { flux_progress_callback = callback; }
 
 /* ------------------------------------------------------------------------------------------ host pieces */
 float *flux_linear_schedule(int num_steps) {

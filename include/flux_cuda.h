@@ -242,6 +242,16 @@ int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int
 int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
                            int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t);
 
+/*
+ * flux_patchify / flux_unpatchify (flux_kernels.c:1038-1094), device pointers, f32: p x p space-to-depth between
+ * VAE latents [B, C, H, W] and DiT latents [B, C p p, H/p, W/p] (new channel = c p p + pi p + pj). Arguments as in
+ * the reference: patchify takes the plain H, W; unpatchify takes the packed H, W.
+ */
+int flux_cuda_patchify(flux_cuda_ctx *ctx, float *out, const float *in, int batch, int channels, int H, int W,
+                       int patch_size);
+int flux_cuda_unpatchify(flux_cuda_ctx *ctx, float *out, const float *in, int batch, int channels, int H, int W,
+                         int patch_size);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,6 +12,7 @@ numpy, what the reference computes on its CPU path:
   * flux_official_schedule, flux_linear/power_schedule         flux_sample.c:49-69, 122-155
   * flux_sample_euler*, flux_sample_euler_cfg*                 flux_sample.c:212-290, 303-444, 457-691
   * flux_rng_seed / flux_randn / flux_init_noise               flux_kernels.c:45-102, flux_sample.c:835-877
+  * flux_patchify / flux_unpatchify                            flux_kernels.c:1038-1094
 
 Parity is PINNED: tests/golden/ holds outputs of the reference itself (compiled from its own
 sources by oracle/Makefile and run through oracle/ref_binding.py by tests/golden/make_golden.py),
@@ -177,6 +178,22 @@ def apply_rope(x, cos, sin):
     out[..., 0::2] = x0 * c - x1 * s
     out[..., 1::2] = x1 * c + x0 * s
     return out
+
+
+# ----------------------------------------------------------------------------------------- patchify
+def patchify(x, p=2):
+    """[B, C, H, W] -> [B, C p p, H/p, W/p], new channel = c p p + pi p + pj (flux_kernels.c:1038-1065)."""
+    B, C, H, W = x.shape
+    y = x.reshape(B, C, H // p, p, W // p, p).transpose(0, 1, 3, 5, 2, 4)
+    return np.ascontiguousarray(y.reshape(B, C * p * p, H // p, W // p))
+
+
+def unpatchify(x, p=2):
+    """[B, C p p, H, W] -> [B, C, H p, W p] (flux_kernels.c:1067-1094)."""
+    B, Cpp, H, W = x.shape
+    C = Cpp // (p * p)
+    y = x.reshape(B, C, p, p, H, W).transpose(0, 1, 4, 2, 5, 3)
+    return np.ascontiguousarray(y.reshape(B, C, H * p, W * p))
 
 
 # ----------------------------------------------------------------------------------------- layers

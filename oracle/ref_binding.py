@@ -96,6 +96,8 @@ class RefLib:
         L.flux_power_schedule.argtypes = [ci, cf]
         L.flux_init_noise.restype = vp
         L.flux_init_noise.argtypes = [ci, ci, ci, ci, ctypes.c_int64]
+        L.flux_patchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
+        L.flux_unpatchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
         L.flux_vae_load_safetensors.restype = vp
         L.flux_vae_load_safetensors.argtypes = [vp]
         L.flux_vae_free.argtypes = [vp]
@@ -129,6 +131,20 @@ class RefLib:
 
     def init_noise(self, channels, h, w, seed):
         return self._take(self.L.flux_init_noise(1, channels, h, w, seed), channels * h * w).reshape(channels, h, w)
+
+    def patchify(self, x, p=2):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        B, C, H, W = x.shape
+        out = np.empty((B, C * p * p, H // p, W // p), dtype=np.float32)
+        self.L.flux_patchify(_fp(out), _fp(x), B, C, H, W, p)
+        return out
+
+    def unpatchify(self, x, p=2):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        B, Cpp, H, W = x.shape
+        out = np.empty((B, Cpp // (p * p), H * p, W * p), dtype=np.float32)
+        self.L.flux_unpatchify(_fp(out), _fp(x), B, Cpp // (p * p), H, W, p)
+        return out
 
     def load_vae(self, safetensors_path):
         """flux_vae_load_safetensors (flux_vae.c:1232-1386)."""

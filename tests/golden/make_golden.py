@@ -114,6 +114,8 @@ def host_fixtures():
         out["noise_%d_%d_%d_sum" % (h, w, seed)] = np.float64(n.astype(np.float64).sum())
         out["noise_%d_%d_%d_abs" % (h, w, seed)] = np.float64(np.abs(n.astype(np.float64)).sum())
     np.savez_compressed(os.path.join(HERE, "reference_host.npz"), **out)
+    x = np.random.default_rng(0).standard_normal((2, 32, 12, 8)).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "reference_patchify.npz"), **{"in": x, "patchified": lib.patchify(x)})
 
 
 if __name__ == "__main__":

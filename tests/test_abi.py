@@ -43,3 +43,22 @@ def test_product_does_not_touch_the_oracle():
                     if re.search(r"\boracle[/.]|from oracle|import oracle|_ref/", src):
                         bad.append(os.path.join(dirpath, f))
     assert not bad, bad
+
+
+def test_seam_defines_every_symbol_of_the_objects_it_replaces():
+    """flux_cuda_seam.c stands in for the reference's flux_transformer.o and flux_sample.o: every function or global
+    those objects export must be defined by the seam, or the reference's other objects would not link."""
+    import subprocess
+    ref = os.path.join(ROOT, "oracle", "_ref")
+    seam = os.path.join(ref, "obj_seam", "flux_cuda_seam.o")
+    theirs = [os.path.join(ref, "obj_blas", f) for f in ("flux_transformer.o", "flux_sample.o")]
+    if not (os.path.exists(seam) and all(os.path.exists(t) for t in theirs)):
+        import pytest
+        pytest.skip("oracle/_ref objects not built (make -C oracle cli)")
+
+    def exported(path):
+        out = subprocess.run(["nm", "--defined-only", "-g", path], capture_output=True, text=True, check=True).stdout
+        return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+    missing = set().union(*[exported(t) for t in theirs]) - exported(seam)
+    assert not missing, sorted(missing)

@@ -70,3 +70,14 @@ def test_noise_is_size_independent(fx):
     sy = (np.arange(16) * 112) // 16
     sx = (np.arange(8) * 112) // 8
     assert np.array_equal(small, big[:, sy][:, :, sx])
+
+
+def test_patchify_oracle_matches_reference():
+    """2x2 space-to-depth between VAE latents and DiT latents (flux_patchify / flux_unpatchify): bit-exact."""
+    from oracle import flux_oracle as fo
+    path = os.path.join(os.path.dirname(GOLDEN), "reference_patchify.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_patchify.npz missing")
+    g = np.load(path)
+    assert np.array_equal(fo.patchify(g["in"]), g["patchified"])
+    assert np.array_equal(fo.unpatchify(g["patchified"]), g["in"])

@@ -117,3 +117,27 @@ def test_fused_qkv_projection_norm_rope(fx, ctx, M, heads, K, seq, dtype):
     assert _rel(out[:, :hid].float(), ref_one(y[:, :hid], wq)) < tol
     assert _rel(out[:, hid:2 * hid].float(), ref_one(y[:, hid:2 * hid], wk)) < tol
     assert _rel(out[:, 2 * hid:].float(), y[:, 2 * hid:]) < tol
+
+
+@pytest.mark.parametrize("B,C,H,W,p", [(2, 32, 12, 8, 2), (1, 32, 64, 64, 2), (1, 3, 9, 6, 3)])
+def test_patchify_round_trip_bit_exact(fx, ctx, B, C, H, W, p):
+    import numpy as np
+    import os
+    from oracle import flux_oracle as fo
+    x = torch.randn(B, C, H, W, device="cuda")
+    packed = torch.zeros(B, C * p * p, H // p, W // p, device="cuda")
+    back = torch.zeros_like(x)
+    torch.cuda.synchronize()
+    ctx.patchify(packed.data_ptr(), x.data_ptr(), B, C, H, W, p)
+    ctx.unpatchify(back.data_ptr(), packed.data_ptr(), B, C, H // p, W // p, p)
+    ctx.sync()
+    assert np.array_equal(packed.cpu().numpy(), fo.patchify(x.cpu().numpy(), p))
+    assert torch.equal(back, x)
+    gold = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_patchify.npz")
+    if (B, C, H, W, p) == (2, 32, 12, 8, 2) and os.path.exists(gold):
+        g = np.load(gold)
+        xin = torch.from_numpy(g["in"]).cuda()
+        torch.cuda.synchronize()
+        ctx.patchify(packed.data_ptr(), xin.data_ptr(), B, C, H, W, p)
+        ctx.sync()
+        assert np.array_equal(packed.cpu().numpy(), g["patchified"])
