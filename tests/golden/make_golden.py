@@ -1,5 +1,5 @@
 """Generates tests/golden/*.npz by running the REFERENCE implementation (compiled by oracle/Makefile into
-oracle/_ref/) on seeded synthetic inputs. Needs /root/reference-built oracle/_ref, ~40 GB of RAM and a few
+oracle/_ref/) on seeded synthetic inputs. Needs oracle/_ref built from the reference's sources, ~40 GB of RAM and a few
 minutes; the fixtures it writes are committed so that the tests need neither.
 
     python tests/golden/make_golden.py            # both weight sets
