@@ -67,6 +67,18 @@ def _declare(L):
     L.flux_cuda_qk_norm_rope.restype = c_int
     L.flux_cuda_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p, c_void_p, c_void_p]
+    L.flux_cuda_qwen3_create.restype = c_int
+    L.flux_cuda_qwen3_create.argtypes = [c_void_p, ctypes.POINTER(CQwenDims), c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_qwen3_load_dir.restype = c_int
+    L.flux_cuda_qwen3_load_dir.argtypes = [c_void_p, c_char_p, c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_qwen3_set_tensor.restype = c_int
+    L.flux_cuda_qwen3_set_tensor.argtypes = [c_void_p, c_char_p, c_void_p, c_int, ctypes.POINTER(c_ll), c_int]
+    L.flux_cuda_qwen3_finalize.restype = c_int
+    L.flux_cuda_qwen3_finalize.argtypes = [c_void_p]
+    L.flux_cuda_qwen3_free.restype = None
+    L.flux_cuda_qwen3_free.argtypes = [c_void_p]
+    L.flux_cuda_qwen3_forward.restype = c_int
+    L.flux_cuda_qwen3_forward.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, fp]
     L.flux_cuda_patchify.restype = c_int
     L.flux_cuda_patchify.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
     L.flux_cuda_unpatchify.restype = c_int
@@ -131,6 +143,11 @@ class CDims(ctypes.Structure):  # flux_cuda_dims
     _fields_ = [(n, ctypes.c_int) for n in ("hidden", "heads", "head_dim", "mlp", "n_double", "n_single", "text_dim",
                                             "latent_ch", "time_dim")] + [("rope_theta", ctypes.c_float),
                                                                          ("axis_dim", ctypes.c_int)]
+
+
+class CQwenDims(ctypes.Structure):  # flux_cuda_qwen3_dims
+    _fields_ = [(n, ctypes.c_int) for n in ("hidden", "heads", "kv_heads", "head_dim", "inter", "layers", "vocab")] + [
+        ("rope_theta", ctypes.c_float), ("out_layers", ctypes.c_int * 3)]
 
 
 class CRef(ctypes.Structure):  # flux_cuda_ref
@@ -341,6 +358,56 @@ class Model:
     def close(self):
         if self.handle:
             lib().flux_cuda_model_free(self.handle)
+            self.handle = ctypes.c_void_p()
+
+
+class TextEncoder:
+    """The Qwen3 text encoder on one GPU. Mirrors qwen3_model_load / qwen3_forward / qwen3_model_free."""
+
+    def __init__(self, ctx, handle, dims):
+        self.ctx, self.handle, self.dims = ctx, handle, dims
+
+    @staticmethod
+    def load_dir(ctx, model_dir, max_seq=512):
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_qwen3_load_dir(ctx.handle, model_dir.encode(), max_seq, ctypes.byref(h)))
+        return TextEncoder(ctx, h, None)
+
+    @staticmethod
+    def from_tensors(ctx, dims, tensors, max_seq=512):
+        cd = CQwenDims()
+        for name in ("hidden", "heads", "kv_heads", "head_dim", "inter", "layers", "vocab", "rope_theta"):
+            setattr(cd, name, getattr(dims, name))
+        for i in range(3):
+            cd.out_layers[i] = dims.out_layers[i]
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_qwen3_create(ctx.handle, ctypes.byref(cd), max_seq, ctypes.byref(h)))
+        np = _np()
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            shape = (ctypes.c_longlong * arr.ndim)(*arr.shape)
+            check(lib().flux_cuda_qwen3_set_tensor(h, name.encode(), arr.ctypes.data, _DTYPES[str(arr.dtype)], shape,
+                                                   arr.ndim))
+        check(lib().flux_cuda_qwen3_finalize(h))
+        return TextEncoder(ctx, h, dims)
+
+    def forward(self, ids, mask=None, hidden=None):
+        """ids, mask: int sequences of one length; returns f32 [seq, 3 * hidden]."""
+        np = _np()
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        ip = ctypes.POINTER(ctypes.c_int)
+        mp = None
+        if mask is not None:
+            mask = np.ascontiguousarray(mask, dtype=np.int32)
+            mp = mask.ctypes.data_as(ip)
+        hdim = hidden or (self.dims.hidden if self.dims is not None else 2560)
+        out = np.empty((len(ids), 3 * hdim), dtype=np.float32)
+        check(lib().flux_cuda_qwen3_forward(self.handle, ids.ctypes.data_as(ip), mp, len(ids), _fp(out)))
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().flux_cuda_qwen3_free(self.handle)
             self.handle = ctypes.c_void_p()
 
 

@@ -192,7 +192,9 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   sg.qk.cos_t = cos_t;
   sg.qk.sin_t = sin_t;
   sg.qk.seq = seq;
-  sg.qk.hidden = hidden;
+  sg.qk.q_cols = hidden;
+  sg.qk.k_cols = hidden;
+  sg.qk.half_split = 0;
   rc = gemm_launch(&P, 256, ctx->num_sms, ctx->stream);
   if (rc) {
     set_error("gemm_qkv_norm_rope: launch failed (rc %d)", rc);

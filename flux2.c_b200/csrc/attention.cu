@@ -389,6 +389,9 @@ int attn_make_params(AttnParams *p, const void *qkv, int batch, int seq, long lo
   p->out_col = out_col;
   p->scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
   p->f16 = f16 != 0;
+  p->kv_group = 1;
+  p->causal = 0;
+  p->key_mask = nullptr;
   p->err = err;
   return 0;
 }

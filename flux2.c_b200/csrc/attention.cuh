@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace fx {
 
@@ -14,6 +15,10 @@ struct alignas(64) AttnParams {
   int out_col;
   float scale_log2;        // log2(e) / sqrt(head_dim)
   int f16;                 // Q, K, V, P and the output are f16 instead of bf16
+  // Options used by the text encoder (attention2.cu only; all zero for the DiT):
+  int kv_group;            // query heads per K/V head (grouped-query attention); 0 or 1 = one K/V head per query head
+  int causal;              // key j is visible to query i only if j <= i
+  const uint32_t *key_mask;  // [batch, ceil(seq/32)] bit j%32 of word j/32 set = key j is valid; NULL = all valid
   int *err;
 };
 

@@ -92,7 +92,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
   const int q0 = blockIdx.x * (QTILES * TILE);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int T = (P.seq + TILE - 1) / TILE;  // key tiles
+  int T = (P.seq + TILE - 1) / TILE;  // key tiles
+  if (P.causal) {  // no key beyond the last query of this CTA is visible
+    const int t_causal = (q0 + QTILES * TILE + TILE - 1) / TILE;
+    if (t_causal < T) T = t_causal;
+  }
+  const int kv_head = P.kv_group > 1 ? head / P.kv_group : head;
 
   if (threadIdx.x == 0) {
     mbar_init(&B->q_full, 1);
@@ -139,11 +144,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
         uint8_t *sk = smem + OFF_KV + s * 65536;
         uint8_t *sv = sk + 32768;
         mbar_arrive_expect_tx(&B->k_full[s], 2 * CHUNK_BYTES);
-        tma_load_3d(sk, &P.tm, &B->k_full[s], P.k_col + head * 128, j * TILE, batch);
-        tma_load_3d(sk + CHUNK_BYTES, &P.tm, &B->k_full[s], P.k_col + head * 128 + 64, j * TILE, batch);
+        tma_load_3d(sk, &P.tm, &B->k_full[s], P.k_col + kv_head * 128, j * TILE, batch);
+        tma_load_3d(sk + CHUNK_BYTES, &P.tm, &B->k_full[s], P.k_col + kv_head * 128 + 64, j * TILE, batch);
         mbar_arrive_expect_tx(&B->v_full[s], 2 * CHUNK_BYTES);
-        tma_load_3d(sv, &P.tm, &B->v_full[s], P.v_col + head * 128, j * TILE, batch);
-        tma_load_3d(sv + CHUNK_BYTES, &P.tm, &B->v_full[s], P.v_col + head * 128 + 64, j * TILE, batch);
+        tma_load_3d(sv, &P.tm, &B->v_full[s], P.v_col + kv_head * 128, j * TILE, batch);
+        tma_load_3d(sv + CHUNK_BYTES, &P.tm, &B->v_full[s], P.v_col + kv_head * 128 + 64, j * TILE, batch);
       }
     }
     __syncwarp();
@@ -226,13 +231,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_32x32(s_addr + c * 32, s[c]);
       tc_wait_ld();
-      const int valid = P.seq - j * TILE;
-      if (valid < TILE) {
+      // keys of this tile this row may see: inside the sequence, not after the query (causal), not masked out
+      int limit = P.seq - j * TILE;
+      if (P.causal) {
+        const int lim_c = q0 + t * TILE + row - j * TILE + 1;
+        if (lim_c < limit) limit = lim_c;
+      }
+      if (limit < TILE || P.key_mask) {
+        uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        if (P.key_mask) {
+          const int words = (P.seq + 31) / 32;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (j * 4 + c < words) mw[c] = __ldg(P.key_mask + static_cast<size_t>(batch) * words + j * 4 + c);
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-1e30f);
+            if (c * 32 + i >= limit || !((mw[c] >> i) & 1u)) s[c][i] = __float_as_uint(-1e30f);
       }
       float mloc = -1e30f;
 #pragma unroll
@@ -371,6 +388,9 @@ int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long l
   p->out_col = out_col;
   p->scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
   p->f16 = f16 != 0;
+  p->kv_group = 1;
+  p->causal = 0;
+  p->key_mask = nullptr;
   p->err = err;
   return 0;
 }

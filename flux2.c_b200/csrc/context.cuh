@@ -21,4 +21,11 @@ void set_error(const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 // Synchronises the context's stream and returns FLUX_CUDA_ERR_KERNEL if a kernel recorded an error.
 int ctx_sync_check(flux_cuda_ctx *ctx);
+// Host-to-device copy ordered on the context's (non-blocking) stream, complete on return. A plain cudaMemcpy from
+// pageable memory may return while the DMA is still in flight and is not ordered against a non-blocking stream,
+// so work queued on that stream right after it could read the old contents.
+inline cudaError_t upload_h2d(cudaStream_t st, void *dst, const void *src, size_t bytes) {
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st);
+  return e != cudaSuccess ? e : cudaStreamSynchronize(st);
+}
 }  // namespace fx

@@ -177,8 +177,11 @@ void model_free(flux_cuda_model *m) {
 // Converts `count` elements of the source dtype (0 = F32, 1 = F16, 2 = BF16) to the model's 16-bit weight format
 // on the host. bf16 -> f16 is exact for 6.1e-5 <= |w| <= 65504 (bf16 has fewer mantissa bits); smaller weights
 // land on f16 subnormals with an absolute error below 3e-8.
-static const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp,
-                                    bool want_f16) {
+float half_to_f32_host(uint16_t bits, int dtype) {
+  return dtype == 1 ? f16_to_f32_host(bits) : bf16_to_f32_host(bits);
+}
+
+const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp, bool want_f16) {
   if ((dtype == 2 && !want_f16) || (dtype == 1 && want_f16)) return reinterpret_cast<const uint16_t *>(data);
   tmp.resize(count);
   const float *f = reinterpret_cast<const float *>(data);
@@ -194,7 +197,7 @@ static const uint16_t *to_half_host(const void *data, int dtype, size_t count, s
 static int upload_interleaved(flux_cuda_model *m, bf16 *dst, const uint16_t *src, size_t half_rows, size_t cols) {
   const size_t bytes = 2 * half_rows * cols * 2;
   if (bytes > m->staging_bytes) return FLUX_CUDA_ERR_ARG;
-  int rc = check_cuda(cudaMemcpy(m->staging, src, bytes, cudaMemcpyHostToDevice), "upload weights");
+  int rc = check_cuda(upload_h2d(m->ctx->stream, m->staging, src, bytes), "upload weights");
   if (rc) return rc;
   const char *st = reinterpret_cast<const char *>(m->staging);
   const size_t blk = 128 * cols * 2;
@@ -231,7 +234,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
     int rc = want(er, ec);
     if (rc) return rc;
     const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
-    return check_cuda(cudaMemcpy(dst, src, count * 2, cudaMemcpyHostToDevice), "upload weights");
+    return check_cuda(upload_h2d(m->ctx->stream, dst, src, count * 2), "upload weights");
   };
   auto vec_f32 = [&](float *dst) -> int {
     if (ndim != 1 || r != 128) {
@@ -244,7 +247,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
       else if (dtype == 1) v[i] = f16_to_f32_host(reinterpret_cast<const uint16_t *>(data)[i]);
       else v[i] = bf16_to_f32_host(reinterpret_cast<const uint16_t *>(data)[i]);
     }
-    return check_cuda(cudaMemcpy(dst, v, sizeof(v), cudaMemcpyHostToDevice), "upload norm weights");
+    return check_cuda(upload_h2d(m->ctx->stream, dst, v, sizeof(v)), "upload norm weights");
   };
 
   int rc = FLUX_CUDA_ERR_MODEL;
@@ -294,7 +297,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
       // rows [Q | K | V | gate | up] (flux_transformer.c:3051-3058): Q, K, V stay; gate/up are interleaved
       if (!(rc = want(3 * h + 2 * mlp, h))) {
         const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
-        rc = check_cuda(cudaMemcpy(b.lin1, src, 3 * h * h * 2, cudaMemcpyHostToDevice), "upload weights");
+        rc = check_cuda(upload_h2d(m->ctx->stream, b.lin1, src, 3 * h * h * 2), "upload weights");
         if (!rc) rc = upload_interleaved(m, b.lin1 + 3 * h * h, src + 3 * h * h, mlp, h);
       }
     } else {
@@ -437,8 +440,8 @@ int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec 
     cudaMemsetAsync(ws->svec, 0, S * hid * 4, m->ctx->stream);
     std::vector<float> cs, sn;
     build_rope(d, *ws, cs, sn);
-    rc = check_cuda(cudaMemcpy(ws->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice), "upload rope");
-    if (!rc) rc = check_cuda(cudaMemcpy(ws->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice), "upload rope");
+    rc = check_cuda(upload_h2d(m->ctx->stream, ws->rope_cos, cs.data(), cs.size() * 4), "upload rope");
+    if (!rc) rc = check_cuda(upload_h2d(m->ctx->stream, ws->rope_sin, sn.data(), sn.size() * 4), "upload rope");
   }
   if (rc) {
     sampler_free(s);
@@ -540,7 +543,9 @@ struct Launcher {
     s.qk.pos0 = pos0;
     s.qk.seq = ws->N;
     s.qk.n_txt = ws->n_txt;
-    s.qk.hidden = m->d.hidden;
+    s.qk.q_cols = m->d.hidden;
+    s.qk.k_cols = m->d.hidden;
+    s.qk.half_split = 0;
     return s;
   }
   EpiSeg seg(int mode, void *out, long long ld, int col0, const float *gate = nullptr) {

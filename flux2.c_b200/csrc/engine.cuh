@@ -11,7 +11,9 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
 
+#include <functional>
 #include <set>
 #include <string>
 #include <vector>
@@ -104,6 +106,12 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
 int model_finalize(flux_cuda_model *m);
 void model_free(flux_cuda_model *m);
 int model_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_model **out);
+int safetensors_for_each(const char *path,
+                         const std::function<int(const char *, const void *, int, const long long *, int)> &visit);
+// Host-side conversion of `count` elements (dtype 0/1/2 = F32/F16/BF16) to 16-bit words in the wanted format;
+// returns `data` itself when no conversion is needed, else a pointer into `tmp`.
+const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp, bool want_f16);
+float half_to_f32_host(uint16_t bits, int dtype);
 
 int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec *refs, int num_refs, int batch,
                    int max_steps, flux_cuda_sampler **out);

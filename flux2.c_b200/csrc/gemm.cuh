@@ -20,13 +20,15 @@ enum EpiMode : int {
                           // (apply_qk_norm + apply_rope_2d, flux_transformer.c:1052-1106, 719-741), V stored as is; bf16
 };
 
-// Extra operands of EPI_QKV_NORM_ROPE. Segment-relative column c: c < hidden is Q, c < 2*hidden is K, else V.
-// Row r of the problem sits at sequence position (pos0 + r) % seq; positions below n_txt use the text stream's
-// norm weights. cos/sin: f32 [seq, 128], one value per element (pairs share a value).
+// Extra operands of EPI_QKV_NORM_ROPE. Segment-relative column c: c < q_cols is Q, c < q_cols + k_cols is K, else
+// V (heads of 128 columns). Row r of the problem sits at sequence position (pos0 + r) % seq; positions below n_txt
+// use the text stream's norm weights. Two rotation conventions:
+//   half_split = 0 (DiT): consecutive pairs (2j, 2j+1), cos/sin f32 [seq, 128] with one value per element;
+//   half_split = 1 (Qwen3 encoder, flux_qwen3.c:264-307): pairs (i, i + 64), cos/sin f32 [seq, 64].
 struct QkvNormRope {
   const float *wq_txt, *wk_txt, *wq_img, *wk_img;
   const float *cos_t, *sin_t;
-  int pos0, seq, n_txt, hidden;
+  int pos0, seq, n_txt, q_cols, k_cols, half_split;
 };
 
 struct EpiSeg {

@@ -125,7 +125,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         const int col = nrel + hd * 128;  // first column of this head inside the [Q|K|V] segment
         const uint32_t th = taddr + hd * 128;
         float rinv = 1.f;
-        const bool rotate = col < 2 * qk.hidden;
+        const bool rotate = col < qk.q_cols + qk.k_cols;
         const float *w = nullptr;
         if (rotate) {
           float ss = 0.f;
@@ -137,8 +137,47 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
             for (int j = 0; j < 32; ++j) ss = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), ss);
           }
           rinv = rsqrtf(ss * (1.0f / 128.0f) + 1e-6f);
-          const bool is_k = col >= qk.hidden;
+          const bool is_k = col >= qk.q_cols;
           w = (pos < qk.n_txt) ? (is_k ? qk.wk_txt : qk.wq_txt) : (is_k ? qk.wk_img : qk.wq_img);
+        }
+        if (rotate && qk.half_split) {
+          // pairs (i, i + 64): chunk c of the first half rotates with chunk c of the second half
+          uint32_t u[32];
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            tc_ld_32x32(th + c * 32, r);
+            tc_ld_32x32(th + 64 + c * 32, u);
+            tc_wait_ld();
+            if (row_ok) {
+              const float *wa = w + c * 32, *wb = w + 64 + c * 32;
+              const float *cs = qk.cos_t + static_cast<size_t>(pos) * 64 + c * 32;
+              const float *sn = qk.sin_t + static_cast<size_t>(pos) * 64 + c * 32;
+              uint4 *da = reinterpret_cast<uint4 *>(dst + hd * 128 + c * 32);
+              uint4 *db = reinterpret_cast<uint4 *>(dst + hd * 128 + 64 + c * 32);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t oa[4], ob[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float ya[2], yb[2];
+#pragma unroll
+                  for (int k = 0; k < 2; ++k) {
+                    const int i = 8 * j + 2 * e + k;
+                    const float x0 = __uint_as_float(r[i]) * rinv * __ldg(wa + i);
+                    const float x1 = __uint_as_float(u[i]) * rinv * __ldg(wb + i);
+                    const float cc = __ldg(cs + i), ss = __ldg(sn + i);
+                    ya[k] = x0 * cc - x1 * ss;
+                    yb[k] = x0 * ss + x1 * cc;
+                  }
+                  oa[e] = pack_16x2(ya[0], ya[1], f16);
+                  ob[e] = pack_16x2(yb[0], yb[1], f16);
+                }
+                da[j] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+                db[j] = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+              }
+            }
+          }
+          continue;
         }
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {

@@ -11,6 +11,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <functional>
 #include <string>
 #include <vector>
 
@@ -176,6 +177,61 @@ static int infer_dims(const std::vector<StEntry> &es, ModelDims &d) {
   if (!d.hidden || !d.latent_ch || !d.text_dim || !d.time_dim || !d.mlp) return -1;
   d.heads = d.hidden / d.head_dim;
   return 0;
+}
+
+// Maps `path`, parses its header and calls visit(name, data, dtype 0/1/2 = F32/F16/BF16, shape, ndim) for every
+// tensor; stops at the first non-zero return. Tensors of other dtypes or ranks are reported as errors.
+int safetensors_for_each(const char *path,
+                         const std::function<int(const char *, const void *, int, const long long *, int)> &visit) {
+  int fd = open(path, O_RDONLY);
+  if (fd < 0) {
+    set_error("cannot open %s", path);
+    return FLUX_CUDA_ERR_IO;
+  }
+  struct stat sb;
+  if (fstat(fd, &sb) != 0 || sb.st_size < 10) {
+    close(fd);
+    set_error("%s: too short to be a safetensors file", path);
+    return FLUX_CUDA_ERR_IO;
+  }
+  const size_t fsize = static_cast<size_t>(sb.st_size);
+  void *map = mmap(nullptr, fsize, PROT_READ, MAP_PRIVATE, fd, 0);
+  close(fd);
+  if (map == MAP_FAILED) {
+    set_error("%s: mmap failed", path);
+    return FLUX_CUDA_ERR_IO;
+  }
+  const unsigned char *base = reinterpret_cast<const unsigned char *>(map);
+  unsigned long long hlen = 0;
+  for (int i = 7; i >= 0; --i) hlen = (hlen << 8) | base[i];
+  int rc = 0;
+  std::vector<StEntry> es;
+  if (hlen == 0 || hlen > fsize - 8 || hlen > (100ull << 20)) {
+    set_error("%s: implausible header length %llu", path, hlen);
+    rc = FLUX_CUDA_ERR_IO;
+  } else if (!parse_header(reinterpret_cast<const char *>(base + 8), hlen, es)) {
+    set_error("%s: malformed header", path);
+    rc = FLUX_CUDA_ERR_IO;
+  }
+  const size_t data0 = 8 + hlen;
+  for (size_t i = 0; !rc && i < es.size(); ++i) {
+    const StEntry &e = es[i];
+    const int dt = e.dtype == "F32" ? 0 : e.dtype == "F16" ? 1 : e.dtype == "BF16" ? 2 : -1;
+    size_t count = 1;
+    for (long long d : e.shape) count *= static_cast<size_t>(d);
+    const size_t esz = dt == 0 ? 4 : 2;
+    if (dt < 0 || e.shape.empty() || e.shape.size() > 2) {
+      set_error("%s: tensor %s has unsupported dtype/rank", path, e.name.c_str());
+      rc = FLUX_CUDA_ERR_MODEL;
+    } else if (e.end < e.begin || e.end - e.begin != count * esz || data0 + e.end > fsize) {
+      set_error("%s: tensor %s has inconsistent offsets (file truncated?)", path, e.name.c_str());
+      rc = FLUX_CUDA_ERR_IO;
+    } else {
+      rc = visit(e.name.c_str(), base + data0 + e.begin, dt, e.shape.data(), static_cast<int>(e.shape.size()));
+    }
+  }
+  munmap(map, fsize);
+  return rc;
 }
 
 int model_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_model **out) {

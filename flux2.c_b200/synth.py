@@ -209,6 +209,83 @@ def make_vae_weights(seed=0, std=0.02):
     return out
 
 
+@dataclass(frozen=True)
+class QwenDims:
+    """Qwen3 text encoder shape (flux_qwen3.h:21-40)."""
+    hidden: int = 2560
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    inter: int = 9728
+    layers: int = 36
+    vocab: int = 151936
+    rope_theta: float = 1000000.0
+    out_layers: tuple = (8, 17, 26)  # hidden states after these layers are concatenated
+
+    @staticmethod
+    def qwen3_4b():
+        return QwenDims()
+
+    @staticmethod
+    def tiny():
+        return QwenDims(hidden=256, heads=4, kv_heads=2, head_dim=128, inter=512, layers=4, vocab=1000,
+                        out_layers=(0, 1, 3))
+
+
+def qwen_tensor_specs(d: QwenDims):
+    """Ordered (name, shape, kind) of the text encoder's tensors (flux_qwen3.c:1216-1251, 1360, 1375)."""
+    specs = [("model.embed_tokens.weight", (d.vocab, d.hidden), "w"), ("model.norm.weight", (d.hidden,), "norm")]
+    for l in range(d.layers):
+        p = "model.layers.%d." % l
+        specs += [
+            (p + "input_layernorm.weight", (d.hidden,), "norm"),
+            (p + "post_attention_layernorm.weight", (d.hidden,), "norm"),
+            (p + "self_attn.q_proj.weight", (d.heads * d.head_dim, d.hidden), "w"),
+            (p + "self_attn.k_proj.weight", (d.kv_heads * d.head_dim, d.hidden), "w"),
+            (p + "self_attn.v_proj.weight", (d.kv_heads * d.head_dim, d.hidden), "w"),
+            (p + "self_attn.o_proj.weight", (d.hidden, d.heads * d.head_dim), "w"),
+            (p + "self_attn.q_norm.weight", (d.head_dim,), "norm"),
+            (p + "self_attn.k_norm.weight", (d.head_dim,), "norm"),
+            (p + "mlp.gate_proj.weight", (d.inter, d.hidden), "w"),
+            (p + "mlp.up_proj.weight", (d.inter, d.hidden), "w"),
+            (p + "mlp.down_proj.weight", (d.hidden, d.inter), "w"),
+        ]
+    return specs
+
+
+def make_qwen_weights(d: QwenDims, seed=0, std=0.02, sharp=True, threads=None, max_layer=None):
+    """dict name -> uint16 bf16 bits. Linear / embedding weights N(0, std^2). With sharp=True the RMSNorm and
+    per-head q/k norm vectors are 1 + N(0, 0.1^2) (a plain N(0, 0.02) init would scale every normalised activation
+    by ~0.02 and make attention uniform, hiding RoPE / mask / GQA mistakes); sharp=False draws them like the rest."""
+    specs = qwen_tensor_specs(d)
+
+    def wanted(name):  # max_layer: only the embedding and layers 0..max_layer (same values as in the full set)
+        if max_layer is None or not name.startswith("model.layers."):
+            return True
+        return int(name.split(".")[2]) <= max_layer
+
+    def job(arg):
+        idx, (name, shape, kind) = arg
+        if kind == "norm" and sharp:
+            rng = np.random.Generator(np.random.Philox(key=[np.uint64(seed), np.uint64(0x51000000 + idx)]))
+            return name, f32_to_bf16_bits(1.0 + 0.1 * rng.standard_normal(shape, dtype=np.float32))
+        return name, _gen_tensor(seed, 0x51000000 + idx, shape, std if kind == "w" else std)
+
+    with ThreadPoolExecutor(max_workers=threads or 8) as ex:
+        return dict(ex.map(job, [(i, sp) for i, sp in enumerate(specs) if wanted(sp[0])]))
+
+
+def write_qwen_shards(model_dir, tensors):
+    """The two-file layout the reference loader insists on (flux_qwen3.c:1341-1356): both files must exist; a tensor
+    may live in either."""
+    import os
+    os.makedirs(model_dir, exist_ok=True)
+    names = list(tensors)
+    half = len(names) // 2
+    write_safetensors(os.path.join(model_dir, "model-00001-of-00002.safetensors"), {n: tensors[n] for n in names[:half]})
+    write_safetensors(os.path.join(model_dir, "model-00002-of-00002.safetensors"), {n: tensors[n] for n in names[half:]})
+
+
 def write_safetensors(path, tensors, dtype="BF16"):
     """Writes name -> array (uint16 bf16 bits for BF16, float32 for F32) in safetensors layout:
     8-byte little-endian header length, JSON header, raw little-endian data (flux_safetensors.c:155-292)."""

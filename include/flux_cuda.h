@@ -187,6 +187,32 @@ void flux_cuda_power_schedule(int num_steps, float alpha, float *out);
 void flux_cuda_init_noise(int channels, int h, int w, long long seed, float *out);
 
 /* ------------------------------------------------------------------------------------------------
+ * Text encoder (Qwen3): the stage right before the denoising loop. Replaces qwen3_model_load / qwen3_forward /
+ * qwen3_model_free (flux_qwen3.c:1329-1430, 1041-1156, 1529-1590): same tensor names, same output.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_qwen3 flux_cuda_qwen3;
+
+typedef struct flux_cuda_qwen3_dims {
+  int hidden, heads, kv_heads, head_dim, inter, layers, vocab;
+  float rope_theta;
+  int out_layers[3]; /* hidden states after these layers (0-based) are concatenated */
+} flux_cuda_qwen3_dims;
+
+/* The Qwen3-4B shape the reference hard-codes (flux_qwen3.h:21-40): outputs after layers 8, 17, 26. */
+void flux_cuda_qwen3_dims_4b(flux_cuda_qwen3_dims *d);
+/* Loads `text_encoder/` (both model-0000{1,2}-of-00002.safetensors must exist, flux_qwen3.c:1341-1356). Only the
+ * layers the output depends on are kept on the device. max_seq: largest token count of a later forward. */
+int flux_cuda_qwen3_load_dir(flux_cuda_ctx *ctx, const char *model_dir, int max_seq, flux_cuda_qwen3 **out);
+int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims, int max_seq, flux_cuda_qwen3 **out);
+int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void *data, int dtype,
+                               const long long *shape, int ndim);
+int flux_cuda_qwen3_finalize(flux_cuda_qwen3 *m);
+void flux_cuda_qwen3_free(flux_cuda_qwen3 *m);
+/* input_ids, attention_mask (may be NULL = all ones): host int[seq]; out: host f32 [seq, 3 * hidden]. Causal,
+ * grouped-query attention with the key padding mask, as the reference's CPU path (flux_qwen3.c:313-452). */
+int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, float *out);
+
+/* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points on DEVICE pointers (unit tests, microbenchmarks). Asynchronous on the
  * context's stream.
  * ---------------------------------------------------------------------------------------------- */

@@ -13,6 +13,7 @@ numpy, what the reference computes on its CPU path:
   * flux_sample_euler*, flux_sample_euler_cfg*                 flux_sample.c:212-290, 303-444, 457-691
   * flux_rng_seed / flux_randn / flux_init_noise               flux_kernels.c:45-102, flux_sample.c:835-877
   * flux_patchify / flux_unpatchify                            flux_kernels.c:1038-1094
+  * qwen3_forward and its layers (text encoder)                flux_qwen3.c:176-517, 1041-1156
 
 Parity is PINNED: tests/golden/ holds outputs of the reference itself (compiled from its own
 sources by oracle/Makefile and run through oracle/ref_binding.py by tests/golden/make_golden.py),
@@ -235,6 +236,84 @@ def attention(q, k, v):
         p /= p.sum(axis=1, keepdims=True, dtype=np.float32)
         out[:, hh, :] = p @ v[:, hh, :]
     return out.reshape(nq, H * d)
+
+
+# ----------------------------------------------------------------------------------------- Qwen3 text encoder
+class QwenOracle:
+    """numpy f32 restatement of the reference's Qwen3 encoder forward on its CPU path: qwen3_forward
+    (flux_qwen3.c:1041-1156), qwen3_layer_forward (484-517), qwen3_attention_forward (313-452: GQA, causal + key
+    padding mask with -1e9, softmax), qwen3_mlp_forward (458-478), qwen3_rms_norm / qwen3_head_rms_norm (176-221),
+    half-split RoPE with theta 1e6 (253-307). Output: hidden states after the layers in dims.out_layers
+    concatenated, [seq, 3 * hidden]. Like the reference's CPU path it can run all layers; the output only depends on
+    the first max(out_layers) + 1."""
+
+    def __init__(self, tensors, dims):
+        self.t, self.d, self.cache = tensors, dims, {}
+
+    def W(self, name):
+        if name not in self.cache:
+            a = self.t[name]
+            self.cache[name] = bf16_bits_to_f32(a) if a.dtype == np.uint16 else np.asarray(a, dtype=np.float32)
+        return self.cache[name]
+
+    @staticmethod
+    def rms(x, w, eps=F(1e-6)):
+        ms = (x * x).mean(axis=-1, keepdims=True, dtype=np.float32)
+        return (x * (F(1.0) / np.sqrt(ms + eps, dtype=np.float32)) * w).astype(np.float32)
+
+    def forward(self, ids, mask=None, num_layers=None):
+        d = self.d
+        seq = len(ids)
+        H, KV, hd = d.heads, d.kv_heads, d.head_dim
+        emb = self.W("model.embed_tokens.weight")
+        x = np.zeros((seq, d.hidden), dtype=np.float32)
+        for s_, tok in enumerate(ids):
+            if 0 <= tok < d.vocab:
+                x[s_] = emb[tok]
+        half = hd // 2
+        i = np.arange(half, dtype=np.float32)
+        freq = (F(1.0) / np.power(F(d.rope_theta), (F(2.0) * i) / F(hd), dtype=np.float32)).astype(np.float32)
+        ang = np.arange(seq, dtype=np.float32)[:, None] * freq[None, :]
+        cos, sin = np.cos(ang, dtype=np.float32), np.sin(ang, dtype=np.float32)
+
+        def rope(t):  # t [seq, heads, hd], pairs (i, i + half)
+            a, b = t[..., :half], t[..., half:]
+            c, s = cos[:, None, :], sin[:, None, :]
+            return np.concatenate([a * c - b * s, a * s + b * c], axis=-1)
+
+        bias = np.zeros((seq, seq), dtype=np.float32)
+        bias[np.triu_indices(seq, 1)] = 1.0
+        if mask is not None:
+            bias[:, np.asarray(mask) == 0] = 1.0
+        masked = bias > 0
+        scale = F(1.0 / np.sqrt(float(hd)))
+        outs = []
+        last = max(d.out_layers) + 1 if num_layers is None else num_layers
+        for l in range(last):
+            p = "model.layers.%d." % l
+            n = self.rms(x, self.W(p + "input_layernorm.weight"))
+            q = (n @ self.W(p + "self_attn.q_proj.weight").T).reshape(seq, H, hd)
+            k = (n @ self.W(p + "self_attn.k_proj.weight").T).reshape(seq, KV, hd)
+            v = (n @ self.W(p + "self_attn.v_proj.weight").T).reshape(seq, KV, hd)
+            q = rope(self.rms(q, self.W(p + "self_attn.q_norm.weight")))
+            k = rope(self.rms(k, self.W(p + "self_attn.k_norm.weight")))
+            att = np.empty((seq, H, hd), dtype=np.float32)
+            for h in range(H):
+                g = h // (H // KV)
+                sc = (q[:, h, :] @ k[:, g, :].T) * scale
+                sc[masked] = F(-1e9)
+                sc -= sc.max(axis=1, keepdims=True)
+                pr = np.exp(sc, dtype=np.float32)
+                pr /= pr.sum(axis=1, keepdims=True, dtype=np.float32)
+                att[:, h, :] = pr @ v[:, g, :]
+            x = x + att.reshape(seq, H * hd) @ self.W(p + "self_attn.o_proj.weight").T
+            n = self.rms(x, self.W(p + "post_attention_layernorm.weight"))
+            gate = n @ self.W(p + "mlp.gate_proj.weight").T
+            up = n @ self.W(p + "mlp.up_proj.weight").T
+            x = (x + (silu(gate) * up) @ self.W(p + "mlp.down_proj.weight").T).astype(np.float32)
+            if l in d.out_layers:
+                outs.append(x.copy())
+        return np.concatenate(outs, axis=1).astype(np.float32)
 
 
 class OracleModel:

@@ -98,6 +98,11 @@ class RefLib:
         L.flux_init_noise.argtypes = [ci, ci, ci, ci, ctypes.c_int64]
         L.flux_patchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
         L.flux_unpatchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
+        L.qwen3_model_load.restype = vp
+        L.qwen3_model_load.argtypes = [ctypes.c_char_p]
+        L.qwen3_model_free.argtypes = [vp]
+        L.qwen3_forward.restype = vp
+        L.qwen3_forward.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ci]
         L.flux_vae_load_safetensors.restype = vp
         L.flux_vae_load_safetensors.argtypes = [vp]
         L.flux_vae_free.argtypes = [vp]
@@ -145,6 +150,21 @@ class RefLib:
         out = np.empty((B, Cpp // (p * p), H * p, W * p), dtype=np.float32)
         self.L.flux_unpatchify(_fp(out), _fp(x), B, Cpp // (p * p), H, W, p)
         return out
+
+    def qwen3_load(self, model_dir):
+        """qwen3_model_load (flux_qwen3.c:1329): directory with the two text-encoder shards."""
+        m = self.L.qwen3_model_load(model_dir.encode())
+        if not m:
+            raise RuntimeError("reference could not load the text encoder from %s" % model_dir)
+        return m
+
+    def qwen3_forward(self, model, ids, mask):
+        """qwen3_forward (flux_qwen3.c:1041): f32 [seq, 7680]."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        mask = np.ascontiguousarray(mask, dtype=np.int32)
+        ip = ctypes.POINTER(ctypes.c_int)
+        p = self.L.qwen3_forward(model, ids.ctypes.data_as(ip), mask.ctypes.data_as(ip), len(ids))
+        return self._take(p, len(ids) * 7680).reshape(len(ids), 7680)
 
     def load_vae(self, safetensors_path):
         """flux_vae_load_safetensors (flux_vae.c:1232-1386)."""

@@ -100,5 +100,37 @@ def guided_512():
     np.savez_compressed(os.path.join(HERE, "reference_guided512.npz"), **out)
 
 
+def qwen3():
+    """Text encoder at the Qwen3-4B shape: 64 tokens (40 valid, 24 padded) through the reference's qwen3_forward;
+    every 4th output column is stored."""
+    import shutil
+    import tempfile
+    lib = rb.RefLib(rb.best_kind())
+    d = synth.QwenDims.qwen3_4b()
+    W = synth.make_qwen_weights(d, seed=0)
+    chk = float(np.abs(synth.bf16_bits_to_f32(W["model.layers.0.self_attn.q_norm.weight"]).astype(np.float64)).sum() +
+                np.abs(synth.bf16_bits_to_f32(W["model.layers.26.mlp.down_proj.weight"][:64]).astype(np.float64)).sum())
+    mdir = tempfile.mkdtemp(prefix="qwen_synth_", dir="/tmp")
+    try:
+        synth.write_qwen_shards(mdir, W)
+        del W
+        m = lib.qwen3_load(mdir)
+    finally:
+        shutil.rmtree(mdir, ignore_errors=True)
+    ids = np.random.default_rng(64).integers(0, d.vocab, 64).astype(np.int32)
+    mask = np.array([1] * 40 + [0] * 24, dtype=np.int32)
+    out = lib.qwen3_forward(m, ids, mask)
+    lib.L.qwen3_model_free(m)
+    np.savez_compressed(os.path.join(HERE, "reference_qwen3.npz"), ids=ids, mask=mask, out_sub=out[:, ::4].copy(),
+                        out_rms=np.float64(np.sqrt((out.astype(np.float64) ** 2).mean())), weights_checksum=chk,
+                        ref_build=lib.kind)
+    print("qwen3 golden written, rms", float(np.sqrt((out.astype(np.float64) ** 2).mean())))
+
+
 if __name__ == "__main__":
-    guided_512() if sys.argv[1:] == ["guided512"] else main()
+    if sys.argv[1:] == ["guided512"]:
+        guided_512()
+    elif sys.argv[1:] == ["qwen3"]:
+        qwen3()
+    else:
+        main()

@@ -85,3 +85,43 @@ def test_tiny_oracle_structure():
     z1 = z + np.float32(-0.5) * rec[0][1]
     assert np.allclose(rec[1][0], z1)
     assert np.allclose(zf, z1 + np.float32(-0.5) * rec[1][1])
+
+
+def test_qwen_oracle_matches_reference(fx):
+    """Text-encoder restatement against the reference's qwen3_forward at the Qwen3-4B shape. Only the first output
+    block (hidden state after layer 8 = output columns 0..2559) is recomputed here, which needs the embedding and
+    nine layers of the seeded weights; the GPU test checks all three blocks."""
+    import flux2_c_b200.synth as synth
+    from oracle import flux_oracle as fo
+    path = os.path.join(GOLDEN, "reference_qwen3.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_qwen3.npz missing")
+    g = np.load(path)
+    d = synth.QwenDims.qwen3_4b()
+    W = synth.make_qwen_weights(d, seed=0, max_layer=8)
+    out = fo.QwenOracle(W, d).forward(g["ids"], g["mask"], num_layers=9)
+    assert out.shape == (64, 2560)
+    assert rel(out[:, ::4], g["out_sub"][:, :640]) < TOL
+
+
+def test_qwen_oracle_structure():
+    import sys
+    sys.path.insert(0, os.path.dirname(GOLDEN))
+    from conftest import load_package
+    load_package()
+    import importlib
+    synth = importlib.import_module("flux2_c_b200.synth")
+    from oracle import flux_oracle as fo
+    d = synth.QwenDims.tiny()
+    o = fo.QwenOracle(synth.make_qwen_weights(d, seed=1, std=0.05), d)
+    ids = np.random.default_rng(0).integers(0, d.vocab, 40)
+    full = o.forward(ids, None)
+    assert full.shape == (40, 3 * d.hidden)
+    # causal: a row does not depend on later tokens
+    ids2 = ids.copy()
+    ids2[30] = (ids2[30] + 1) % d.vocab
+    out2 = o.forward(ids2, None)
+    assert np.allclose(out2[:30], full[:30], atol=1e-5) and rel(out2[30:], full[30:]) > 1e-3
+    # key padding mask: masking the tail changes nothing for rows before it
+    m = np.array([1] * 25 + [0] * 15)
+    assert np.allclose(o.forward(ids, m)[:25], full[:25], atol=1e-5)
