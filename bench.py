@@ -2,7 +2,7 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|attn|adaln|qwen3 [...]            # one kernel, small memory (for ncu captures)
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
 (1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
@@ -231,6 +231,33 @@ def run_micro(args):
         gbs = rows * hid * 6.0 / ms / 1e6
         print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
                           gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    elif args.micro == "qwen3":
+        # The text encoder at the Qwen3-4B shape (only the 27 layers the output depends on are built), one prompt
+        # of --seq tokens through the host-buffer entry point: token ids in, [seq, 7680] f32 embeddings out.
+        import numpy as np
+        synth = importlib.import_module("flux2_c_b200.synth")
+        d = synth.QwenDims(layers=27)
+        W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count())
+        enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=max(512, args.seq))
+        del W
+        seq = args.seq
+        ids = np.random.default_rng(0).integers(0, d.vocab, seq)
+        for _ in range(max(3, args.warmup)):
+            out = enc.forward(ids, None)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            out = enc.forward(ids, None)
+        ms = (time.perf_counter() - t0) * 1e3 / iters
+        qd, kd = d.heads * d.head_dim, d.kv_heads * d.head_dim
+        per_layer = 2.0 * seq * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter) + 2.0 * seq * seq * qd
+        flops = 27 * per_layer
+        wbytes = 27 * 2.0 * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter)
+        print(json.dumps({"micro": "qwen3", "seq": seq, "layers_run": 27, "ms_per_prompt_e2e": ms,
+                          "model_tflops": flops / ms / 1e9, "weight_gb_per_pass": wbytes / 1e9,
+                          "weight_stream_ms_at_hbm_peak": wbytes / peaks["hbm_gbs"] / 1e6,
+                          "d2h_bytes": int(out.nbytes), "finite": bool(np.isfinite(out).all()),
+                          "peak_source": peaks["source"]}))
+        enc.close()
     return 0
 
 
@@ -434,7 +461,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--seq", type=int, default=1536)

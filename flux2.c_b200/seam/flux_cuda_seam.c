@@ -5,7 +5,8 @@
  * flux_sample.c / flux_transformer.c define them. This file defines the same symbols on top of
  * flux_cuda.h, so that building the reference with this file (and libflux_cuda.so) IN PLACE OF
  * flux_transformer.c and flux_sample.c gives the unmodified CLI / library (main.c, flux.c, flux_cli.c,
- * flux_vae.c, flux_qwen3.c, flux_kernels.c, ...) a GPU denoising path. It is compiled inside the
+ * flux_vae.c, flux_kernels.c, ...) a GPU denoising path (flux_cuda_qwen3_seam.c does the same for
+ * flux_qwen3.c). It is compiled inside the
  * reference's source tree (it includes the reference's own flux_safetensors.h and flux_kernels.h for the
  * struct layouts and the global callback pointers those files own).
  *
@@ -78,6 +79,9 @@ static flux_cuda_ctx *seam_ctx(void) {
   }
   return g_ctx;
 }
+
+/* The seam's one context, for the other seam files (flux_cuda_qwen3_seam.c). */
+flux_cuda_ctx *flux_cuda_seam_context(void) { return seam_ctx(); }
 
 /* ------------------------------------------------------------------------------------------ loading */
 static flux_transformer_t *load_from(safetensors_file_t *sf) {

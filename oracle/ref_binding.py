@@ -38,7 +38,7 @@ def _preload(prefix):
 
 
 def available(kind="blas"):
-    return os.path.exists(os.path.join(REF_DIR, "libflux_ref_%s.so" % kind))
+    return os.path.exists(os.path.join(REF_DIR, "libflux_seam.so" if kind == "seam" else "libflux_ref_%s.so" % kind))
 
 
 def best_kind():
@@ -58,7 +58,9 @@ def _fp(a):
 
 class RefLib:
     def __init__(self, kind="blas"):
-        path = os.path.join(REF_DIR, "libflux_ref_%s.so" % kind)
+        # kind "seam": the reference's library with flux_transformer.c, flux_sample.c and flux_qwen3.c replaced by the
+        # CUDA engine's seam files (oracle/Makefile, libflux_seam.so) - same symbols, same binding, needs a GPU
+        path = os.path.join(REF_DIR, "libflux_seam.so" if kind == "seam" else "libflux_ref_%s.so" % kind)
         self.kind = kind
         if kind == "blas":
             # the bundled OpenBLAS needs the libgfortran that sits next to it; load both by full path first
