@@ -79,6 +79,9 @@ def _declare(L):
     L.flux_cuda_qwen3_free.argtypes = [c_void_p]
     L.flux_cuda_qwen3_forward.restype = c_int
     L.flux_cuda_qwen3_forward.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, fp]
+    L.flux_cuda_qwen3_forward_device.restype = c_int
+    L.flux_cuda_qwen3_forward_device.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
+                                                 ctypes.POINTER(c_void_p)]
     L.flux_cuda_patchify.restype = c_int
     L.flux_cuda_patchify.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
     L.flux_cuda_unpatchify.restype = c_int
@@ -405,6 +408,19 @@ class TextEncoder:
         check(lib().flux_cuda_qwen3_forward(self.handle, ids.ctypes.data_as(ip), mp, len(ids), _fp(out)))
         return out
 
+    def forward_device(self, ids, mask=None):
+        """Queues the pass and returns the device address of the f32 [seq, 3 * hidden] result (no wait, no copy)."""
+        np = _np()
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        ip = ctypes.POINTER(ctypes.c_int)
+        mp = None
+        if mask is not None:
+            mask = np.ascontiguousarray(mask, dtype=np.int32)
+            mp = mask.ctypes.data_as(ip)
+        dev = ctypes.c_void_p()
+        check(lib().flux_cuda_qwen3_forward_device(self.handle, ids.ctypes.data_as(ip), mp, len(ids), ctypes.byref(dev)))
+        return dev.value
+
     def close(self):
         if self.handle:
             lib().flux_cuda_qwen3_free(self.handle)
@@ -425,7 +441,7 @@ class Sampler:
         self.n_refs = len(ref_shapes)
 
     def upload(self, z0_ptr, ctx_ptr, ctx_uncond_ptr=None, ref_ptrs=()):
-        """Host pointers (ints) of f32 buffers; pinned memory makes the copies asynchronous."""
+        """Addresses (ints) of f32 buffers, host (pinned memory makes the copies asynchronous) or device."""
         refs = (ctypes.c_void_p * max(1, len(ref_ptrs)))(*ref_ptrs)
         check(lib().flux_cuda_sampler_upload(self.handle, z0_ptr, ctx_ptr, ctx_uncond_ptr, refs))
 

@@ -470,10 +470,10 @@ int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, con
     return FLUX_CUDA_ERR_ARG;
   }
   const size_t C = d.latent_ch, ctx_n = static_cast<size_t>(ws->n_txt) * d.text_dim;
-  int rc = check_cuda(cudaMemcpyAsync(ws->z_in, z0, C * ws->n_img * 4, cudaMemcpyHostToDevice, st), "upload z");
-  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->ctx_in, ctx0, ctx_n * 4, cudaMemcpyHostToDevice, st), "upload ctx");
+  int rc = check_cuda(cudaMemcpyAsync(ws->z_in, z0, C * ws->n_img * 4, cudaMemcpyDefault, st), "upload z");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->ctx_in, ctx0, ctx_n * 4, cudaMemcpyDefault, st), "upload ctx");
   if (!rc && ws->B == 2)
-    rc = check_cuda(cudaMemcpyAsync(ws->ctx_in + ctx_n, ctx1, ctx_n * 4, cudaMemcpyHostToDevice, st), "upload ctx");
+    rc = check_cuda(cudaMemcpyAsync(ws->ctx_in + ctx_n, ctx1, ctx_n * 4, cudaMemcpyDefault, st), "upload ctx");
   size_t off = 0;
   for (size_t i = 0; !rc && i < ws->refs.size(); ++i) {
     const size_t n = static_cast<size_t>(ws->refs[i].h) * ws->refs[i].w;
@@ -481,7 +481,7 @@ int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, con
       set_error("upload: reference latent %zu is null", i);
       return FLUX_CUDA_ERR_ARG;
     }
-    rc = check_cuda(cudaMemcpyAsync(ws->ref_in + off * C, ref_latents[i], C * n * 4, cudaMemcpyHostToDevice, st),
+    rc = check_cuda(cudaMemcpyAsync(ws->ref_in + off * C, ref_latents[i], C * n * 4, cudaMemcpyDefault, st),
                     "upload ref");
     off += n;
   }

@@ -224,7 +224,7 @@ int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims,
     flux_cuda_qwen3_free(m);
     return rc;
   }
-  m->expected = 2 + static_cast<size_t>(d.layers) * 11;
+  m->expected = 1 + static_cast<size_t>(m->run_layers) * 11;  // the embedding and the layers the output depends on
   *out = m;
   return FLUX_CUDA_OK;
 }
@@ -314,7 +314,8 @@ int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void 
   } else {
     set_error("unknown tensor %s", name);
   }
-  if (rc == 0) m->seen.insert(n);
+  // completeness is judged on what the output depends on: the final norm and later layers are accepted, not required
+  if (rc == 0 && (n == "model.embed_tokens.weight" || (idx >= 0 && idx < m->run_layers))) m->seen.insert(n);
   return rc;
 }
 
@@ -370,8 +371,9 @@ static int q_gemm(flux_cuda_qwen3 *m, const void *X, long long ldx, const void *
   return pair ? gemm2_launch(&P, m->ctx->num_sms, m->ctx->stream) : gemm_launch(&P, 256, m->ctx->num_sms, m->ctx->stream);
 }
 
-int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, float *out) {
-  if (!m || !input_ids || !out || seq < 1) {
+// Queues the whole pass on the context's stream; the result is m->out ([seq, 3 * hidden] f32, device).
+static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq) {
+  if (!m || !input_ids || seq < 1) {
     set_error("qwen3_forward: bad argument");
     return FLUX_CUDA_ERR_ARG;
   }
@@ -456,10 +458,34 @@ int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int 
     ctx_sync_check(m->ctx);
     return gr == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
   }
-  rc = check_cuda(cudaMemcpyAsync(out, m->out, static_cast<size_t>(seq) * 3 * h * sizeof(float), cudaMemcpyDeviceToHost, st),
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, float *out) {
+  if (!out) {
+    set_error("qwen3_forward: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq);
+  if (rc) return rc;
+  rc = check_cuda(cudaMemcpyAsync(out, m->out, static_cast<size_t>(seq) * 3 * m->d.hidden * sizeof(float),
+                                  cudaMemcpyDeviceToHost, m->ctx->stream),
                   "download embeddings");
   if (!rc) rc = ctx_sync_check(m->ctx);
   return rc;
+}
+
+int flux_cuda_qwen3_forward_device(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq,
+                                   const float **out_dev) {
+  if (!out_dev) {
+    set_error("qwen3_forward_device: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  *out_dev = nullptr;
+  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq);
+  if (rc) return rc;
+  *out_dev = m->out;
+  return FLUX_CUDA_OK;
 }
 
 }  // extern "C"

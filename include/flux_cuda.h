@@ -136,7 +136,8 @@ typedef struct flux_cuda_ref_shape { int h, w, t_offset; } flux_cuda_ref_shape;
 int flux_cuda_sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const flux_cuda_ref_shape *refs,
                              int num_refs, int batch, int max_steps, flux_cuda_sampler **out);
 void flux_cuda_sampler_free(flux_cuda_sampler *s);
-/* Asynchronous host -> device copies of the raw f32 inputs (pinned host memory makes them overlap). */
+/* Asynchronous copies of the raw f32 inputs into the sampler's buffers, ordered on the context's stream. Each
+ * pointer may be host memory (pinned host memory makes the copies overlap) or memory of the context's device. */
 int flux_cuda_sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx, const float *ctx_uncond,
                              const float *const *ref_latents);
 /* Queues input preparation + num_steps x (forward, update) on the context's stream; does not wait.
@@ -201,7 +202,7 @@ typedef struct flux_cuda_qwen3_dims {
 /* The Qwen3-4B shape the reference hard-codes (flux_qwen3.h:21-40): outputs after layers 8, 17, 26. */
 void flux_cuda_qwen3_dims_4b(flux_cuda_qwen3_dims *d);
 /* Loads `text_encoder/` (both model-0000{1,2}-of-00002.safetensors must exist, flux_qwen3.c:1341-1356). Only the
- * layers the output depends on are kept on the device. max_seq: largest token count of a later forward. */
+ * layers the output depends on are kept on the device (and only those must be present in the files). max_seq: largest token count of a later forward. */
 int flux_cuda_qwen3_load_dir(flux_cuda_ctx *ctx, const char *model_dir, int max_seq, flux_cuda_qwen3 **out);
 int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims, int max_seq, flux_cuda_qwen3 **out);
 int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void *data, int dtype,
@@ -211,6 +212,12 @@ void flux_cuda_qwen3_free(flux_cuda_qwen3 *m);
 /* input_ids, attention_mask (may be NULL = all ones): host int[seq]; out: host f32 [seq, 3 * hidden]. Causal,
  * grouped-query attention with the key padding mask, as the reference's CPU path (flux_qwen3.c:313-452). */
 int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, float *out);
+/* The same pass, queued on the context's stream without waiting and without the device -> host copy: *out_dev is the
+ * encoder's own device buffer, f32 [seq, 3 * hidden], valid (in stream order) until the next forward on this
+ * encoder. Hand it to flux_cuda_sampler_upload as the context: prompt -> latent then never leaves the device. No
+ * counterpart in the reference, whose encoder and transformer exchange host buffers (flux.c:330-360). */
+int flux_cuda_qwen3_forward_device(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq,
+                                   const float **out_dev);
 
 /* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points on DEVICE pointers (unit tests, microbenchmarks). Asynchronous on the

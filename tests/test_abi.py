@@ -62,3 +62,8 @@ def test_seam_defines_every_symbol_of_the_objects_it_replaces():
 
     missing = set().union(*[exported(t) for t in theirs]) - exported(seam)
     assert not missing, sorted(missing)
+    # the same for the text encoder's file and its seam
+    qseam, qtheirs = os.path.join(ref, "obj_seam", "flux_cuda_qwen3_seam.o"), os.path.join(ref, "obj_blas", "flux_qwen3.o")
+    if os.path.exists(qseam) and os.path.exists(qtheirs):
+        missing = exported(qtheirs) - exported(qseam)
+        assert not missing, sorted(missing)

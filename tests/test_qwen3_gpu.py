@@ -74,6 +74,31 @@ def test_encoder_rejects_bad_calls(tiny_enc, fx, ctx):
         fx.TextEncoder.from_tensors(ctx, d, W)
 
 
+def test_embeddings_stay_on_the_device(tiny_enc, fx, ctx):
+    """forward_device hands the sampler a device buffer: the latent equals the one obtained through host embeddings."""
+    import torch
+    synth, d, enc, oracle = tiny_enc
+    dd = synth.Dims(hidden=256, heads=2, head_dim=128, mlp=768, n_double=1, n_single=2, text_dim=3 * d.hidden)
+    model = fx.Model.from_tensors(ctx, dd, synth.make_transformer_weights(dd, seed=3, sharp=True, std=0.08))
+    try:
+        h, w, seq = 6, 4, 40
+        ids = np.random.default_rng(9).integers(0, d.vocab, seq)
+        z0 = fx.init_noise(dd.latent_ch, h, w, 5)
+        sch = fx.official_schedule(3, h * w)
+        want = model.sample(z0, h, w, enc.forward(ids, None), sch)
+        sampler = fx.Sampler(model, h, w, seq, batch=1, max_steps=3)
+        zp = torch.from_numpy(z0.copy()).pin_memory()
+        got = torch.zeros(z0.size, dtype=torch.float32).pin_memory()
+        for _ in range(2):  # twice: the encoder's buffer is reused by the next forward
+            sampler.upload(zp.data_ptr(), enc.forward_device(ids, None))
+            sampler.run(sch)
+            sampler.download(got.data_ptr())
+            assert rel(got.numpy().reshape(z0.shape), want) < 1e-6
+        sampler.close()
+    finally:
+        model.close()
+
+
 def test_qwen3_4b_matches_reference(fx, ctx):
     """Qwen3-4B shape, seeded weights, 64 tokens of which 40 are valid: output of the reference's qwen3_forward
     (stored for every 4th column)."""

@@ -68,7 +68,8 @@ def test_seam_transformer_and_samplers_match_oracle(seam, scratch, fx):
 
 def test_seam_text_encoder_loads_shards_and_matches_reference(seam, scratch):
     """qwen3_model_load on a directory with the two shards, qwen3_forward on 64 tokens (40 valid) against the output the
-    reference produced from the same files' contents."""
+    reference produced from the same tensors. Only layers 0..26 are written here: the output does not depend on the
+    rest, and the engine's loader does not ask for them."""
     import flux2_c_b200.synth as synth
     path = os.path.join(GOLDEN, "reference_qwen3.npz")
     if not os.path.exists(path):
@@ -76,7 +77,7 @@ def test_seam_text_encoder_loads_shards_and_matches_reference(seam, scratch):
     g = np.load(path)
     d = synth.QwenDims.qwen3_4b()
     mdir = os.path.join(scratch, "text_encoder")
-    W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count())
+    W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count(), max_layer=26)
     synth.write_qwen_shards(mdir, W)
     del W
     m = seam.qwen3_load(mdir)
