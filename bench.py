@@ -2,7 +2,7 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln|qwen3 [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|attn|adaln|qwen3|vae [...]            # one kernel, small memory (for ncu captures)
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
 (1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
@@ -231,6 +231,33 @@ def run_micro(args):
         gbs = rows * hid * 6.0 / ms / 1e6
         print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
                           gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    elif args.micro == "vae":
+        # The VAE decoder on a --size x --size image (latent size/16): device time with the latent resident, and the
+        # host-buffer call (latent in, uint8 RGB out).
+        import numpy as np
+        synth = importlib.import_module("flux2_c_b200.synth")
+        vae = fx.Vae.from_tensors(ctx, synth.make_vae_weights(seed=5, rich=True))
+        hl = args.size // 16
+        lat = torch.from_numpy(synth.make_latent(42, 128, hl, hl)).cuda()
+        img = np.empty((16 * hl, 16 * hl, 3), dtype=np.uint8)
+        torch.cuda.synchronize()
+        ms = timed(lambda: vae.decode_device(lat.data_ptr(), hl, hl))
+        lat_h = lat.cpu().numpy()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            vae.decode_ptr(lat_h.ctypes.data, hl, hl, img.ctypes.data)
+        e2e = (time.perf_counter() - t0) * 1e3 / iters
+        px = [(2 * hl) ** 2 * 4 ** i for i in range(4)]  # pixels per level: 1/8, 1/4, 1/2 and full resolution
+        c3 = lambda p, ci, co: 2.0 * 9 * ci * co * p
+        flops = (c3(px[0], 32, 512) + 10 * c3(px[0], 512, 512) + 4 * 2.0 * px[0] * 512 * 512 + 4.0 * px[0] * px[0] * 512 +
+                 7 * c3(px[1], 512, 512) + c3(px[2], 512, 512) + c3(px[2], 512, 256) + 5 * c3(px[2], 256, 256) +
+                 2.0 * px[2] * 512 * 256 + c3(px[3], 256, 256) + c3(px[3], 256, 128) + 5 * c3(px[3], 128, 128) +
+                 2.0 * px[3] * 256 * 128 + c3(px[3], 128, 3))
+        print(json.dumps({"micro": "vae", "image": [16 * hl, 16 * hl], "ms_device": ms, "ms_e2e": e2e,
+                          "launches": vae.last_launches(), "conv_tflops": flops / ms / 1e9,
+                          "algorithmic_gflop": flops / 1e9, "image_std": float(img.std()),
+                          "peak_source": peaks["source"]}))
+        vae.close()
     elif args.micro == "qwen3":
         # The text encoder at the Qwen3-4B shape (only the 27 layers the output depends on are built), one prompt
         # of --seq tokens through the host-buffer entry point: token ids in, [seq, 7680] f32 embeddings out.
@@ -533,11 +560,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--size", type=int, default=512, help="image side for --micro vae")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-text-encoder", action="store_true", help="skip the prompt -> latent leg")
     ap.add_argument("--dump-launches", default=None, help="write [ms, class] of every launch of one image to this file")

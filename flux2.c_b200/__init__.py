@@ -79,6 +79,34 @@ def _declare(L):
     L.flux_cuda_qwen3_free.argtypes = [c_void_p]
     L.flux_cuda_qwen3_forward.restype = c_int
     L.flux_cuda_qwen3_forward.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, fp]
+    L.flux_cuda_vae_load_safetensors.restype = c_int
+    L.flux_cuda_vae_load_safetensors.argtypes = [c_void_p, ctypes.c_char_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_vae_create.restype = c_int
+    L.flux_cuda_vae_create.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_vae_set_tensor.restype = c_int
+    L.flux_cuda_vae_set_tensor.argtypes = [c_void_p, ctypes.c_char_p, c_void_p, c_int, ctypes.POINTER(ctypes.c_longlong),
+                                           c_int]
+    L.flux_cuda_vae_finalize.restype = c_int
+    L.flux_cuda_vae_finalize.argtypes = [c_void_p]
+    L.flux_cuda_vae_free.restype = None
+    L.flux_cuda_vae_free.argtypes = [c_void_p]
+    L.flux_cuda_vae_decode.restype = c_int
+    L.flux_cuda_vae_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
+    L.flux_cuda_vae_decode_device.restype = c_int
+    L.flux_cuda_vae_decode_device.argtypes = [c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_vae_last_launches.restype = ctypes.c_longlong
+    L.flux_cuda_vae_last_launches.argtypes = [c_void_p]
+    L.flux_cuda_sampler_latent_device.restype = c_int
+    L.flux_cuda_sampler_latent_device.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_conv3x3.restype = c_int
+    L.flux_cuda_conv3x3.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                    c_void_p, ctypes.c_longlong, c_int]
+    L.flux_cuda_gemm_bias.restype = c_int
+    L.flux_cuda_gemm_bias.argtypes = [c_void_p, c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_int, c_int,
+                                      c_int, c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int]
+    L.flux_cuda_group_norm.restype = c_int
+    L.flux_cuda_group_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, ctypes.c_longlong, c_int, c_void_p,
+                                       c_void_p, ctypes.c_float, c_int, c_int]
     L.flux_cuda_qwen3_forward_device.restype = c_int
     L.flux_cuda_qwen3_forward_device.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
                                                  ctypes.POINTER(c_void_p)]
@@ -226,6 +254,18 @@ class Context:
 
     def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, f16=False):
         check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, int(f16)))
+
+    def conv3x3(self, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld, f16=True):
+        check(lib().flux_cuda_conv3x3(self.handle, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld,
+                                      int(f16)))
+
+    def gemm_bias(self, x_ptr, ldx, w_ptr, ldw, M, N, K, bias_ptr, mode, out_ptr, ld, w_rows=None, f16=True):
+        check(lib().flux_cuda_gemm_bias(self.handle, x_ptr, ldx, w_ptr, ldw, M, N, K, N if w_rows is None else w_rows,
+                                        bias_ptr, mode, out_ptr, ld, int(f16)))
+
+    def group_norm(self, x_ptr, in16, out_ptr, n_img, pixels, C, gamma_ptr, beta_ptr, eps, swish, f16=True):
+        check(lib().flux_cuda_group_norm(self.handle, x_ptr, int(in16), out_ptr, n_img, pixels, C, gamma_ptr, beta_ptr,
+                                         eps, int(swish), int(f16)))
 
     def patchify(self, out_ptr, in_ptr, batch, channels, H, W, patch):
         check(lib().flux_cuda_patchify(self.handle, out_ptr, in_ptr, batch, channels, H, W, patch))
@@ -427,6 +467,59 @@ class TextEncoder:
             self.handle = ctypes.c_void_p()
 
 
+class Vae:
+    """The VAE decoder on one GPU. Mirrors flux_vae_load_safetensors / flux_vae_decode / flux_vae_free."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    @staticmethod
+    def load_safetensors(ctx, path):
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_vae_load_safetensors(ctx.handle, path.encode(), ctypes.byref(h)))
+        return Vae(ctx, h)
+
+    @staticmethod
+    def from_tensors(ctx, tensors):
+        h = ctypes.c_void_p()
+        check(lib().flux_cuda_vae_create(ctx.handle, ctypes.byref(h)))
+        np = _np()
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            shape = (ctypes.c_longlong * arr.ndim)(*arr.shape)
+            check(lib().flux_cuda_vae_set_tensor(h, name.encode(), arr.ctypes.data, _DTYPES[str(arr.dtype)], shape,
+                                                 arr.ndim))
+        check(lib().flux_cuda_vae_finalize(h))
+        return Vae(ctx, h)
+
+    def decode(self, latent):
+        """latent f32 [128, h, w] -> uint8 RGB [16h, 16w, 3]."""
+        np = _np()
+        lat = np.ascontiguousarray(latent, dtype=np.float32)
+        _, h, w = lat.shape
+        out = np.empty((16 * h, 16 * w, 3), dtype=np.uint8)
+        check(lib().flux_cuda_vae_decode(self.handle, lat.ctypes.data, h, w, out.ctypes.data))
+        return out
+
+    def decode_ptr(self, latent_ptr, h, w, rgb_host_ptr):
+        """latent_ptr: host or device address of f32 [128, h, w]; rgb_host_ptr: host address of uint8 [16h, 16w, 3]."""
+        check(lib().flux_cuda_vae_decode(self.handle, latent_ptr, h, w, rgb_host_ptr))
+
+    def decode_device(self, latent_ptr, h, w):
+        """Queues the decode (no wait); returns the device address of the uint8 [16h, 16w, 3] image."""
+        p = ctypes.c_void_p()
+        check(lib().flux_cuda_vae_decode_device(self.handle, latent_ptr, h, w, ctypes.byref(p)))
+        return p.value
+
+    def last_launches(self):
+        return int(lib().flux_cuda_vae_last_launches(self.handle))
+
+    def close(self):
+        if self.handle:
+            lib().flux_cuda_vae_free(self.handle)
+            self.handle = ctypes.c_void_p()
+
+
 class Sampler:
     """Buffers for one (h, w, txt_seq, refs, batch) shape: upload / run / download as separate phases."""
 
@@ -468,6 +561,12 @@ class Sampler:
 
     def apply_velocity(self, v_dev_ptr, step):
         check(lib().flux_cuda_sampler_apply_velocity(self.handle, v_dev_ptr, step))
+
+    def latent_device(self):
+        """Device address of the current latent (f32 [128, h, w])."""
+        p = ctypes.c_void_p()
+        check(lib().flux_cuda_sampler_latent_device(self.handle, ctypes.byref(p)))
+        return p.value
 
     def download(self, latent_ptr, velocities_ptr=None):
         check(lib().flux_cuda_sampler_download(self.handle, latent_ptr, velocities_ptr))

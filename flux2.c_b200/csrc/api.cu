@@ -13,7 +13,9 @@
 #include "context.cuh"
 #include "elementwise.cuh"
 #include "engine.cuh"
+#include "conv.cuh"
 #include "gemm.cuh"
+#include "vae_kernels.cuh"
 
 namespace fx {
 static thread_local char g_err[512] = "";
@@ -85,7 +87,8 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
   if (const char *e = getenv("FLUX_CUDA_GEMM_PAIR")) c->gemm_pair = atoi(e) != 0;
   if (const char *e = getenv("FLUX_CUDA_BF16")) c->f16 = atoi(e) == 0;
   if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 1 ? 1 : 2;
-  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || attn2_init() != 0 || elementwise_init() != 0) {
+  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || attn2_init() != 0 || elementwise_init() != 0 ||
+      conv_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
     flux_cuda_ctx_destroy(c);
     return FLUX_CUDA_ERR_CUDA;
@@ -103,6 +106,7 @@ void flux_cuda_ctx_destroy(flux_cuda_ctx *ctx) {
   }
   if (ctx->err_dev) cudaFree(ctx->err_dev);
   if (ctx->err_host) cudaFreeHost(ctx->err_host);
+  if (ctx->gn_scratch) cudaFree(ctx->gn_scratch);
   delete ctx;
 }
 
@@ -251,6 +255,72 @@ int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int
   return FLUX_CUDA_OK;
 }
 
+static int conv_finish(flux_cuda_ctx *ctx, ConvParams &P, const float *bias, int mode, void *out, long long ld, int f16,
+                       const char *what) {
+  if (mode < 0 || mode > 3 || !out) {
+    set_error("%s: bad mode or output", what);
+    return FLUX_CUDA_ERR_ARG;
+  }
+  P.mode = mode;
+  P.out = out;
+  P.ld = ld;
+  P.bias = bias;
+  P.out_f16 = P.x_f16 = f16 ? 1 : 0;
+  P.err = ctx->err_dev;
+  if (conv_launch(&P, ctx->num_sms, ctx->stream) != 0) {
+    set_error("%s: launch failed: %s", what, cudaGetErrorString(cudaGetLastError()));
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_conv3x3(flux_cuda_ctx *ctx, const void *x16, int n_img, int H, int W, int cin, const void *w16, int cout,
+                      const float *bias, int mode, void *out, long long ld, int f16) {
+  if (!ctx || !x16 || !w16) return FLUX_CUDA_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  ConvParams P;
+  memset(&P, 0, sizeof(P));
+  if (conv_make_3x3(&P, x16, n_img, H, W, cin, w16, cout) != 0) {
+    set_error("conv3x3: unsupported shape (cin %% 64, cout %% 128, 16-byte aligned pointers)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  return conv_finish(ctx, P, bias, mode, out, ld, f16, "conv3x3");
+}
+
+int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, const void *w16, long long ldw, int M, int N,
+                        int K, int w_rows, const float *bias, int mode, void *out, long long ld, int f16) {
+  if (!ctx || !x16 || !w16) return FLUX_CUDA_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  ConvParams P;
+  memset(&P, 0, sizeof(P));
+  if (conv_make_gemm(&P, x16, ldx, w16, ldw, M, N, K, w_rows) != 0) {
+    set_error("gemm_bias: unsupported shape (K %% 64, N %% 128, 16-byte aligned pointers and pitches)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  return conv_finish(ctx, P, bias, mode, out, ld, f16, "gemm_bias");
+}
+
+int flux_cuda_group_norm(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels, int C,
+                         const float *gamma, const float *beta, float eps, int swish, int f16) {
+  if (!ctx || !x || !out16 || !gamma || !beta || n_img < 1 || n_img > 8) return FLUX_CUDA_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  const size_t part = static_cast<size_t>(8) * GN_MAX_BLOCKS * 64, stats = 8 * GN_GROUPS * 2;
+  if (!ctx->gn_scratch) {
+    int rc = check_cuda(cudaMalloc(&ctx->gn_scratch, (part + stats + 8) * 4), "cudaMalloc");
+    if (rc) return rc;
+    cudaMemsetAsync(ctx->gn_scratch, 0, (part + stats + 8) * 4, ctx->stream);
+  }
+  float *st = ctx->gn_scratch + part;
+  unsigned int *counters = reinterpret_cast<unsigned int *>(st + stats);
+  int rc = launch_gn_stats(x, in16, f16, n_img, pixels, C, eps, ctx->gn_scratch, counters, st, ctx->stream);
+  if (!rc) rc = launch_gn_apply(x, in16, out16, f16, n_img, pixels, C, st, gamma, beta, swish, ctx->stream);
+  if (rc) {
+    set_error("group_norm: unsupported channel count %d or launch failure", C);
+    return rc == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
 int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
                            int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t) {
   if (!ctx || !qkv || !wq || !wk || !cos_t || !sin_t) return FLUX_CUDA_ERR_ARG;
@@ -378,6 +448,11 @@ int flux_cuda_sampler_apply_velocity(flux_cuda_sampler *s, const float *v_dev, i
 }
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
   return sampler_download(s, latent_out, velocities_out);
+}
+int flux_cuda_sampler_latent_device(flux_cuda_sampler *s, const float **latent_dev) {
+  if (!s || !latent_dev) return FLUX_CUDA_ERR_ARG;
+  *latent_dev = s->ws->z;
+  return FLUX_CUDA_OK;
 }
 int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kernel_launches) {
   if (!s) return FLUX_CUDA_ERR_ARG;

@@ -14,6 +14,7 @@ struct flux_cuda_ctx {
   bool f16 = true;                // 16-bit tensors (weights and activations) are f16; false: bf16
   int attn_version = 2;           // 1: attention.cu, 2: attention2.cu
   bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
+  float *gn_scratch = nullptr;    // lazily allocated scratch of the kernel-level GroupNorm entry point
 };
 
 namespace fx {

@@ -1,0 +1,49 @@
+// Host-visible description of one launch of the tcgen05 implicit-GEMM convolution kernel (conv_tcgen05.cu):
+// a 3x3, stride 1, zero-padded convolution over a channels-last (NHWC) 16-bit activation tensor, or - with
+// taps = 1 - a plain GEMM over rows with a bias (1x1 convolutions, attention products). This is the engine's
+// replacement for the reference's flux_conv2d call sites in the VAE (flux_vae.c:127-145, flux_kernels.c:342-505).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fx {
+
+enum ConvEpi : int {
+  CONV_STORE_16 = 0,    // out16[row, col] = acc + bias[col]
+  CONV_STORE_F32 = 1,   // out32[row, col] = acc + bias[col]
+  CONV_ADD_F32 = 2,     // out32[row, col] += acc + bias[col]   (residual connection of a ResNet block)
+  CONV_STORE_RGB8 = 3,  // out8[row * 3 + c] = clamp((acc[c] + bias[c] + 1) * 127.5, 0, 255) truncated, c < 3
+                        // (flux_vae.c:822-833: the decoder's last convolution and its conversion to an image)
+};
+
+struct alignas(64) ConvParams {
+  CUtensorMap tmA;  // taps == 9: {C, W, H, N} channels-last, box {64, BW, BH, 1}; taps == 1: [M, K], box {64, 128}
+  CUtensorMap tmB;  // weights [Cout, taps * Cin] (tap-major, input channel minor), box {64, BN / 2}
+  int taps;         // 9 or 1
+  int n_img, H, W;  // taps == 9
+  int bw_log2;      // a CTA's 128 rows are a patch of 2^bw_log2 columns x (128 >> bw_log2) rows of pixels
+  int tiles_x, tiles_y;
+  int M;            // rows = pixels of all images
+  int Cin, Cout;    // Cin % 64 == 0 (pad with zero channels), Cout % bn == 0
+  int bn;           // 128 or 256 output columns per tile
+  int patches, tiles_m, tiles_n;
+  int x_f16;        // operands hold f16 instead of bf16
+  int mode, out_f16;
+  void *out;
+  long long ld;       // destination row pitch in elements
+  const float *bias;  // [Cout] or null
+  int *err;
+};
+
+int conv_init();
+// x: [n_img, H, W, Cin] 16-bit; w: [Cout, 9 * Cin] 16-bit.
+int conv_make_3x3(ConvParams *p, const void *x, int n_img, int H, int W, int Cin, const void *w, int Cout);
+// Y[M, N] = X[M, K] (row pitch ldx) * Wt[N, K]^T (row pitch ldw). Only the first w_rows rows of Wt exist in memory
+// (w_rows <= N): the columns of Y beyond them come out as the bias alone.
+int conv_make_gemm(ConvParams *p, const void *X, long long ldx, const void *Wt, long long ldw, int M, int N, int K,
+                   int w_rows);
+// Fill mode / out / ld / bias / out_f16 / x_f16 / err before launching.
+int conv_launch(ConvParams *p, int num_sms, cudaStream_t stream);
+
+}  // namespace fx

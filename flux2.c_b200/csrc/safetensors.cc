@@ -220,7 +220,7 @@ int safetensors_for_each(const char *path,
     size_t count = 1;
     for (long long d : e.shape) count *= static_cast<size_t>(d);
     const size_t esz = dt == 0 ? 4 : 2;
-    if (dt < 0 || e.shape.empty() || e.shape.size() > 2) {
+    if (dt < 0 || e.shape.empty() || e.shape.size() > 4) {  // the visitor judges the rank it expects
       set_error("%s: tensor %s has unsupported dtype/rank", path, e.name.c_str());
       rc = FLUX_CUDA_ERR_MODEL;
     } else if (e.end < e.begin || e.end - e.begin != count * esz || data0 + e.end > fsize) {

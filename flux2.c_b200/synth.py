@@ -196,16 +196,28 @@ def vae_tensor_specs():
     return specs
 
 
-def make_vae_weights(seed=0, std=0.02):
+def make_vae_weights(seed=0, std=0.02, rich=False):
     """dict name -> float32 array: conv/linear weights N(0, std^2), norm scales 1, biases and running mean 0,
-    running variance 1. Only used to turn latents into pixels for the decoded-image PSNR check."""
+    running variance 1 (the set the decoded-image PSNR check of the denoising path uses).
+    rich=True is the set for the VAE's own parity tests: every bias N(0, 0.1^2), norm scales 1 + N(0, 0.2^2),
+    running mean N(0, 0.5^2), running variance uniform(0.5, 2), attention q/k projections ten times larger, so
+    that biases, affine terms, de-normalisation and a non-uniform softmax all show in the output."""
     out = {}
     for idx, (name, shape, kind) in enumerate(vae_tensor_specs()):
+        rng = np.random.Generator(np.random.Philox(key=[np.uint64(seed), np.uint64(0x7A0000 + idx)]))
         if kind == "w":
-            rng = np.random.Generator(np.random.Philox(key=[np.uint64(seed), np.uint64(0x7A0000 + idx)]))
-            out[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
-        else:
+            scale = std * (10.0 if rich and (".to_q." in name or ".to_k." in name) else 1.0)
+            out[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(np.float32)
+        elif not rich:
             out[name] = np.full(shape, 1.0 if kind == "one" else 0.0, dtype=np.float32)
+        elif name == "bn.running_var":
+            out[name] = rng.uniform(0.5, 2.0, shape).astype(np.float32)
+        elif name == "bn.running_mean":
+            out[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.5)).astype(np.float32)
+        elif kind == "one":
+            out[name] = (1.0 + rng.standard_normal(shape, dtype=np.float32) * np.float32(0.2)).astype(np.float32)
+        else:
+            out[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.1)).astype(np.float32)
     return out
 
 

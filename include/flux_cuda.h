@@ -220,6 +220,33 @@ int flux_cuda_qwen3_forward_device(flux_cuda_qwen3 *m, const int *input_ids, con
                                    const float **out_dev);
 
 /* ------------------------------------------------------------------------------------------------
+ * The stage after the loop: the VAE decoder (latent -> RGB image). Mirrors flux_vae_load_safetensors /
+ * flux_vae_decode / flux_vae_free (flux_vae.c:1232-1386, 690-837, 1034-1104) for the decoder half: channel
+ * configuration 128 x (1, 2, 4, 4), two + one ResNet blocks per level, GroupNorm(32), one attention block.
+ * Tensor names are the file's own ("decoder.*", "post_quant_conv.*", optional "bn.running_mean/var"); tensors of
+ * the encoder half are accepted and ignored.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_vae flux_cuda_vae;
+int flux_cuda_vae_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_vae **out);
+int flux_cuda_vae_create(flux_cuda_ctx *ctx, flux_cuda_vae **out);
+/* dtype as flux_cuda_model_set_tensor; convolution weights in the file's [out, in, kh, kw] order. */
+int flux_cuda_vae_set_tensor(flux_cuda_vae *v, const char *name, const void *data, int dtype, const long long *shape,
+                             int ndim);
+int flux_cuda_vae_finalize(flux_cuda_vae *v);
+void flux_cuda_vae_free(flux_cuda_vae *v);
+/* latent: f32 [128, h, w], host memory or memory of the context's device (e.g. flux_cuda_sampler_latent_device);
+ * rgb_out: host uint8 [16h, 16w, 3], values (x + 1) * 127.5 clamped to [0, 255] and truncated like the reference's
+ * conversion (flux_vae.c:822-833). Buffers grow to the largest size decoded so far. */
+int flux_cuda_vae_decode(flux_cuda_vae *v, const float *latent, int h, int w, unsigned char *rgb_out);
+/* The same, queued without waiting; *rgb_dev is the decoder's own device buffer (valid until the next decode). */
+int flux_cuda_vae_decode_device(flux_cuda_vae *v, const float *latent, int h, int w, const unsigned char **rgb_dev);
+/* Kernels launched by the last decode. */
+long long flux_cuda_vae_last_launches(const flux_cuda_vae *v);
+/* Device address of a sampler's current latent (f32 [128, h, w]; batch 2: the shared latent), in stream order
+ * after the last run. */
+int flux_cuda_sampler_latent_device(flux_cuda_sampler *s, const float **latent_dev);
+
+/* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points on DEVICE pointers (unit tests, microbenchmarks). Asynchronous on the
  * context's stream.
  * ---------------------------------------------------------------------------------------------- */
@@ -271,6 +298,20 @@ int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq,
 /* apply_adaln (flux_transformer.c:979-1048): out_16 = (1 + scale) * LayerNorm(x_f32) + shift, rows x hidden. */
 int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
                     const float *scale, int f16 /* out in f16 instead of bf16 */);
+/* K8, the VAE's convolution (flux_conv2d, flux_kernels.c:342-505, for 3x3 / stride 1 / padding 1): channels-last
+ * x16 [n_img, H, W, cin] (cin a multiple of 64), w16 [cout, 9, cin] (tap-major; cout a multiple of 128), bias f32
+ * [cout] or NULL. mode 0: out16[pixel, co]; 1: out32[pixel, co]; 2: out32[pixel, co] += ...; 3: uint8 RGB from
+ * output channels 0..2 as (v + 1) * 127.5 clamped and truncated. ld: row pitch of out in elements. */
+int flux_cuda_conv3x3(flux_cuda_ctx *ctx, const void *x16, int n_img, int H, int W, int cin, const void *w16, int cout,
+                      const float *bias, int mode, void *out, long long ld, int f16);
+/* The same kernel as a plain GEMM with a bias: out[M, N] = x16[M, K] * w16[N, K]^T + bias (modes 0-2). Only the first
+ * w_rows rows of w16 are read; the rest count as zero. 1x1 convolutions and the VAE attention block's products. */
+int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, const void *w16, long long ldw, int M, int N,
+                        int K, int w_rows, const float *bias, int mode, void *out, long long ld, int f16);
+/* GroupNorm with 32 groups over channels-last x [n_img, pixels, C] (f32, or 16-bit when in16 != 0), optional swish,
+ * 16-bit result (flux_group_norm, flux_kernels.c:511-553; swish_inplace, flux_vae.c:174-177). n_img <= 8. */
+int flux_cuda_group_norm(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels, int C,
+                         const float *gamma, const float *beta, float eps, int swish, int f16);
 /* apply_qk_norm + apply_rope_2d (flux_transformer.c:1052-1106, 719-741) in place on bf16 Q and K. */
 int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
                            int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t);
