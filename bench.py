@@ -2,7 +2,7 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln|qwen3|vae [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv [...]            # one kernel, small memory (for ncu captures)
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
 (1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
@@ -231,6 +231,22 @@ def run_micro(args):
         gbs = rows * hid * 6.0 / ms / 1e6
         print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
                           gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    elif args.micro == "conv":
+        # K8 alone: 3x3 convolution, --size x --size pixels, --shape[1] -> --shape[2] channels (shape[0] unused),
+        # 16-bit channels-last in, f32 out (the upsampling convolutions of the VAE decoder).
+        side, cin, cout = args.size, args.shape[1], args.shape[2]
+        x = torch.randn(1, side, side, cin, device="cuda").to(torch.float16)
+        w = (torch.randn(cout, 9 * cin, device="cuda") * 0.02).to(torch.float16)
+        b = torch.randn(cout, device="cuda")
+        out = torch.zeros(side * side, cout, device="cuda")
+        torch.cuda.synchronize()
+        ms = timed(lambda: ctx.conv3x3(x.data_ptr(), 1, side, side, cin, w.data_ptr(), cout, b.data_ptr(), 1,
+                                       out.data_ptr(), cout))
+        tf = 2.0 * 9 * cin * cout * side * side / ms / 1e9
+        algo = side * side * (cin * 2 + cout * 4) + w.numel() * 2
+        print(json.dumps({"micro": "conv", "pixels": [side, side], "cin": cin, "cout": cout, "ms": ms, "tflops": tf,
+                          "frac_of_burst_peak": tf / peaks["bf16"], "algorithmic_bytes": algo,
+                          "peak_source": peaks["source"]}))
     elif args.micro == "vae":
         # The VAE decoder on a --size x --size image (latent size/16): device time with the latent resident, and the
         # host-buffer call (latent in, uint8 RGB out).
@@ -342,12 +358,48 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     barrier()
     enc_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     finite = bool(torch.isfinite(out).all())
+
+    # the same plus the VAE decoder: the latent goes from the sampler to the decoder on the device, the 512x512 RGB
+    # image (786 KB) is what returns to the host
+    vae = fx.Vae.from_tensors(ctx, synth.make_vae_weights(seed=5, rich=True))
+    rgb = torch.zeros(16 * H_LAT * 16 * W_LAT * 3, dtype=torch.uint8).pin_memory()
+
+    def one_image(i):
+        sampler.upload(z0.data_ptr(), enc.forward_device(ids[i % len(ids)]))
+        sampler.run(sched)
+        vae.decode_ptr(sampler.latent_device(), H_LAT, W_LAT, rgb.data_ptr())  # waits for the image
+
+    for i in range(3):
+        one_image(i)
+    barrier()
+    with torch.cuda.stream(stream):
+        e0.record()
+    for i in range(args.steps):
+        one_image(i)
+    with torch.cuda.stream(stream):
+        e1.record()
+    barrier()
+    img_ms = max_over_ranks(e0.elapsed_time(e1))
+    with torch.cuda.stream(stream):
+        e0.record()
+    for i in range(args.steps):
+        vae.decode_device(sampler.latent_device(), H_LAT, W_LAT)
+    with torch.cuda.stream(stream):
+        e1.record()
+    barrier()
+    vae_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    img_std = float(rgb.float().std())
+    vae.close()
     enc.close()
     return {"workload": "per image: %d token ids -> Qwen3-4B-shaped encoder (27 of 36 layers: the ones the output "
             "depends on) -> 4 DiT steps at 512x512 -> latent on the host" % TXT, "value": args.steps * world / (ms * 1e-3),
             "unit": "images/s", "ms_per_image": ms / args.steps, "text_encoder_ms": enc_ms,
             "h2d_bytes_per_image": int(TXT * 4 + z0.numel() * 4), "d2h_bytes_per_image": int(out.numel() * 4),
-            "finite": finite}
+            "finite": finite,
+            "prompt_to_image": {"workload": "the same, then the VAE decoder on the device; a 512x512 uint8 RGB image "
+                                "returns to the host", "value": args.steps * world / (img_ms * 1e-3), "unit": "images/s",
+                                "ms_per_image": img_ms / args.steps, "vae_decode_ms": vae_ms,
+                                "d2h_bytes_per_image": int(rgb.numel()), "image_std": img_std}}
 
 
 # ---------------------------------------------------------------------------------------------- main arm
@@ -560,7 +612,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--seq", type=int, default=1536)

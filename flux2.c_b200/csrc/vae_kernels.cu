@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256) gn_stats_kernel(const void *__restrict__ 
   const int qd = threadIdx.x % quads, pl = threadIdx.x / quads;
   const size_t base = static_cast<size_t>(img) * pixels * C;
   float s = 0.f, ss = 0.f;
-  for (long long p = static_cast<long long>(blockIdx.x) * lanes + pl; p < pixels; p += static_cast<long long>(nblk) * lanes) {
+  auto load4 = [&](long long p) {
     float4 v;
     if (IN16) {
       const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(xv) + base + p * C + qd * 4);
@@ -101,9 +101,22 @@ __global__ void __launch_bounds__(256) gn_stats_kernel(const void *__restrict__ 
     } else {
       v = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(xv) + base + p * C + qd * 4);
     }
+    return v;
+  };
+  auto add4 = [&](const float4 &v) {
     s += (v.x + v.y) + (v.z + v.w);
     ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+  };
+  const long long stride = static_cast<long long>(nblk) * lanes;
+  long long p = static_cast<long long>(blockIdx.x) * lanes + pl;
+  for (; p + 3 * stride < pixels; p += 4 * stride) {  // four independent loads in flight per thread
+    const float4 a = load4(p), b = load4(p + stride), c = load4(p + 2 * stride), d = load4(p + 3 * stride);
+    add4(a);
+    add4(b);
+    add4(c);
+    add4(d);
   }
+  for (; p < pixels; p += stride) add4(load4(p));
   ps[threadIdx.x] = s;
   pss[threadIdx.x] = ss;
   __syncthreads();
@@ -126,20 +139,28 @@ __global__ void __launch_bounds__(256) gn_stats_kernel(const void *__restrict__ 
   __syncthreads();
   if (!last) return;
   __threadfence();
-  if (threadIdx.x < GN_GROUPS) {
-    const int g = threadIdx.x;
+  {
+    // eight threads per group, each over every eighth block in ascending order, then a fixed-order shuffle fold
+    const int g = threadIdx.x >> 3, sub = threadIdx.x & 7;
     double a = 0.0, b = 0.0;
     const float *pp = partial + static_cast<size_t>(img) * GN_MAX_BLOCKS * 64;
-    for (int k = 0; k < nblk; ++k) {
+    for (int k = sub; k < nblk; k += 8) {
       a += static_cast<double>(__ldcg(pp + k * 64 + 2 * g));
       b += static_cast<double>(__ldcg(pp + k * 64 + 2 * g + 1));
     }
-    const double n = static_cast<double>(pixels) * cpg;
-    const double mean = a / n;
-    double var = b / n - mean * mean;
-    if (var < 0.0) var = 0.0;
-    stats[(img * GN_GROUPS + g) * 2] = static_cast<float>(mean);
-    stats[(img * GN_GROUPS + g) * 2 + 1] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (sub == 0) {
+      const double n = static_cast<double>(pixels) * cpg;
+      const double mean = a / n;
+      double var = b / n - mean * mean;
+      if (var < 0.0) var = 0.0;
+      stats[(img * GN_GROUPS + g) * 2] = static_cast<float>(mean);
+      stats[(img * GN_GROUPS + g) * 2 + 1] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
+    }
   }
   if (threadIdx.x == 0) counters[img] = 0;
 }
@@ -149,7 +170,7 @@ int launch_gn_stats(const void *x, int in16, int f16, int n_img, long long pixel
   if (C % 128 || C > 1024 || 256 % (C >> 2) || pixels < 1) return -1;
   const int lanes = 256 / (C >> 2);
   long long nb = (pixels + lanes - 1) / lanes;
-  const long long cap = n_img > 1 ? 148 : 296;
+  const long long cap = n_img > 1 ? 296 : 592;  // four resident blocks per SM for one image
   if (nb > cap) nb = cap;
   if (nb > GN_MAX_BLOCKS) nb = GN_MAX_BLOCKS;
   const dim3 grid(static_cast<unsigned>(nb), n_img), block(256);

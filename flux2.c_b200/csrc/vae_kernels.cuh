@@ -7,7 +7,7 @@
 namespace fx {
 
 static constexpr int GN_GROUPS = 32;
-static constexpr int GN_MAX_BLOCKS = 512;  // per image; size of the partial-sum scratch is n_img * this * 64 floats
+static constexpr int GN_MAX_BLOCKS = 640;  // per image; size of the partial-sum scratch is n_img * this * 64 floats
 
 // latent f32 [n_img, 128, h, w] -> per-channel de-normalisation x * sqrt(var + eps) + mean -> 2x2 depth-to-space
 // -> 1x1 convolution 32 -> 32 (wq [32, 32] f32, bq [32]) -> out16 [n_img, 2h, 2w, 64], channels 32..63 zero

@@ -67,7 +67,8 @@ class RefLib:
             _preload("libquadmath-2284e583")
             _preload("libgfortran-83c28eba")
             _preload("libopenblasp-")
-        self.L = L = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+        # local scope (and -Bsymbolic at link time): several builds of the same sources can live in one process
+        self.L = L = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
         self.libc = ctypes.CDLL(None)
         self.libc.free.argtypes = [ctypes.c_void_p]
         vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
@@ -105,6 +106,12 @@ class RefLib:
         L.qwen3_model_free.argtypes = [vp]
         L.qwen3_forward.restype = vp
         L.qwen3_forward.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ci]
+        if kind == "seam":
+            # the seam redirects these three at link time (-Wl,--wrap); calls from outside the library must name the
+            # wrappers themselves to take the path the library's own callers take
+            L.flux_vae_load_safetensors = getattr(L, "__wrap_flux_vae_load_safetensors")
+            L.flux_vae_decode = getattr(L, "__wrap_flux_vae_decode")
+            L.flux_vae_free = getattr(L, "__wrap_flux_vae_free")
         L.flux_vae_load_safetensors.restype = vp
         L.flux_vae_load_safetensors.argtypes = [vp]
         L.flux_vae_free.argtypes = [vp]

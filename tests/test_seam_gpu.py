@@ -90,3 +90,25 @@ def test_seam_text_encoder_loads_shards_and_matches_reference(seam, scratch):
         seam.L.qwen3_model_free(m)
     with pytest.raises(RuntimeError):
         seam.qwen3_load(os.path.join(scratch, "no_such_dir"))
+
+
+def test_seam_vae_decode_is_served_by_the_engine(seam, scratch, fx, ctx):
+    """flux_vae_load_safetensors / flux_vae_decode as the library's own callers reach them (redirected at link time):
+    the image must match the CPU restatement of the reference's decoder, and be the engine's own result bit for bit."""
+    import flux2_c_b200.synth as synth
+    from oracle.vae_oracle import VaeOracle
+    W = synth.make_vae_weights(seed=5, rich=True)
+    path = os.path.join(scratch, "vae.safetensors")
+    synth.write_safetensors(path, W, dtype="F32")
+    vae = seam.load_vae(path)
+    try:
+        lat = synth.make_latent(11, 128, 6, 5)
+        got = seam.vae_decode(vae, lat)
+        want, _ = VaeOracle(W).decode(lat)
+        mse = float(((got.astype(np.float64) - want.astype(np.float64)) ** 2).mean())
+        assert 10.0 * np.log10(255.0 ** 2 / max(mse, 1e-12)) >= 40.0
+        direct = fx.Vae.from_tensors(ctx, W)
+        assert np.array_equal(direct.decode(lat), got)
+        direct.close()
+    finally:
+        seam.L.flux_vae_free(vae)
