@@ -107,6 +107,8 @@ def _declare(L):
     L.flux_cuda_group_norm.restype = c_int
     L.flux_cuda_group_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, ctypes.c_longlong, c_int, c_void_p,
                                        c_void_p, ctypes.c_float, c_int, c_int]
+    L.flux_cuda_group_norm_noalloc.restype = c_int
+    L.flux_cuda_group_norm_noalloc.argtypes = L.flux_cuda_group_norm.argtypes
     L.flux_cuda_qwen3_forward_device.restype = c_int
     L.flux_cuda_qwen3_forward_device.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
                                                  ctypes.POINTER(c_void_p)]
@@ -266,6 +268,10 @@ class Context:
     def group_norm(self, x_ptr, in16, out_ptr, n_img, pixels, C, gamma_ptr, beta_ptr, eps, swish, f16=True):
         check(lib().flux_cuda_group_norm(self.handle, x_ptr, int(in16), out_ptr, n_img, pixels, C, gamma_ptr, beta_ptr,
                                          eps, int(swish), int(f16)))
+
+    def group_norm_noalloc(self, x_ptr, in16, out_ptr, n_img, pixels, C, gamma_ptr, beta_ptr, eps, swish, f16=True):
+        check(lib().flux_cuda_group_norm_noalloc(self.handle, x_ptr, int(in16), out_ptr, n_img, pixels, C, gamma_ptr,
+                                                 beta_ptr, eps, int(swish), int(f16)))
 
     def patchify(self, out_ptr, in_ptr, batch, channels, H, W, patch):
         check(lib().flux_cuda_patchify(self.handle, out_ptr, in_ptr, batch, channels, H, W, patch))

@@ -312,6 +312,15 @@ int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, cons
  * 16-bit result (flux_group_norm, flux_kernels.c:511-553; swish_inplace, flux_vae.c:174-177). n_img <= 8. */
 int flux_cuda_group_norm(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels, int C,
                          const float *gamma, const float *beta, float eps, int swish, int f16);
+/* The same operation for callers that must not allocate: hosts that gave all device memory to their own pool at
+ * start-up, or loops that cannot tolerate an allocation's device-wide synchronisation. No counterpart in the
+ * reference (it has no device memory to manage). The reduction scratch is a fixed array inside the library image
+ * (641 KB per device), so this call performs no allocation at all, on the device or through any library.
+ * Limits: n_img <= 4 per call (larger is rejected with FLUX_CUDA_ERR_ARG); the scratch is one per device and shared by
+ * every call on it, so calls that overlap in time (other streams or threads) race - serialise them. The first call on
+ * a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream capture begins. */
+int flux_cuda_group_norm_noalloc(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels,
+                                 int C, const float *gamma, const float *beta, float eps, int swish, int f16);
 /* apply_qk_norm + apply_rope_2d (flux_transformer.c:1052-1106, 719-741) in place on bf16 Q and K. */
 int flux_cuda_qk_norm_rope(flux_cuda_ctx *ctx, void *qkv, long long ld, int q_col, int k_col, int seq, int batch,
                            int heads, const float *wq, const float *wk, const float *cos_t, const float *sin_t);
