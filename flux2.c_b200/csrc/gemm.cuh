@@ -64,12 +64,15 @@ struct alignas(64) GemmParams {
 
 // Fills the tensor maps and tile counts of `p` for tile width bn (128 or 256). Returns 0 on success.
 // ldx = row pitch of X in elements (>= K), so X may be a column slice of a wider buffer.
-int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn);
+// ldw = row pitch of W in elements (0: K), so W may be a K-slice of a wider matrix (split-K).
+int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn,
+                      long long ldw = 0);
 // Launches the persistent kernel over P.nprob problems. bn must match gemm_make_problem.
 int gemm_launch(GemmParams *P, int bn, int num_sms, cudaStream_t stream);
 // Paired variant (gemm2_tcgen05.cu): two CTAs per 256 x 256 tile, tile width fixed at 256.
 int gemm2_init();
-int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K);
+int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K,
+                           long long ldw = 0);
 int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream);
 int gemm_init();  // resolves cuTensorMapEncodeTiled and opts the kernels into large shared memory
 

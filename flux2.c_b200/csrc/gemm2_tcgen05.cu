@@ -210,11 +210,13 @@ int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
              : -8;
 }
 
-int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K) {
-  if (M <= 0 || N <= 0 || K <= 0 || (K % P_BK) || (N % P_BN) || ldx < K) return -5;
+int gemm_make_problem_pair(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K,
+                           long long ldw) {
+  if (ldw == 0) ldw = K;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % P_BK) || (N % P_BN) || ldx < K || ldw < K) return -5;
   int rc = make_tmap_2d_bf16(&p->tmA, X, M, K, ldx, P_BM, P_BK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&p->tmB, W, N, K, K, P_BN / 2, P_BK);
+  rc = make_tmap_2d_bf16(&p->tmB, W, N, K, ldw, P_BN / 2, P_BK);
   if (rc) return rc;
   p->M = M;
   p->N = N;

@@ -231,11 +231,13 @@ int make_tmap_2d_bf16(CUtensorMap *m, const void *base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -4;
 }
 
-int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn) {
-  if (M <= 0 || N <= 0 || K <= 0 || (K % BK) || (N % bn) || (bn != 128 && bn != 256) || ldx < K) return -5;
+int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn,
+                      long long ldw) {
+  if (ldw == 0) ldw = K;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % BK) || (N % bn) || (bn != 128 && bn != 256) || ldx < K || ldw < K) return -5;
   int rc = make_tmap_2d_bf16(&p->tmA, X, M, K, ldx, BM, BK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&p->tmB, W, N, K, K, bn, BK);
+  rc = make_tmap_2d_bf16(&p->tmB, W, N, K, ldw, bn, BK);
   if (rc) return rc;
   p->M = M;
   p->N = N;

@@ -7,6 +7,7 @@
 // all 36, its GPU path stops at the same layer).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <set>
@@ -42,23 +43,42 @@ __global__ void embed_gather_kernel(const uint16_t *__restrict__ table, const in
 }
 
 // RMSNorm: out_16[r, :] = x[r, :] * rsqrt(mean(x^2) + 1e-6) * w (qwen3_rms_norm, flux_qwen3.c:176-196).
-// One warp per row, the row stays in registers between the two passes.
+// One warp per row, the row stays in registers between the two passes. With nsplit > 0 the row first receives the
+// partial products of the preceding split-K projection, x[r, :] += sum_s part[s][r, :] (in ascending s, so the
+// result does not depend on scheduling), and is written back: the residual add of that projection. out == nullptr
+// stops after the add.
 template <int VPL>
-__global__ void __launch_bounds__(128, 3) rmsnorm_kernel(const float *__restrict__ x, uint16_t *__restrict__ out,
-                                                         const float *__restrict__ w, int rows, int hidden, int f16) {
+__global__ void __launch_bounds__(128, 3) rmsnorm_kernel(float *__restrict__ x, uint16_t *__restrict__ out,
+                                                         const float *__restrict__ w, int rows, int hidden, int f16,
+                                                         const float *__restrict__ part, int nsplit, long long pstride) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
-  const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * hidden);
+  float4 *xr = reinterpret_cast<float4 *>(x + static_cast<size_t>(row) * hidden);
   float4 v[VPL];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    v[i] = xr[i * 32 + lane];
-    ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+  for (int i = 0; i < VPL; ++i) v[i] = xr[i * 32 + lane];
+  if (nsplit > 0) {
+    for (int s = 0; s < nsplit; ++s) {
+      const float4 *pr = reinterpret_cast<const float4 *>(part + s * pstride + static_cast<size_t>(row) * hidden);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const float4 a = pr[i * 32 + lane];
+        v[i].x += a.x;
+        v[i].y += a.y;
+        v[i].z += a.z;
+        v[i].w += a.w;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) xr[i * 32 + lane] = v[i];
+    if (!out) return;
   }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
   const float rinv = rsqrtf(warp_sum(ss) / static_cast<float>(hidden) + 1e-6f);
   const float4 *w4 = reinterpret_cast<const float4 *>(w);
   uint2 *o2 = reinterpret_cast<uint2 *>(out + static_cast<size_t>(row) * hidden);
@@ -70,17 +90,20 @@ __global__ void __launch_bounds__(128, 3) rmsnorm_kernel(const float *__restrict
   }
 }
 
-static int launch_rmsnorm(const float *x, void *out, const float *w, int rows, int hidden, int f16, cudaStream_t st) {
+static int launch_rmsnorm(float *x, void *out, const float *w, int rows, int hidden, int f16, const float *part,
+                          int nsplit, long long pstride, cudaStream_t st) {
   const dim3 grid((rows + 3) / 4), block(128);
   uint16_t *o = reinterpret_cast<uint16_t *>(out);
   cudaError_t e;
+#define RMS_LAUNCH(V) launch_kernel(rmsnorm_kernel<V>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16, part, nsplit, pstride)
   switch (hidden) {
-    case 2560: e = launch_kernel(rmsnorm_kernel<20>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16); break;
-    case 256: e = launch_kernel(rmsnorm_kernel<2>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16); break;
-    case 512: e = launch_kernel(rmsnorm_kernel<4>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16); break;
-    case 1024: e = launch_kernel(rmsnorm_kernel<8>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16); break;
+    case 2560: e = RMS_LAUNCH(20); break;
+    case 256: e = RMS_LAUNCH(2); break;
+    case 512: e = RMS_LAUNCH(4); break;
+    case 1024: e = RMS_LAUNCH(8); break;
     default: return -1;
   }
+#undef RMS_LAUNCH
   return e == cudaSuccess ? 0 : -8;
 }
 
@@ -108,7 +131,8 @@ struct flux_cuda_qwen3 {
   size_t expected = 0;
   bool finalized = false;
   // workspace for max_seq tokens
-  float *hidden = nullptr, *out = nullptr, *ones = nullptr, *cos_t = nullptr, *sin_t = nullptr;
+  float *hidden = nullptr, *out = nullptr, *ones = nullptr, *cos_t = nullptr, *sin_t = nullptr, *part = nullptr;
+  bool split_k = true;  // FLUX_CUDA_QWEN_SPLITK=0: every projection as one problem
   uint16_t *norm = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr;
   int *ids = nullptr;
   uint32_t *mask = nullptr;
@@ -198,6 +222,8 @@ int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims,
   m->staging = stg;
   if (!rc) rc = q_alloc(m, &m->hidden, S * h);
   if (!rc) rc = q_alloc(m, &m->out, S * 3 * h);
+  if (!rc) rc = q_alloc(m, &m->part, GEMM_MAX_PROBLEMS * S * h);
+  if (const char *e = getenv("FLUX_CUDA_QWEN_SPLITK")) m->split_k = atoi(e) != 0;
   if (!rc) rc = q_alloc(m, &m->ones, h);
   if (!rc) rc = q_alloc(m, &m->cos_t, S * 64);
   if (!rc) rc = q_alloc(m, &m->sin_t, S * 64);
@@ -371,6 +397,53 @@ static int q_gemm(flux_cuda_qwen3 *m, const void *X, long long ldx, const void *
   return pair ? gemm2_launch(&P, m->ctx->num_sms, m->ctx->stream) : gemm_launch(&P, 256, m->ctx->num_sms, m->ctx->stream);
 }
 
+// Residual projection hidden += X[M, K] * W[h, K]^T. A plain launch has only ceil(M / 256) * h / 256 output tiles
+// (20 at 512 tokens) for 74 SM pairs, each with a long K loop. When at least two K-slices fit on the idle pairs, K is
+// cut into up to four slices that run as independent problems of ONE launch and store f32 partial products; the next
+// RMSNorm pass adds them to the residual stream in slice order (deterministic, no atomics). Returns the number of
+// slices written to m->part (0: accumulated directly), or a negative launch error.
+static int q_residual_gemm(flux_cuda_qwen3 *m, const void *X, long long ldx, const uint16_t *W, int M, int K) {
+  const int h = m->d.hidden;
+  const bool pair = m->ctx->gemm_pair;
+  const int units = pair ? m->ctx->num_sms / 2 : m->ctx->num_sms;
+  const int tiles = ((M + (pair ? 255 : 127)) / (pair ? 256 : 128)) * (h / 256);
+  const int KB = K / 64;
+  int S = m->split_k ? units / tiles : 1;
+  if (S > GEMM_MAX_PROBLEMS) S = GEMM_MAX_PROBLEMS;
+  if (S > KB) S = KB;
+  EpiSeg sg;
+  memset(&sg, 0, sizeof(sg));
+  sg.out_f16 = m->f16;
+  sg.ld = h;
+  if (S < 2) {
+    sg.mode = EPI_GATED_RES_F32;
+    sg.out = m->hidden;
+    sg.gate = m->ones;
+    int rc = q_gemm(m, X, ldx, W, M, h, K, sg);
+    return rc ? (rc < 0 ? rc : -rc) : 0;
+  }
+  GemmParams P;
+  memset(&P, 0, sizeof(P));
+  P.nprob = S;
+  P.err = m->ctx->err_dev;
+  int kb0 = 0;
+  for (int s = 0; s < S; ++s) {
+    const int kbs = KB / S + (s < KB % S ? 1 : 0);
+    const uint16_t *Xs = reinterpret_cast<const uint16_t *>(X) + static_cast<size_t>(kb0) * 64;
+    const uint16_t *Ws = W + static_cast<size_t>(kb0) * 64;
+    int rc = pair ? gemm_make_problem_pair(&P.p[s], Xs, ldx, Ws, M, h, kbs * 64, K)
+                  : gemm_make_problem(&P.p[s], Xs, ldx, Ws, M, h, kbs * 64, 256, K);
+    if (rc) return rc < 0 ? rc : -rc;
+    P.p[s].x_f16 = m->f16;
+    sg.mode = EPI_STORE_F32;
+    sg.out = m->part + static_cast<size_t>(s) * m->max_seq * h;
+    P.p[s].seg[0] = sg;
+    kb0 += kbs;
+  }
+  int rc = pair ? gemm2_launch(&P, m->ctx->num_sms, m->ctx->stream) : gemm_launch(&P, 256, m->ctx->num_sms, m->ctx->stream);
+  return rc ? (rc < 0 ? rc : -rc) : S;
+}
+
 // Queues the whole pass on the context's stream; the result is m->out ([seq, 3 * hidden] f32, device).
 static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq) {
   if (!m || !input_ids || seq < 1) {
@@ -412,9 +485,12 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
   };
   int gr = 0;
   int next_out = 0;
+  int pending = 0;  // K-slices of the last residual projection still to be added to the residual stream
+  const long long pstride = static_cast<long long>(m->max_seq) * h;
   for (int l = 0; l < m->run_layers && !gr; ++l) {
     const QwenLayer &w = m->layers[l];
-    gr = launch_rmsnorm(m->hidden, m->norm, w.ln1, seq, h, f16, st);
+    gr = launch_rmsnorm(m->hidden, m->norm, w.ln1, seq, h, f16, m->part, pending, pstride, st);
+    pending = 0;
     if (gr) break;
     EpiSeg sq = seg(EPI_QKV_NORM_ROPE, m->qkv, qkv_n, 0, nullptr);
     sq.qk.wq_txt = sq.qk.wq_img = w.qn;
@@ -437,15 +513,28 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
     A.key_mask = m->mask;
     gr = attn2_launch(&A, st);
     if (gr) break;
-    gr = q_gemm(m, m->attn, qd, w.o, seq, h, qd, seg(EPI_GATED_RES_F32, m->hidden, h, 0, m->ones));
-    if (gr) break;
-    gr = launch_rmsnorm(m->hidden, m->norm, w.ln2, seq, h, f16, st);
+    pending = q_residual_gemm(m, m->attn, qd, w.o, seq, qd);
+    if (pending < 0) {
+      gr = pending;
+      break;
+    }
+    gr = launch_rmsnorm(m->hidden, m->norm, w.ln2, seq, h, f16, m->part, pending, pstride, st);
+    pending = 0;
     if (gr) break;
     gr = q_gemm(m, m->norm, h, w.gateup, seq, 2 * it, h, seg(EPI_SWIGLU_BF16, m->act, it, 0, nullptr));
     if (gr) break;
-    gr = q_gemm(m, m->act, it, w.down, seq, h, it, seg(EPI_GATED_RES_F32, m->hidden, h, 0, m->ones));
-    if (gr) break;
-    if (next_out < 3 && l == d.out_layers[next_out]) {
+    pending = q_residual_gemm(m, m->act, it, w.down, seq, it);
+    if (pending < 0) {
+      gr = pending;
+      break;
+    }
+    const bool collect = next_out < 3 && l == d.out_layers[next_out];
+    if (pending > 0 && (collect || l + 1 == m->run_layers)) {  // nobody after this layer folds the slices: do it now
+      gr = launch_rmsnorm(m->hidden, nullptr, w.ln1, seq, h, f16, m->part, pending, pstride, st);
+      pending = 0;
+      if (gr) break;
+    }
+    if (collect) {
       rc = check_cuda(cudaMemcpy2DAsync(m->out + static_cast<size_t>(next_out) * h, 3 * h * sizeof(float), m->hidden,
                                         h * sizeof(float), h * sizeof(float), seq, cudaMemcpyDeviceToDevice, st),
                       "collect layer output");
@@ -456,7 +545,7 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
   if (gr) {
     set_error("qwen3_forward: kernel launch failed (rc %d, cuda: %s)", gr, cudaGetErrorString(cudaGetLastError()));
     ctx_sync_check(m->ctx);
-    return gr == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
+    return (gr == -1 || gr == -5) ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
   }
   return FLUX_CUDA_OK;
 }
