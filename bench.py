@@ -313,20 +313,42 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     import numpy as np
     import torch
     qd = synth.QwenDims(layers=27)
+
+    def all_ok(ok):
+        # every rank calls this the same number of times, whether its own part worked or not, so that a failure on
+        # one rank ends the leg everywhere instead of leaving the others waiting in a barrier
+        if world == 1:
+            return ok
+        t = torch.tensor([1.0 if ok else 0.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item() > 0.5)
+
+    enc, err = None, None
     if world == 1:
         enc = fx.TextEncoder.from_tensors(ctx, qd, synth.make_qwen_weights(qd, seed=0, threads=os.cpu_count()),
                                           max_seq=TXT)
     else:
         shm = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
         mdir = os.path.join(shm, "flux_bench_qwen_%s" % os.environ.get("MASTER_PORT", "0"))
-        if rank == 0:
-            synth.write_qwen_shards(mdir, synth.make_qwen_weights(qd, seed=0, threads=os.cpu_count()))
-        dist.barrier()
-        enc = fx.TextEncoder.load_dir(ctx, mdir, max_seq=TXT)
-        dist.barrier()
+        try:
+            if rank == 0:
+                synth.write_qwen_shards(mdir, synth.make_qwen_weights(qd, seed=0, threads=os.cpu_count()))
+        except Exception as e:
+            err = e
+        wrote = all_ok(err is None)
+        try:
+            if wrote:
+                enc = fx.TextEncoder.load_dir(ctx, mdir, max_seq=TXT)
+        except Exception as e:
+            err = e
+        loaded = all_ok(wrote and enc is not None)
         if rank == 0:
             import shutil
             shutil.rmtree(mdir, ignore_errors=True)
+        if not loaded:
+            if enc is not None:
+                enc.close()
+            raise RuntimeError("text encoder set-up failed on some rank: %r" % (err,))
     rng = np.random.default_rng(1000 + rank)
     ids = [rng.integers(0, qd.vocab, TXT).astype(np.int32) for _ in range(args.steps)]
 
