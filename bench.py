@@ -2,7 +2,7 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv|load [...]            # one kernel, small memory (for ncu captures)
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
 (1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
@@ -231,6 +231,27 @@ def run_micro(args):
         gbs = rows * hid * 6.0 / ms / 1e6
         print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
                           gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    elif args.micro == "load":
+        # Load time of the klein-4B-shaped transformer file (7.75 GB, bf16) through the engine's safetensors loader:
+        # map, validate, copy, convert bf16 -> f16 and re-lay on the device. The file sits in RAM-backed storage, so
+        # this is the loader's own cost, not a disk's.
+        synth = importlib.import_module("flux2_c_b200.synth")
+        dims = synth.Dims.klein4b()
+        shm = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
+        path = os.path.join(shm, "flux_bench_load_%d.safetensors" % os.getpid())
+        synth.write_safetensors(path, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
+        size = os.path.getsize(path)
+        times = []
+        try:
+            for _ in range(max(2, min(iters, 3))):
+                t0 = time.perf_counter()
+                model = fx.Model.load_safetensors(ctx, path)
+                ctx.sync()
+                times.append(time.perf_counter() - t0)
+                model.close()
+        finally:
+            os.remove(path)
+        print(json.dumps({"micro": "load", "file_gb": size / 1e9, "seconds": times, "best_gb_per_s": size / 1e9 / min(times)}))
     elif args.micro == "conv":
         # K8 alone: 3x3 convolution, --size x --size pixels, --shape[1] -> --shape[2] channels (shape[0] unused),
         # 16-bit channels-last in, f32 out (the upsampling convolutions of the VAE decoder).
@@ -634,7 +655,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "load"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--seq", type=int, default=1536)

@@ -94,6 +94,10 @@ def _declare(L):
     L.flux_cuda_vae_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
     L.flux_cuda_vae_decode_device.restype = c_int
     L.flux_cuda_vae_decode_device.argtypes = [c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_vae_encode.restype = c_int
+    L.flux_cuda_vae_encode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
+    L.flux_cuda_vae_has_encoder.restype = c_int
+    L.flux_cuda_vae_has_encoder.argtypes = [c_void_p]
     L.flux_cuda_vae_last_launches.restype = ctypes.c_longlong
     L.flux_cuda_vae_last_launches.argtypes = [c_void_p]
     L.flux_cuda_sampler_latent_device.restype = c_int
@@ -101,6 +105,8 @@ def _declare(L):
     L.flux_cuda_conv3x3.restype = c_int
     L.flux_cuda_conv3x3.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, ctypes.c_longlong, c_int]
+    L.flux_cuda_conv3x3_stride2.restype = c_int
+    L.flux_cuda_conv3x3_stride2.argtypes = L.flux_cuda_conv3x3.argtypes
     L.flux_cuda_gemm_bias.restype = c_int
     L.flux_cuda_gemm_bias.argtypes = [c_void_p, c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_int, c_int,
                                       c_int, c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int]
@@ -257,9 +263,9 @@ class Context:
     def adaln(self, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, f16=False):
         check(lib().flux_cuda_adaln(self.handle, x_ptr, out_ptr, rows, hidden, shift_ptr, scale_ptr, int(f16)))
 
-    def conv3x3(self, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld, f16=True):
-        check(lib().flux_cuda_conv3x3(self.handle, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld,
-                                      int(f16)))
+    def conv3x3(self, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld, f16=True, stride2=False):
+        fn = lib().flux_cuda_conv3x3_stride2 if stride2 else lib().flux_cuda_conv3x3
+        check(fn(self.handle, x_ptr, n_img, H, W, cin, w_ptr, cout, bias_ptr, mode, out_ptr, ld, int(f16)))
 
     def gemm_bias(self, x_ptr, ldx, w_ptr, ldw, M, N, K, bias_ptr, mode, out_ptr, ld, w_rows=None, f16=True):
         check(lib().flux_cuda_gemm_bias(self.handle, x_ptr, ldx, w_ptr, ldw, M, N, K, N if w_rows is None else w_rows,
@@ -506,6 +512,18 @@ class Vae:
         out = np.empty((16 * h, 16 * w, 3), dtype=np.uint8)
         check(lib().flux_cuda_vae_decode(self.handle, lat.ctypes.data, h, w, out.ctypes.data))
         return out
+
+    def encode(self, image):
+        """image f32 [3, H, W] in [-1, 1] -> latent f32 [128, H/16, W/16]."""
+        np = _np()
+        img = np.ascontiguousarray(image, dtype=np.float32)
+        _, H, W = img.shape
+        out = np.empty((128, H // 16, W // 16), dtype=np.float32)
+        check(lib().flux_cuda_vae_encode(self.handle, img.ctypes.data, H, W, out.ctypes.data))
+        return out
+
+    def has_encoder(self):
+        return bool(lib().flux_cuda_vae_has_encoder(self.handle))
 
     def decode_ptr(self, latent_ptr, h, w, rgb_host_ptr):
         """latent_ptr: host or device address of f32 [128, h, w]; rgb_host_ptr: host address of uint8 [16h, 16w, 3]."""

@@ -287,6 +287,19 @@ int flux_cuda_conv3x3(flux_cuda_ctx *ctx, const void *x16, int n_img, int H, int
   return conv_finish(ctx, P, bias, mode, out, ld, f16, "conv3x3");
 }
 
+int flux_cuda_conv3x3_stride2(flux_cuda_ctx *ctx, const void *planes16, int n_img, int Ho, int Wo, int cin,
+                              const void *w16, int cout, const float *bias, int mode, void *out, long long ld, int f16) {
+  if (!ctx || !planes16 || !w16) return FLUX_CUDA_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  ConvParams P;
+  memset(&P, 0, sizeof(P));
+  if (conv_make_3x3_s2(&P, planes16, n_img, Ho, Wo, cin, w16, cout) != 0) {
+    set_error("conv3x3_stride2: unsupported shape (cin %% 64, cout %% 128, 16-byte aligned pointers)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  return conv_finish(ctx, P, bias, mode, out, ld, f16, "conv3x3_stride2");
+}
+
 int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, const void *w16, long long ldw, int M, int N,
                         int K, int w_rows, const float *bias, int mode, void *out, long long ld, int f16) {
   if (!ctx || !x16 || !w16) return FLUX_CUDA_ERR_ARG;

@@ -21,6 +21,7 @@ struct alignas(64) ConvParams {
   CUtensorMap tmA;  // taps == 9: {C, W, H, N} channels-last, box {64, BW, BH, 1}; taps == 1: [M, K], box {64, 128}
   CUtensorMap tmB;  // weights [Cout, taps * Cin] (tap-major, input channel minor), box {64, BN / 2}
   int taps;         // 9 or 1
+  int stride2;      // taps == 9 only: the input is stored as four parity planes (see conv_make_3x3_s2)
   int n_img, H, W;  // taps == 9
   int bw_log2;      // a CTA's 128 rows are a patch of 2^bw_log2 columns x (128 >> bw_log2) rows of pixels
   int tiles_x, tiles_y;
@@ -39,6 +40,12 @@ struct alignas(64) ConvParams {
 int conv_init();
 // x: [n_img, H, W, Cin] 16-bit; w: [Cout, 9 * Cin] 16-bit.
 int conv_make_3x3(ConvParams *p, const void *x, int n_img, int H, int W, int Cin, const void *w, int Cout);
+// 3x3 convolution with stride 2 over an input padded by one zero row at the bottom and one zero column at the right
+// (the VAE encoder's downsampling, flux_vae.c:146-171, 360-372): out[y, x] = sum in[2y + ky, 2x + kx]. The input is
+// given as parity planes, planes[(n * 4 + py * 2 + px), y, x, c] = in[n, 2y + py, 2x + px, c], each Ho x Wo pixels,
+// so that tap (ky, kx) is a stride-1 read of plane (ky & 1, kx & 1) shifted by (ky >> 1, kx >> 1); the shift past the
+// last row / column is the zero padding. Ho, Wo: output size.
+int conv_make_3x3_s2(ConvParams *p, const void *planes, int n_img, int Ho, int Wo, int Cin, const void *w, int Cout);
 // Y[M, N] = X[M, K] (row pitch ldx) * Wt[N, K]^T (row pitch ldw). Only the first w_rows rows of Wt exist in memory
 // (w_rows <= N): the columns of Y beyond them come out as the bias alone.
 int conv_make_gemm(ConvParams *p, const void *X, long long ldx, const void *Wt, long long ldw, int M, int N, int K,

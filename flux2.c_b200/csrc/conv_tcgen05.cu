@@ -187,7 +187,11 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
           if (P.taps == 9) {
             const int tap = kb / cb, c0 = (kb - tap * cb) * C_BK;
             const int ky = tap / 3, kx = tap - 3 * ky;
-            tma_load_4d_pair(sa, &P.tmA, full_leader, c0, tx * bw + kx - 1, ty * bh + ky - 1, img);
+            if (P.stride2)
+              tma_load_4d_pair(sa, &P.tmA, full_leader, c0, tx * bw + (kx >> 1), ty * bh + (ky >> 1),
+                               img * 4 + (ky & 1) * 2 + (kx & 1));
+            else
+              tma_load_4d_pair(sa, &P.tmA, full_leader, c0, tx * bw + kx - 1, ty * bh + ky - 1, img);
           } else {
             tma_load_2d_pair(sa, &P.tmA, full_leader, kb * C_BK, patch * C_BM);
           }
@@ -306,7 +310,21 @@ static void finish_tiles(ConvParams *p) {
   p->tiles_n = p->Cout / p->bn;
 }
 
+static int conv_make_3x3_impl(ConvParams *p, const void *x, int n_img, int H, int W, int Cin, const void *w, int Cout,
+                              int planes_per_img);
+
 int conv_make_3x3(ConvParams *p, const void *x, int n_img, int H, int W, int Cin, const void *w, int Cout) {
+  return conv_make_3x3_impl(p, x, n_img, H, W, Cin, w, Cout, 1);
+}
+
+int conv_make_3x3_s2(ConvParams *p, const void *planes, int n_img, int Ho, int Wo, int Cin, const void *w, int Cout) {
+  int rc = conv_make_3x3_impl(p, planes, n_img, Ho, Wo, Cin, w, Cout, 4);
+  if (!rc) p->stride2 = 1;
+  return rc;
+}
+
+static int conv_make_3x3_impl(ConvParams *p, const void *x, int n_img, int H, int W, int Cin, const void *w, int Cout,
+                              int planes_per_img) {
   if (!g_conv_encode && conv_init() != 0) return -1;
   const int bn = pick_bn(Cout);
   if (n_img < 1 || H < 1 || W < 1 || Cin < 64 || (Cin % 64) || !bn) return -5;
@@ -315,7 +333,7 @@ int conv_make_3x3(ConvParams *p, const void *x, int n_img, int H, int W, int Cin
   while (bl > 0 && (1 << bl) > W) --bl;
   const int bw = 1 << bl, bh = C_BM >> bl;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(Cin), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
-                        static_cast<cuuint64_t>(n_img)};
+                        static_cast<cuuint64_t>(n_img) * planes_per_img};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(Cin) * 2, static_cast<cuuint64_t>(W) * Cin * 2,
                            static_cast<cuuint64_t>(H) * W * Cin * 2};
   cuuint32_t box[4] = {C_BK, static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), 1};
@@ -327,6 +345,7 @@ int conv_make_3x3(ConvParams *p, const void *x, int n_img, int H, int W, int Cin
   int rc = make_tmap_2d_bf16(&p->tmB, w, Cout, 9ull * Cin, 9ull * Cin, bn / 2, C_BK);
   if (rc) return rc;
   p->taps = 9;
+  p->stride2 = 0;
   p->n_img = n_img;
   p->H = H;
   p->W = W;

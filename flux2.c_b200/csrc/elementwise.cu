@@ -359,4 +359,44 @@ int launch_cfg_euler(float *z, const float *v_cond, const float *v_uncond, float
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
+// ------------------------------------------------------------------------------------------------ 16-bit formats
+__device__ __forceinline__ uint32_t cvt16_pair(uint32_t u, bool to_f16) {
+  if (to_f16) {
+    const float lo = __uint_as_float(u << 16), hi = __uint_as_float(u & 0xFFFF0000u);
+    return pack_f16x2(lo, hi);
+  }
+  const float lo = __half2float(__ushort_as_half(static_cast<unsigned short>(u & 0xFFFFu)));
+  const float hi = __half2float(__ushort_as_half(static_cast<unsigned short>(u >> 16)));
+  return pack_bf16x2(lo, hi);
+}
+
+__global__ void __launch_bounds__(256) convert16_kernel(uint16_t *__restrict__ p, long long n, int to_f16) {
+  const long long n8 = n >> 3;
+  uint4 *p4 = reinterpret_cast<uint4 *>(p);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 v = p4[i];
+    v.x = cvt16_pair(v.x, to_f16 != 0);
+    v.y = cvt16_pair(v.y, to_f16 != 0);
+    v.z = cvt16_pair(v.z, to_f16 != 0);
+    v.w = cvt16_pair(v.w, to_f16 != 0);
+    p4[i] = v;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = n8 << 3; i < n; ++i) {  // at most seven trailing elements
+      const uint32_t r = cvt16_pair(static_cast<uint32_t>(p[i]), to_f16 != 0);
+      p[i] = static_cast<uint16_t>(r & 0xFFFFu);
+    }
+}
+
+int launch_convert16_inplace(void *p, long long n, int to_f16, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (reinterpret_cast<uintptr_t>(p) & 15) return -1;
+  long long nb = ((n >> 3) + 255) / 256;
+  if (nb < 1) nb = 1;
+  if (nb > 148 * 8) nb = 148 * 8;
+  convert16_kernel<<<static_cast<unsigned>(nb), 256, 0, st>>>(reinterpret_cast<uint16_t *>(p), n, to_f16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
 }  // namespace fx

@@ -21,6 +21,9 @@ int launch_gemv_multi(const void *W_16, const float *x, float *y, int R, int K, 
                       cudaStream_t st);
 int launch_pack_tokens(const float *z, void *tok_16, int C, int n, int f16, cudaStream_t st);
 int launch_f32_to_bf16(const float *in, void *out_16, long long n, int f16, cudaStream_t st);
+// In place, n 16-bit elements: bf16 -> f16 (to_f16 != 0; round to nearest even, saturating at +-65504) or f16 -> bf16.
+// The load-time format conversion of the weights, done on the device so that the host never walks over them.
+int launch_convert16_inplace(void *p, long long n, int to_f16, cudaStream_t st);
 // to_packed != 0: packed[B, C p p, H/p, W/p] = patchify(plain[B, C, H, W]); else the inverse.
 int launch_patchify(float *packed, float *plain, int batch, int C, int H, int W, int p, int to_packed, cudaStream_t st);
 int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st);

@@ -193,11 +193,31 @@ const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vec
   return tmp.data();
 }
 
+int upload_16(flux_cuda_ctx *ctx, void *dst, const void *data, int dtype, size_t off, size_t count, bool want_f16,
+              std::vector<uint16_t> &tmp) {
+  if (dtype == 0) {
+    const uint16_t *src = to_half_host(reinterpret_cast<const float *>(data) + off, 0, count, tmp, want_f16);
+    return check_cuda(upload_h2d(ctx->stream, dst, src, count * 2), "upload weights");
+  }
+  int rc = check_cuda(cudaMemcpyAsync(dst, reinterpret_cast<const uint16_t *>(data) + off, count * 2,
+                                      cudaMemcpyHostToDevice, ctx->stream),
+                      "upload weights");
+  if (rc) return rc;
+  const bool is_f16 = dtype == 1;
+  if (is_f16 != want_f16 && launch_convert16_inplace(dst, static_cast<long long>(count), want_f16 ? 1 : 0, ctx->stream)) {
+    set_error("weight format conversion could not be launched");
+    return FLUX_CUDA_ERR_CUDA;
+  }
+  return check_cuda(cudaStreamSynchronize(ctx->stream), "upload weights");
+}
+
 // dst rows [0, 2*half): per block of 128 output columns, 128 rows of the first half then the matching 128 of the second.
-static int upload_interleaved(flux_cuda_model *m, bf16 *dst, const uint16_t *src, size_t half_rows, size_t cols) {
+// The source is elements [off, off + 2 * half_rows * cols) of `data`.
+static int upload_interleaved(flux_cuda_model *m, bf16 *dst, const void *data, int dtype, size_t off, size_t half_rows,
+                              size_t cols, std::vector<uint16_t> &tmp) {
   const size_t bytes = 2 * half_rows * cols * 2;
   if (bytes > m->staging_bytes) return FLUX_CUDA_ERR_ARG;
-  int rc = check_cuda(upload_h2d(m->ctx->stream, m->staging, src, bytes), "upload weights");
+  int rc = upload_16(m->ctx, m->staging, data, dtype, off, 2 * half_rows * cols, m->f16, tmp);
   if (rc) return rc;
   const char *st = reinterpret_cast<const char *>(m->staging);
   const size_t blk = 128 * cols * 2;
@@ -233,8 +253,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
   auto plain = [&](bf16 *dst, long long er, long long ec) -> int {
     int rc = want(er, ec);
     if (rc) return rc;
-    const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
-    return check_cuda(upload_h2d(m->ctx->stream, dst, src, count * 2), "upload weights");
+    return upload_16(m->ctx, dst, data, dtype, 0, count, m->f16, tmp);
   };
   auto vec_f32 = [&](float *dst) -> int {
     if (ndim != 1 || r != 128) {
@@ -282,8 +301,7 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
     else if (t == "ff.linear_in.weight" || t == "ff_context.linear_in.weight") {
       // rows [0, mlp) = gate, [mlp, 2 mlp) = up (flux_transformer.c:4503-4523)
       if (!(rc = want(2 * mlp, h)))
-        rc = upload_interleaved(m, b.ffin[t == "ff.linear_in.weight" ? 1 : 0], to_half_host(data, dtype, count, tmp, m->f16),
-                                mlp, h);
+        rc = upload_interleaved(m, b.ffin[t == "ff.linear_in.weight" ? 1 : 0], data, dtype, 0, mlp, h, tmp);
     } else {
       set_error("unknown tensor %s", name);
     }
@@ -296,9 +314,8 @@ int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int
     else if (t == "attn.to_qkv_mlp_proj.weight") {
       // rows [Q | K | V | gate | up] (flux_transformer.c:3051-3058): Q, K, V stay; gate/up are interleaved
       if (!(rc = want(3 * h + 2 * mlp, h))) {
-        const uint16_t *src = to_half_host(data, dtype, count, tmp, m->f16);
-        rc = check_cuda(upload_h2d(m->ctx->stream, b.lin1, src, 3 * h * h * 2), "upload weights");
-        if (!rc) rc = upload_interleaved(m, b.lin1 + 3 * h * h, src + 3 * h * h, mlp, h);
+        rc = upload_16(m->ctx, b.lin1, data, dtype, 0, 3 * h * h, m->f16, tmp);
+        if (!rc) rc = upload_interleaved(m, b.lin1 + 3 * h * h, data, dtype, 3 * h * h, mlp, h, tmp);
       }
     } else {
       set_error("unknown tensor %s", name);

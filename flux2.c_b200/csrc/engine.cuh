@@ -112,6 +112,11 @@ int safetensors_for_each(const char *path,
 // returns `data` itself when no conversion is needed, else a pointer into `tmp`.
 const uint16_t *to_half_host(const void *data, int dtype, size_t count, std::vector<uint16_t> &tmp, bool want_f16);
 float half_to_f32_host(uint16_t bits, int dtype);
+// Puts elements [off, off + count) of `data` (dtype 0/1/2) at `dst` (device, 16-byte aligned) in the wanted 16-bit
+// format, complete on return. 16-bit sources are copied as they are and, if they hold the other 16-bit format,
+// converted in place by a kernel; only f32 sources are converted on the host (tmp is its scratch).
+int upload_16(flux_cuda_ctx *ctx, void *dst, const void *data, int dtype, size_t off, size_t count, bool want_f16,
+              std::vector<uint16_t> &tmp);
 
 int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec *refs, int num_refs, int batch,
                    int max_steps, flux_cuda_sampler **out);

@@ -278,8 +278,7 @@ int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void 
   auto plain = [&](uint16_t *dst, long long er, long long ec) -> int {
     int rc = want(er, ec);
     if (rc) return rc;
-    return check_cuda(upload_h2d(m->ctx->stream, dst, to_half_host(data, dtype, count, tmp, m->f16), count * 2),
-                      "upload weights");
+    return upload_16(m->ctx, dst, data, dtype, 0, count, m->f16, tmp);
   };
   auto vec = [&](float *dst, long long n) -> int {
     if (ndim != 1 || r != n) {
@@ -296,8 +295,7 @@ int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void 
   auto interleave = [&](uint16_t *dst, int half) -> int {
     int rc = want(it, h);
     if (rc) return rc;
-    rc = check_cuda(upload_h2d(m->ctx->stream, m->staging, to_half_host(data, dtype, count, tmp, m->f16), count * 2),
-                    "upload weights");
+    rc = upload_16(m->ctx, m->staging, data, dtype, 0, count, m->f16, tmp);
     if (rc) return rc;
     const size_t blk = 128 * h * 2;
     for (long long b = 0; b < it / 128; ++b)

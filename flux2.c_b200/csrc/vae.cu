@@ -1,6 +1,7 @@
-// The VAE decoder on the GPU: the stage right after the denoising loop. Replaces the reference's
-// flux_vae_load_safetensors (decoder part) / flux_vae_decode / flux_vae_free (flux_vae.c:1232-1386, 690-837, 1034-1104)
-// with the same tensor names and the same output (uint8 RGB, [16h, 16w, 3]).
+// The VAE on the GPU: the decoder, the stage right after the denoising loop, and the encoder, which turns img2img
+// reference images into latents before it. Replaces the reference's flux_vae_load_safetensors / flux_vae_decode /
+// flux_vae_encode / flux_vae_free (flux_vae.c:1232-1386, 690-837, 320-440, 1034-1104) with the same tensor names and the
+// same outputs (uint8 RGB [16h, 16w, 3]; latent f32 [128, H/16, W/16]).
 //
 // Layout in HBM: activations channels-last; the residual stream x is f32 [pixels, C], everything a convolution reads is
 // 16-bit [pixels, C] (GroupNorm+swish output, upsampled tensor, attention operands); 3x3 weights are re-laid from the
@@ -8,7 +9,8 @@
 // (conv_tcgen05.cu). ResNet block: GN+swish -> conv1(+bias) -> GN+swish -> conv2(+bias) accumulated onto x in the
 // convolution's epilogue; a 1x1 shortcut, where channels change, writes the new x first. Upsampling writes the 2x
 // tensor once in 16 bits and the following convolution writes x. The single attention block (one head of 512
-// channels over all latent pixels) is three GEMMs around a row softmax.
+// channels over all latent pixels) is three GEMMs around a row softmax. The encoder mirrors this; its stride-2
+// convolutions read the input as four parity planes written by one 16-bit conversion pass (conv.cuh).
 #include <math.h>
 #include <stdio.h>
 #include <string.h>
@@ -40,6 +42,11 @@ struct ResW {
   int cin = 0, cout = 0;
 };
 
+struct AttnW {
+  float *g = nullptr, *b = nullptr;
+  ConvW qkv, out;
+};
+
 struct Slot {  // where a named tensor of the file goes
   enum Kind { CONV_W, CONV_B, VEC, QKV_W, QKV_B, PQ_W } kind;
   ConvW *conv;
@@ -54,9 +61,16 @@ struct flux_cuda_vae {
   bool f16 = true;
   float eps = 1e-4f;  // flux_vae.c:1247: used by the GroupNorms and by the latent de-normalisation
   float *bn_mean = nullptr, *bn_var = nullptr, *pq_w = nullptr, *pq_b = nullptr;
-  ConvW conv_in, conv_out, ups[3], attn_qkv, attn_out;
-  float *attn_g = nullptr, *attn_b = nullptr, *out_g = nullptr, *out_b = nullptr;
+  ConvW conv_in, conv_out, ups[3];
+  AttnW attn;
+  float *out_g = nullptr, *out_b = nullptr;
   ResW mid[2], up[12];
+  // encoder half (optional: decoding works without it)
+  ConvW e_conv_in, e_conv_out, e_down[3];
+  AttnW e_attn;
+  float *e_out_g = nullptr, *e_out_b = nullptr, *q_w = nullptr, *q_b = nullptr;  // quant_conv [64, 64], [64] in f32
+  ResW e_mid[2], e_res[8];
+  bool has_encoder = false;
   std::map<std::string, Slot> slots;
   std::set<std::string> seen, optional;
   std::vector<void *> allocs;
@@ -64,6 +78,7 @@ struct flux_cuda_vae {
   // workspace, grown on demand
   size_t cap_elems = 0, cap_tok = 0;
   float *xa = nullptr, *xb = nullptr, *scores = nullptr, *stats = nullptr, *partial = nullptr, *lat = nullptr;
+  float *img_in = nullptr;  // the encoder's input image [3, 16h, 16w]
   uint16_t *a16 = nullptr, *h16 = nullptr, *qkv16 = nullptr, *vt16 = nullptr, *p16 = nullptr, *o16 = nullptr;
   unsigned int *counters = nullptr;
   uint8_t *img = nullptr;
@@ -128,6 +143,23 @@ int make_res(flux_cuda_vae *v, ResW *r, const std::string &prefix, int cin, int 
   return 0;
 }
 
+int make_attn(flux_cuda_vae *v, AttnW *a, const std::string &prefix, int ch) {
+  int rc = make_vec(v, &a->g, ch);
+  if (!rc) rc = make_vec(v, &a->b, ch);
+  if (!rc) rc = make_conv(v, &a->qkv, ch, 3 * ch, 1);
+  if (!rc) rc = make_conv(v, &a->out, ch, ch, 1);
+  if (rc) return rc;
+  reg_vec(v, prefix + ".group_norm.weight", a->g, ch);
+  reg_vec(v, prefix + ".group_norm.bias", a->b, ch);
+  const char *qkv[3] = {"to_q", "to_k", "to_v"};
+  for (int i = 0; i < 3; ++i) {
+    v->slots[prefix + "." + qkv[i] + ".weight"] = Slot{Slot::QKV_W, &a->qkv, nullptr, i};
+    v->slots[prefix + "." + qkv[i] + ".bias"] = Slot{Slot::QKV_B, &a->qkv, nullptr, i};
+  }
+  reg_conv(v, prefix + ".to_out.0", &a->out);
+  return 0;
+}
+
 int ensure_workspace(flux_cuda_vae *v, int h, int w) {
   const size_t tok = static_cast<size_t>(4) * h * w;            // latent-resolution pixels (2h x 2w)
   const size_t elems = static_cast<size_t>(256) * h * w * 256;  // 16h x 16w pixels x 256 channels
@@ -149,6 +181,7 @@ int ensure_workspace(flux_cuda_vae *v, int h, int w) {
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->p16, chunk * tpad, true);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->lat, static_cast<size_t>(128) * h * w);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->img, static_cast<size_t>(256) * h * w * 3);
+  if (!rc && v->has_encoder) rc = v_alloc(v, v->ws_allocs, &v->img_in, static_cast<size_t>(256) * h * w * 3);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->stats, GN_GROUPS * 2);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->partial, static_cast<size_t>(GN_MAX_BLOCKS) * 64);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->counters, 4, true);
@@ -176,6 +209,14 @@ struct Runner {
     if (r) return note(r);
     finish(P, c, mode, out, ld);
   }
+  void conv3_s2(const ConvW &c, const void *planes16, int Ho, int Wo, int mode, void *out, long long ld) {
+    if (rc) return;
+    ConvParams P;
+    memset(&P, 0, sizeof(P));
+    int r = conv_make_3x3_s2(&P, planes16, 1, Ho, Wo, c.cin_pad, c.w, c.cout_pad);
+    if (r) return note(r);
+    finish(P, c, mode, out, ld);
+  }
   void gemm(const ConvW &c, const void *in16, long long ldx, long long M, int mode, void *out, long long ld) {
     if (rc) return;
     ConvParams P;
@@ -199,6 +240,34 @@ struct Runner {
     note(launch_gn_stats(x, in16, f16, 1, pixels, C, v->eps, v->partial, v->counters, v->stats, st));
     if (rc) return;
     note(launch_gn_apply(x, in16, out16, f16, 1, pixels, C, v->stats, g, b, swish, st));
+  }
+  // Attention over T pixels, one head of 512 channels (flux_vae.c:223-314): x += out(softmax(q k^T / sqrt(512)) v)
+  void attention(const AttnW &a, float *x, long long T) {
+    const long long tpad = (T + 127) / 128 * 128;
+    gn(x, 0, T, 512, a.g, a.b, 0, v->a16);
+    gemm(a.qkv, v->a16, 512, T, CONV_STORE_16, v->qkv16, 1536);
+    if (!rc) note(check_cuda(cudaMemsetAsync(v->vt16, 0, static_cast<size_t>(512) * tpad * 2, st), "clear") ? -8 : 0);
+    if (!rc) note(launch_transpose16(v->qkv16 + 1024, 1536, v->vt16, tpad, static_cast<int>(T), 512, st));
+    const long long chunk = T < 8192 ? tpad : 8192;
+    ConvW none;
+    for (long long r0 = 0; r0 < T && !rc; r0 += chunk) {
+      const long long rows = T - r0 < chunk ? T - r0 : chunk;
+      ConvParams P;
+      memset(&P, 0, sizeof(P));
+      // scores[rows, tpad] = Q[r0.., :] K^T; key rows beyond T are read as zeros by the tensor map
+      int r = conv_make_gemm(&P, v->qkv16 + r0 * 1536, 1536, v->qkv16 + 512, 1536, static_cast<int>(rows),
+                             static_cast<int>(tpad), 512, static_cast<int>(T));
+      if (r) return note(r);
+      finish(P, none, CONV_STORE_F32, v->scores, tpad);
+      if (!rc)
+        note(launch_softmax_rows(v->scores, v->p16, f16, rows, static_cast<int>(T), static_cast<int>(tpad),
+                                 1.0f / sqrtf(512.0f), st));
+      memset(&P, 0, sizeof(P));
+      r = conv_make_gemm(&P, v->p16, tpad, v->vt16, tpad, static_cast<int>(rows), 512, static_cast<int>(tpad), 512);
+      if (r) return note(r);
+      finish(P, none, CONV_STORE_16, v->o16 + r0 * 512, 512);
+    }
+    gemm(a.out, v->o16, 512, T, CONV_ADD_F32, x, 512);
   }
   // x (f32 [P, cin]) -> x (f32 [P, cout]); returns the buffer that holds the result
   float *res(const ResW &r, float *x, float *other, int H, int W) {
@@ -248,10 +317,7 @@ int flux_cuda_vae_create(flux_cuda_ctx *ctx, flux_cuda_vae **out) {
   if (!rc) rc = make_conv(v, &v->conv_in, 32, mid, 9);
   if (!rc) rc = make_res(v, &v->mid[0], "decoder.mid_block.resnets.0", mid, mid);
   if (!rc) rc = make_res(v, &v->mid[1], "decoder.mid_block.resnets.1", mid, mid);
-  if (!rc) rc = make_vec(v, &v->attn_g, mid);
-  if (!rc) rc = make_vec(v, &v->attn_b, mid);
-  if (!rc) rc = make_conv(v, &v->attn_qkv, mid, 3 * mid, 1);
-  if (!rc) rc = make_conv(v, &v->attn_out, mid, mid, 1);
+  if (!rc) rc = make_attn(v, &v->attn, "decoder.mid_block.attentions.0", mid);
   int bi = 0;
   for (int level = 3; !rc && level >= 0; --level) {  // flux_vae.c:1322-1334: up_blocks.0 is the deepest level
     const int ch = base * mult[level], prev = level == 3 ? mid : base * mult[level + 1];
@@ -271,23 +337,47 @@ int flux_cuda_vae_create(flux_cuda_ctx *ctx, flux_cuda_vae **out) {
   if (!rc) rc = make_vec(v, &v->out_g, base);
   if (!rc) rc = make_vec(v, &v->out_b, base);
   if (!rc) rc = make_conv(v, &v->conv_out, base, 3, 9);
+  // encoder half (flux_vae.c:1255-1300)
+  const size_t dec_slots = v->slots.size();
+  if (!rc) rc = make_conv(v, &v->e_conv_in, 3, base, 9);
+  int ei = 0;
+  for (int level = 0; !rc && level < 4; ++level) {
+    const int ch = base * mult[level], prev = level == 0 ? base : base * mult[level - 1];
+    for (int r = 0; !rc && r < 2; ++r) {
+      char name[96];
+      snprintf(name, sizeof(name), "encoder.down_blocks.%d.resnets.%d", level, r);
+      rc = make_res(v, &v->e_res[ei++], name, (r == 0 && level > 0) ? prev : ch, ch);
+    }
+    if (!rc && level < 3) {
+      rc = make_conv(v, &v->e_down[level], ch, ch, 9);
+      char name[96];
+      snprintf(name, sizeof(name), "encoder.down_blocks.%d.downsamplers.0.conv", level);
+      if (!rc) reg_conv(v, name, &v->e_down[level]);
+    }
+  }
+  if (!rc) rc = make_res(v, &v->e_mid[0], "encoder.mid_block.resnets.0", mid, mid);
+  if (!rc) rc = make_res(v, &v->e_mid[1], "encoder.mid_block.resnets.1", mid, mid);
+  if (!rc) rc = make_attn(v, &v->e_attn, "encoder.mid_block.attentions.0", mid);
+  if (!rc) rc = make_vec(v, &v->e_out_g, mid);
+  if (!rc) rc = make_vec(v, &v->e_out_b, mid);
+  if (!rc) rc = make_conv(v, &v->e_conv_out, mid, 64, 9);
+  if (!rc) rc = make_vec(v, &v->q_w, 64 * 64);
+  if (!rc) rc = make_vec(v, &v->q_b, 64);
   if (rc) {
     flux_cuda_vae_free(v);
     return rc;
   }
+  reg_conv(v, "encoder.conv_in", &v->e_conv_in);
+  reg_conv(v, "encoder.conv_out", &v->e_conv_out);
+  reg_vec(v, "encoder.conv_norm_out.weight", v->e_out_g, mid);
+  reg_vec(v, "encoder.conv_norm_out.bias", v->e_out_b, mid);
+  v->slots["quant_conv.weight"] = Slot{Slot::PQ_W, nullptr, v->q_w, 64 * 64};
+  reg_vec(v, "quant_conv.bias", v->q_b, 64);
+  (void)dec_slots;
   reg_conv(v, "decoder.conv_in", &v->conv_in);
   reg_conv(v, "decoder.conv_out", &v->conv_out);
   reg_vec(v, "decoder.conv_norm_out.weight", v->out_g, base);
   reg_vec(v, "decoder.conv_norm_out.bias", v->out_b, base);
-  reg_vec(v, "decoder.mid_block.attentions.0.group_norm.weight", v->attn_g, mid);
-  reg_vec(v, "decoder.mid_block.attentions.0.group_norm.bias", v->attn_b, mid);
-  const char *qkv[3] = {"to_q", "to_k", "to_v"};
-  for (int i = 0; i < 3; ++i) {
-    const std::string p = std::string("decoder.mid_block.attentions.0.") + qkv[i];
-    v->slots[p + ".weight"] = Slot{Slot::QKV_W, &v->attn_qkv, nullptr, i};
-    v->slots[p + ".bias"] = Slot{Slot::QKV_B, &v->attn_qkv, nullptr, i};
-  }
-  reg_conv(v, "decoder.mid_block.attentions.0.to_out.0", &v->attn_out);
   v->slots["post_quant_conv.weight"] = Slot{Slot::PQ_W, nullptr, v->pq_w, 32 * 32};
   reg_vec(v, "post_quant_conv.bias", v->pq_b, 32);
   reg_vec(v, "bn.running_mean", v->bn_mean, 128);
@@ -372,11 +462,27 @@ int flux_cuda_vae_set_tensor(flux_cuda_vae *v, const char *name, const void *dat
 
 int flux_cuda_vae_finalize(flux_cuda_vae *v) {
   if (!v) return FLUX_CUDA_ERR_ARG;
-  for (const auto &kv : v->slots)
-    if (!v->seen.count(kv.first) && !v->optional.count(kv.first)) {
+  bool enc_all = true, enc_any = false;
+  std::string enc_missing;
+  for (const auto &kv : v->slots) {
+    const bool is_enc = kv.first.rfind("encoder.", 0) == 0 || kv.first.rfind("quant_conv.", 0) == 0;
+    const bool have = v->seen.count(kv.first) != 0;
+    if (is_enc) {
+      enc_any |= have;
+      if (!have) {
+        enc_all = false;
+        if (enc_missing.empty()) enc_missing = kv.first;
+      }
+    } else if (!have && !v->optional.count(kv.first)) {
       set_error("VAE incomplete: tensor %s was not provided", kv.first.c_str());
       return FLUX_CUDA_ERR_MODEL;
     }
+  }
+  if (enc_any && !enc_all) {  // a file with half an encoder is a broken file, not a decoder-only file
+    set_error("VAE incomplete: encoder tensor %s was not provided", enc_missing.c_str());
+    return FLUX_CUDA_ERR_MODEL;
+  }
+  v->has_encoder = enc_all;
   v->finalized = true;
   return FLUX_CUDA_OK;
 }
@@ -418,7 +524,7 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
   Runner R{v, st, v->f16 ? 1 : 0, v->ctx->num_sms};
   v->launches = 0;
   int H = 2 * h, W = 2 * w;
-  const long long T = static_cast<long long>(H) * W, tpad = (T + 127) / 128 * 128;
+  const long long T = static_cast<long long>(H) * W;
   R.note(launch_vae_prologue(v->lat, v->a16, 1, h, w, v->bn_mean, v->bn_var, v->eps, v->pq_w, v->pq_b, R.f16, st));
   float *x = v->xa, *other = v->xb;
   auto swap_to = [&](float *now) {
@@ -429,38 +535,7 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
   };
   R.conv3(v->conv_in, v->a16, H, W, CONV_STORE_F32, x, 512);
   swap_to(R.res(v->mid[0], x, other, H, W));
-  {  // attention over the T latent-resolution pixels, one head of 512 channels (flux_vae.c:223-314)
-    R.gn(x, 0, T, 512, v->attn_g, v->attn_b, 0, v->a16);
-    R.gemm(v->attn_qkv, v->a16, 512, T, CONV_STORE_16, v->qkv16, 1536);
-    if (!R.rc) R.note(check_cuda(cudaMemsetAsync(v->vt16, 0, static_cast<size_t>(512) * tpad * 2, st), "clear") ? -8 : 0);
-    if (!R.rc) R.note(launch_transpose16(v->qkv16 + 1024, 1536, v->vt16, tpad, static_cast<int>(T), 512, st));
-    const long long chunk = T < 8192 ? tpad : 8192;
-    for (long long r0 = 0; r0 < T && !R.rc; r0 += chunk) {
-      const long long rows = T - r0 < chunk ? T - r0 : chunk;
-      ConvParams P;
-      memset(&P, 0, sizeof(P));
-      // scores[rows, tpad] = Q[r0.., :] K^T; key rows beyond T are read as zeros by the tensor map
-      int r = conv_make_gemm(&P, v->qkv16 + r0 * 1536, 1536, v->qkv16 + 512, 1536, static_cast<int>(rows),
-                             static_cast<int>(tpad), 512, static_cast<int>(T));
-      if (r) {
-        R.note(r);
-        break;
-      }
-      ConvW none;
-      R.finish(P, none, CONV_STORE_F32, v->scores, tpad);
-      if (!R.rc)
-        R.note(launch_softmax_rows(v->scores, v->p16, R.f16, rows, static_cast<int>(T), static_cast<int>(tpad),
-                                   1.0f / sqrtf(512.0f), st));
-      memset(&P, 0, sizeof(P));
-      r = conv_make_gemm(&P, v->p16, tpad, v->vt16, tpad, static_cast<int>(rows), 512, static_cast<int>(tpad), 512);
-      if (r) {
-        R.note(r);
-        break;
-      }
-      R.finish(P, none, CONV_STORE_16, v->o16 + r0 * 512, 512);
-    }
-    R.gemm(v->attn_out, v->o16, 512, T, CONV_ADD_F32, x, 512);
-  }
+  R.attention(v->attn, x, T);
   swap_to(R.res(v->mid[1], x, other, H, W));
   int bi = 0;
   for (int level = 3; level >= 0; --level) {
@@ -482,6 +557,81 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
   }
   return FLUX_CUDA_OK;
 }
+
+// Queues the whole encoder: image f32 [3, H, W] (host or device; H, W multiples of 16) -> v->lat (device, f32
+// [128, H/16, W/16]).
+static int vae_encode_enqueue(flux_cuda_vae *v, const float *image, int H, int W) {
+  if (!v || !image || H < 16 || W < 16 || (H % 16) || (W % 16)) {
+    set_error("vae_encode: bad argument (image sides must be multiples of 16)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  if (!v->finalized || !v->has_encoder) {
+    set_error("vae_encode: the encoder tensors were not loaded");
+    return FLUX_CUDA_ERR_MODEL;
+  }
+  cudaSetDevice(v->ctx->device);
+  const int h = H / 16, w = W / 16;
+  if (!v->img_in) {  // the workspace was sized before the encoder was known to be needed
+    v->cap_elems = 0;
+  }
+  int rc = ensure_workspace(v, h, w);
+  if (rc) return rc;
+  cudaStream_t st = v->ctx->stream;
+  rc = check_cuda(cudaMemcpyAsync(v->img_in, image, static_cast<size_t>(3) * H * W * 4, cudaMemcpyDefault, st), "upload image");
+  if (rc) return rc;
+  Runner R{v, st, v->f16 ? 1 : 0, v->ctx->num_sms};
+  v->launches = 0;
+  R.note(launch_image_to_nhwc(v->img_in, v->a16, R.f16, H, W, st));
+  float *x = v->xa, *other = v->xb;
+  auto swap_to = [&](float *now) {
+    if (now != x) {
+      other = x;
+      x = now;
+    }
+  };
+  R.conv3(v->e_conv_in, v->a16, H, W, CONV_STORE_F32, x, 128);
+  int ei = 0;
+  for (int level = 0; level < 4; ++level) {
+    for (int r = 0; r < 2; ++r) swap_to(R.res(v->e_res[ei++], x, other, H, W));
+    if (level < 3) {
+      const ConvW &c = v->e_down[level];
+      if (!R.rc) R.note(launch_parity_planes(x, v->a16, R.f16, 1, H, W, c.cin, st));
+      H /= 2;
+      W /= 2;
+      R.conv3_s2(c, v->a16, H, W, CONV_STORE_F32, x, c.cout);
+    }
+  }
+  const long long T = static_cast<long long>(H) * W;
+  swap_to(R.res(v->e_mid[0], x, other, H, W));
+  R.attention(v->e_attn, x, T);
+  swap_to(R.res(v->e_mid[1], x, other, H, W));
+  R.gn(x, 0, T, 512, v->e_out_g, v->e_out_b, 1, v->a16);
+  R.conv3(v->e_conv_out, v->a16, H, W, CONV_STORE_F32, other, 128);  // 64 channels of 128 columns are real
+  if (!R.rc)
+    R.note(launch_vae_encode_tail(other, 128, v->lat, H, W, v->q_w, v->q_b, v->bn_mean, v->bn_var, v->eps, st));
+  if (R.rc) {
+    set_error("vae_encode: kernel launch failed (rc %d, cuda: %s)", R.rc, cudaGetErrorString(cudaGetLastError()));
+    ctx_sync_check(v->ctx);
+    return R.rc == -1 || R.rc == -5 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
+  }
+  return FLUX_CUDA_OK;
+}
+
+int flux_cuda_vae_encode(flux_cuda_vae *v, const float *image, int H, int W, float *latent_out) {
+  if (!latent_out) {
+    set_error("vae_encode: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  int rc = vae_encode_enqueue(v, image, H, W);
+  if (rc) return rc;
+  rc = check_cuda(cudaMemcpyAsync(latent_out, v->lat, static_cast<size_t>(128) * (H / 16) * (W / 16) * 4,
+                                  cudaMemcpyDeviceToHost, v->ctx->stream),
+                  "download latent");
+  if (!rc) rc = ctx_sync_check(v->ctx);
+  return rc;
+}
+
+int flux_cuda_vae_has_encoder(const flux_cuda_vae *v) { return v && v->has_encoder ? 1 : 0; }
 
 int flux_cuda_vae_decode(flux_cuda_vae *v, const float *latent, int h, int w, unsigned char *rgb_out) {
   if (!rgb_out) {

@@ -273,6 +273,97 @@ int launch_upsample2x(const float *x, void *out16, int f16, int n_img, int H, in
              : -8;
 }
 
+// ------------------------------------------------------------------------------------------------ encoder edges
+__global__ void __launch_bounds__(256) parity_planes_kernel(const float *__restrict__ x, uint16_t *__restrict__ out,
+                                                            int f16, int H, int W, int C, long long total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c8 = C >> 3, Ho = H >> 1, Wo = W >> 1;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c8);
+    const long long ip = i / c8;  // input pixel over all images
+    const int ix = static_cast<int>(ip % W), iy = static_cast<int>((ip / W) % H);
+    const long long img = ip / (static_cast<long long>(W) * H);
+    const float *src = x + ip * C + cc * 8;
+    const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+    const long long plane = img * 4 + (iy & 1) * 2 + (ix & 1);
+    uint16_t *dst = out + ((plane * Ho + (iy >> 1)) * Wo + (ix >> 1)) * C + cc * 8;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(pack_16x2(a.x, a.y, f16 != 0), pack_16x2(a.z, a.w, f16 != 0),
+                                                 pack_16x2(b.x, b.y, f16 != 0), pack_16x2(b.z, b.w, f16 != 0));
+  }
+}
+
+int launch_parity_planes(const float *x, void *out16, int f16, int n_img, int H, int W, int C, cudaStream_t st) {
+  if (C % 8 || (H & 1) || (W & 1)) return -1;
+  const long long total8 = static_cast<long long>(n_img) * H * W * (C / 8);
+  long long nb = (total8 + 255) / 256;
+  if (nb > 148 * 8) nb = 148 * 8;
+  return launch_kernel(parity_planes_kernel, dim3(static_cast<unsigned>(nb)), dim3(256), 0, st, 1, x,
+                       reinterpret_cast<uint16_t *>(out16), f16, H, W, C, total8) == cudaSuccess
+             ? 0
+             : -8;
+}
+
+__global__ void __launch_bounds__(256) image_to_nhwc_kernel(const float *__restrict__ img, uint16_t *__restrict__ out,
+                                                            int f16, long long pixels) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long p = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; p < pixels;
+       p += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float r = img[p], g = img[pixels + p], b = img[2 * pixels + p];
+    uint4 *dst = reinterpret_cast<uint4 *>(out + p * 64);
+    dst[0] = make_uint4(pack_16x2(r, g, f16 != 0), pack_16x2(b, 0.f, f16 != 0), 0u, 0u);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) dst[j] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+int launch_image_to_nhwc(const float *img, void *out16, int f16, int H, int W, cudaStream_t st) {
+  const long long pixels = static_cast<long long>(H) * W;
+  long long nb = (pixels + 255) / 256;
+  if (nb > 148 * 8) nb = 148 * 8;
+  return launch_kernel(image_to_nhwc_kernel, dim3(static_cast<unsigned>(nb)), dim3(256), 0, st, 1, img,
+                       reinterpret_cast<uint16_t *>(out16), f16, pixels) == cudaSuccess
+             ? 0
+             : -8;
+}
+
+// one warp per latent-resolution pixel: lane = output channel of the mean half
+__global__ void __launch_bounds__(128) vae_encode_tail_kernel(const float *__restrict__ y, int ld, float *__restrict__ latent,
+                                                              int Hl, int Wl, const float *__restrict__ wq,
+                                                              const float *__restrict__ bq, const float *__restrict__ bn_mean,
+                                                              const float *__restrict__ bn_var, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long pix = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (pix >= static_cast<long long>(Hl) * Wl) return;
+  const float *row = y + pix * ld;
+  const float v0 = row[lane], v1 = row[lane + 32];
+  float acc = bq ? bq[lane] : 0.f;
+  const float *wr = wq + lane * 64;
+#pragma unroll 8
+  for (int k = 0; k < 32; ++k) {
+    acc = fmaf(wr[k], __shfl_sync(0xffffffffu, v0, k), acc);
+    acc = fmaf(wr[k + 32], __shfl_sync(0xffffffffu, v1, k), acc);
+  }
+  const int Y = static_cast<int>(pix / Wl), X = static_cast<int>(pix % Wl);
+  const int lc = lane * 4 + (Y & 1) * 2 + (X & 1);  // channel of the packed latent (flux_patchify, p = 2)
+  const int h = Hl >> 1, w = Wl >> 1;
+  latent[(static_cast<size_t>(lc) * h + (Y >> 1)) * w + (X >> 1)] = (acc - bn_mean[lc]) / sqrtf(bn_var[lc] + eps);
+}
+
+int launch_vae_encode_tail(const float *y, int ld, float *latent, int Hl, int Wl, const float *wq, const float *bq,
+                           const float *bn_mean, const float *bn_var, float eps, cudaStream_t st) {
+  if ((Hl & 1) || (Wl & 1) || ld < 64) return -1;
+  const long long pixels = static_cast<long long>(Hl) * Wl;
+  return launch_kernel(vae_encode_tail_kernel, dim3(static_cast<unsigned>((pixels + 3) / 4)), dim3(128), 0, st, 1, y, ld,
+                       latent, Hl, Wl, wq, bq, bn_mean, bn_var, eps) == cudaSuccess
+             ? 0
+             : -8;
+}
+
 // ------------------------------------------------------------------------------------------------ softmax
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float *sm) {
 #pragma unroll

@@ -25,6 +25,16 @@ int launch_gn_apply(const void *x, int in16, void *out16, int f16, int n_img, lo
                     const float *stats, const float *gamma, const float *beta, int swish, cudaStream_t st);
 // Nearest-neighbour 2x upsampling, f32 [n_img, H, W, C] -> 16-bit [n_img, 2H, 2W, C] (flux_kernels.c:1017-1036).
 int launch_upsample2x(const float *x, void *out16, int f16, int n_img, int H, int W, int C, cudaStream_t st);
+// Parity planes for the stride-2 convolution: out16[(n * 4 + py * 2 + px), y, x, c] = x[n, 2y + py, 2x + px, c],
+// f32 [n_img, H, W, C] -> 16-bit [4 n_img, H/2, W/2, C]; H and W even.
+int launch_parity_planes(const float *x, void *out16, int f16, int n_img, int H, int W, int C, cudaStream_t st);
+// Image f32 [3, H, W] (planar, as flux_image_to_tensor produces it) -> 16-bit channels-last [H, W, 64], channels 3..63 zero.
+int launch_image_to_nhwc(const float *img, void *out16, int f16, int H, int W, cudaStream_t st);
+// The encoder's tail (flux_vae.c:404-437): per latent-resolution pixel the first 32 rows of the 1x1 quant_conv
+// (wq [64, 64] f32 row-major, bq [64]; only the mean half of the 64 outputs is used) applied to conv_out's 64
+// channels (f32 [pixels, ld]), then 2x2 space-to-depth into [128, Hl/2, Wl/2] and (x - mean) / sqrt(var + eps).
+int launch_vae_encode_tail(const float *y, int ld, float *latent, int Hl, int Wl, const float *wq, const float *bq,
+                           const float *bn_mean, const float *bn_var, float eps, cudaStream_t st);
 // out16[r, 0..cols) = softmax(scale * s[r, 0..cols)), out16[r, cols..ld) = 0; both with row pitch ld (flux_kernels.c:596-628).
 int launch_softmax_rows(const float *s, void *out16, int f16, long long rows, int cols, int ld, float scale,
                         cudaStream_t st);

@@ -1,10 +1,11 @@
 /*
- * flux_cuda_vae_seam.c - the reference's VAE decoder, served by the B200 engine.
+ * flux_cuda_vae_seam.c - the reference's VAE decoder and encoder, served by the B200 engine.
  *
- * flux_vae.c stays in the build (it still encodes reference images for img2img on the CPU and owns flux_vae_t);
- * only three of its functions are redirected at link time:
+ * flux_vae.c stays in the build (it owns flux_vae_t, flux_image_to_tensor and the legacy loader); four of its
+ * functions are redirected at link time:
  *
- *     -Wl,--wrap=flux_vae_load_safetensors -Wl,--wrap=flux_vae_decode -Wl,--wrap=flux_vae_free
+ *     -Wl,--wrap=flux_vae_load_safetensors -Wl,--wrap=flux_vae_decode -Wl,--wrap=flux_vae_encode
+ *     -Wl,--wrap=flux_vae_free
  *
  * With these flags every call of flux_vae_decode from flux.c (flux.c:480, 569, 659, 846, 1052, 1104, 1226) and from
  * the sampler seam's step-image callback lands in __wrap_flux_vae_decode below, which decodes on the GPU through
@@ -12,8 +13,9 @@
  * half, 16-bit, ~100 MB) and remembers which engine decoder belongs to which flux_vae_t.
  *
  * Behaviour kept: flux_image ownership (caller frees with flux_image_free), NULL on failure with the reason on
- * stderr, the progress callback (reported as complete when the image is back). Calls the engine cannot serve
- * (batch != 1) go to the reference's own code.
+ * stderr, the progress callback (reported as complete when the image is back), malloc ownership of the latent
+ * flux_vae_encode returns. Calls the engine cannot serve (batch != 1, image sides that are not multiples of 16) go to
+ * the reference's own code.
  */
 #include <stdio.h>
 #include <stdlib.h>
@@ -26,6 +28,7 @@
 typedef struct flux_vae flux_vae_t;
 flux_vae_t *__real_flux_vae_load_safetensors(safetensors_file_t *sf);
 flux_image *__real_flux_vae_decode(flux_vae_t *vae, const float *latent, int batch, int latent_h, int latent_w);
+float *__real_flux_vae_encode(flux_vae_t *vae, const float *img, int batch, int H, int W, int *out_h, int *out_w);
 void __real_flux_vae_free(flux_vae_t *vae);
 flux_cuda_ctx *flux_cuda_seam_context(void); /* flux_cuda_seam.c */
 
@@ -73,6 +76,24 @@ flux_image *__wrap_flux_vae_decode(flux_vae_t *vae, const float *latent, int bat
   }
   if (flux_vae_progress_callback) flux_vae_progress_callback(14, 15); /* 3 mid + 12 up blocks, flux_vae.c:750 */
   return img;
+}
+
+float *__wrap_flux_vae_encode(flux_vae_t *vae, const float *img, int batch, int H, int W, int *out_h, int *out_w) {
+  flux_cuda_vae *gpu = find_gpu(vae);
+  if (!gpu || batch != 1 || !flux_cuda_vae_has_encoder(gpu) || H < 16 || W < 16 || (H % 16) || (W % 16))
+    return __real_flux_vae_encode(vae, img, batch, H, W, out_h, out_w);
+  if (!img || !out_h || !out_w) return NULL;
+  float *latent = (float *)malloc((size_t)128 * (H / 16) * (W / 16) * sizeof(float));
+  if (!latent) return NULL;
+  if (flux_cuda_vae_encode(gpu, img, H, W, latent) != FLUX_CUDA_OK) {
+    fprintf(stderr, "flux_vae_encode: %s\n", flux_cuda_last_error());
+    free(latent);
+    return NULL;
+  }
+  *out_h = H / 16;
+  *out_w = W / 16;
+  if (flux_vae_progress_callback) flux_vae_progress_callback(10, 11); /* 8 down + 3 mid blocks, flux_vae.c:343 */
+  return latent;
 }
 
 void __wrap_flux_vae_free(flux_vae_t *vae) {

@@ -223,8 +223,8 @@ int flux_cuda_qwen3_forward_device(flux_cuda_qwen3 *m, const int *input_ids, con
  * The stage after the loop: the VAE decoder (latent -> RGB image). Mirrors flux_vae_load_safetensors /
  * flux_vae_decode / flux_vae_free (flux_vae.c:1232-1386, 690-837, 1034-1104) for the decoder half: channel
  * configuration 128 x (1, 2, 4, 4), two + one ResNet blocks per level, GroupNorm(32), one attention block.
- * Tensor names are the file's own ("decoder.*", "post_quant_conv.*", optional "bn.running_mean/var"); tensors of
- * the encoder half are accepted and ignored.
+ * Tensor names are the file's own ("decoder.*", "post_quant_conv.*", optional "bn.running_mean/var"); the encoder
+ * half ("encoder.*", "quant_conv.*") is optional as a whole.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct flux_cuda_vae flux_cuda_vae;
 int flux_cuda_vae_load_safetensors(flux_cuda_ctx *ctx, const char *path, flux_cuda_vae **out);
@@ -240,7 +240,14 @@ void flux_cuda_vae_free(flux_cuda_vae *v);
 int flux_cuda_vae_decode(flux_cuda_vae *v, const float *latent, int h, int w, unsigned char *rgb_out);
 /* The same, queued without waiting; *rgb_dev is the decoder's own device buffer (valid until the next decode). */
 int flux_cuda_vae_decode_device(flux_cuda_vae *v, const float *latent, int h, int w, const unsigned char **rgb_dev);
-/* Kernels launched by the last decode. */
+/* The encoder (flux_vae_encode, flux_vae.c:320-440): image f32 [3, H, W] planar, values in [-1, 1] as
+ * flux_image_to_tensor produces them, host or device memory, H and W multiples of 16 -> latent_out: host f32
+ * [128, H/16, W/16] (mean of the posterior, 2x2 packed, batch-normalised with the file's running statistics).
+ * Needs the file's "encoder.*" and "quant_conv.*" tensors: a model created without them decodes only
+ * (flux_cuda_vae_has_encoder returns 0 and this call FLUX_CUDA_ERR_MODEL). */
+int flux_cuda_vae_encode(flux_cuda_vae *v, const float *image, int H, int W, float *latent_out);
+int flux_cuda_vae_has_encoder(const flux_cuda_vae *v);
+/* Kernels launched by the last decode or encode. */
 long long flux_cuda_vae_last_launches(const flux_cuda_vae *v);
 /* Device address of a sampler's current latent (f32 [128, h, w]; batch 2: the shared latent), in stream order
  * after the last run. */
@@ -304,6 +311,11 @@ int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int
  * output channels 0..2 as (v + 1) * 127.5 clamped and truncated. ld: row pitch of out in elements. */
 int flux_cuda_conv3x3(flux_cuda_ctx *ctx, const void *x16, int n_img, int H, int W, int cin, const void *w16, int cout,
                       const float *bias, int mode, void *out, long long ld, int f16);
+/* The encoder's downsampling convolution (flux_vae.c:146-171, 360-372): 3x3, stride 2, over the input extended by one
+ * zero row at the bottom and one zero column at the right. planes16 holds the input as four parity planes,
+ * [(n * 4 + py * 2 + px), Ho, Wo, cin] = in[n, 2y + py, 2x + px, :]; Ho x Wo is the output size. Otherwise as above. */
+int flux_cuda_conv3x3_stride2(flux_cuda_ctx *ctx, const void *planes16, int n_img, int Ho, int Wo, int cin,
+                              const void *w16, int cout, const float *bias, int mode, void *out, long long ld, int f16);
 /* The same kernel as a plain GEMM with a bias: out[M, N] = x16[M, K] * w16[N, K]^T + bias (modes 0-2). Only the first
  * w_rows rows of w16 are read; the rest count as zero. 1x1 convolutions and the VAE attention block's products. */
 int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, const void *w16, long long ldw, int M, int N,

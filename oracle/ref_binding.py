@@ -106,7 +106,12 @@ class RefLib:
         L.qwen3_model_free.argtypes = [vp]
         L.qwen3_forward.restype = vp
         L.qwen3_forward.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ci]
+        L.flux_vae_encode.restype = vp
+        L.flux_vae_encode.argtypes = [vp, c_float_p, ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
         if kind == "seam":
+            L.flux_vae_encode = getattr(L, "__wrap_flux_vae_encode")
+            L.flux_vae_encode.restype = vp
+            L.flux_vae_encode.argtypes = [vp, c_float_p, ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
             # the seam redirects these three at link time (-Wl,--wrap); calls from outside the library must name the
             # wrappers themselves to take the path the library's own callers take
             L.flux_vae_load_safetensors = getattr(L, "__wrap_flux_vae_load_safetensors")
@@ -185,6 +190,13 @@ class RefLib:
         if not vae:
             raise RuntimeError("reference could not load the VAE")
         return vae
+
+    def vae_encode(self, vae, image):
+        """flux_vae_encode (flux_vae.c:320-440): image f32 [3, H, W] -> latent f32 [128, H/16, W/16]."""
+        img = np.ascontiguousarray(image, dtype=np.float32)
+        oh, ow = ctypes.c_int(), ctypes.c_int()
+        p = self.L.flux_vae_encode(vae, _fp(img), 1, img.shape[1], img.shape[2], ctypes.byref(oh), ctypes.byref(ow))
+        return self._take(p, 128 * oh.value * ow.value).reshape(128, oh.value, ow.value)
 
     def vae_decode(self, vae, latent):
         """flux_vae_decode (flux_vae.c:690-837): latent f32 [128, h, w] -> uint8 RGB [16h, 16w, 3]."""

@@ -5,7 +5,10 @@ batch de-normalisation with eps 1e-4 (717-729, 1247), unpatchify (733), post_qua
 mid block = ResNet block, single-head attention over all pixels, ResNet block (752-767; resblock_forward 179-220,
 attnblock_forward 223-314), four up levels of three ResNet blocks with nearest 2x upsampling + 3x3 convolution between
 them (773-800), GroupNorm(32) + swish + conv_out (804-811), conversion to uint8 by clamping (v + 1) * 127.5 and
-truncating (822-833). Pinned against the reference build by tests/test_vae_oracle.py. Besides the image it returns the
+truncating (822-833); and of its encoder, flux_vae_encode (320-440): conv_in, four levels of two ResNet blocks with
+a stride-2 convolution over the input padded at the right and bottom between them (146-171, 360-372), the same mid
+block, GroupNorm + swish + conv_out, quant_conv 1x1, the mean half of the 64 channels, patchify, batch-norm with the
+running statistics. Pinned against the reference build by tests/test_vae_oracle.py. Besides the image it returns the
 float tensor before the conversion and, on request, every block's output, which the reference does not expose."""
 import numpy as np
 import torch
@@ -17,8 +20,7 @@ GROUPS = 32
 
 class VaeOracle:
     def __init__(self, tensors):
-        self.t = {k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)) for k, v in tensors.items()
-                  if k.startswith(("decoder.", "post_quant_conv.", "bn."))}
+        self.t = {k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)) for k, v in tensors.items()}
 
     def _conv(self, x, name, pad):
         w = self.t[name + ".weight"]
@@ -46,6 +48,29 @@ class VaeOracle:
         p = torch.softmax((q * (1.0 / np.sqrt(c))) @ k.transpose(1, 2), dim=-1)
         o = (p @ v).transpose(1, 2).reshape(b, c, hh, ww)
         return x + self._conv(o, prefix + ".to_out.0", 0)
+
+    @torch.no_grad()
+    def encode(self, image):
+        """image f32 [3, H, W] -> latent f32 [128, H/16, W/16]."""
+        x = torch.from_numpy(np.ascontiguousarray(image, dtype=np.float32))[None]
+        x = self._conv(x, "encoder.conv_in", 1)
+        for lvl in range(4):
+            for r in range(2):
+                x = self._res(x, "encoder.down_blocks.%d.resnets.%d" % (lvl, r))
+            if lvl < 3:
+                p = "encoder.down_blocks.%d.downsamplers.0.conv" % lvl
+                x = F.conv2d(F.pad(x, (0, 1, 0, 1)), self.t[p + ".weight"], self.t[p + ".bias"], stride=2)
+        x = self._res(x, "encoder.mid_block.resnets.0")
+        x = self._attn(x, "encoder.mid_block.attentions.0")
+        x = self._res(x, "encoder.mid_block.resnets.1")
+        x = self._conv(self._gn(x, "encoder.conv_norm_out", True), "encoder.conv_out", 1)
+        x = self._conv(x, "quant_conv", 0)[:, :32]
+        _, _, hl, wl = x.shape
+        z = x.reshape(1, 32, hl // 2, 2, wl // 2, 2).permute(0, 1, 3, 5, 2, 4).reshape(1, 128, hl // 2, wl // 2)
+        mean = self.t.get("bn.running_mean", torch.zeros(128))
+        var = self.t.get("bn.running_var", torch.ones(128))
+        z = (z - mean[None, :, None, None]) / torch.sqrt(var + EPS)[None, :, None, None]
+        return z[0].numpy().copy()
 
     @torch.no_grad()
     def decode(self, latent, taps=None):

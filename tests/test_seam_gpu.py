@@ -112,3 +112,19 @@ def test_seam_vae_decode_is_served_by_the_engine(seam, scratch, fx, ctx):
         direct.close()
     finally:
         seam.L.flux_vae_free(vae)
+
+
+def test_seam_vae_encode_is_served_by_the_engine(seam, scratch):
+    import flux2_c_b200.synth as synth
+    from oracle.vae_oracle import VaeOracle
+    W = synth.make_vae_weights(seed=5, rich=True)
+    path = os.path.join(scratch, "vae_enc.safetensors")
+    synth.write_safetensors(path, W, dtype="F32")
+    vae = seam.load_vae(path)
+    try:
+        img = np.random.default_rng(2).uniform(-1.0, 1.0, (3, 64, 48)).astype(np.float32)
+        got = seam.vae_encode(vae, img)
+        assert got.shape == (128, 4, 3)
+        assert rel(got, VaeOracle(W).encode(img)) < 1e-2
+    finally:
+        seam.L.flux_vae_free(vae)

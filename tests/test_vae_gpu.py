@@ -206,3 +206,58 @@ def test_sampler_latent_decodes_without_leaving_the_device(vae, fx, ctx):
         s.close()
     finally:
         model.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16])
+@pytest.mark.parametrize("n,Ho,Wo,cin,cout", [(1, 8, 8, 64, 128), (1, 32, 32, 128, 128), (2, 5, 9, 64, 256),
+                                              (1, 128, 128, 256, 256), (1, 1, 1, 64, 128)])
+def test_conv3x3_stride2_matches_torch(fx, ctx, n, Ho, Wo, cin, cout, dtype):
+    """The encoder's downsampling: zero row/column appended at the bottom/right, 3x3, stride 2, no other padding. The
+    kernel-level entry takes the input as parity planes, which this test builds with torch."""
+    g = torch.Generator(device="cuda").manual_seed(Ho * 100 + Wo)
+    H, W = 2 * Ho, 2 * Wo
+    x = torch.randn(n, H, W, cin, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(cout, cin, 3, 3, device="cuda", generator=g) * 0.05).to(dtype)
+    b = torch.randn(cout, device="cuda", generator=g)
+    planes = torch.stack([x[:, py::2, px::2, :] for py in (0, 1) for px in (0, 1)], dim=1).contiguous()  # [n,4,Ho,Wo,C]
+    ref = torch.nn.functional.conv2d(torch.nn.functional.pad(x.float().permute(0, 3, 1, 2), (0, 1, 0, 1)), w.float(), b,
+                                     stride=2).permute(0, 2, 3, 1).reshape(n * Ho * Wo, cout)
+    out = torch.zeros(n * Ho * Wo, cout, device="cuda")
+    torch.cuda.synchronize()
+    ctx.conv3x3(planes.data_ptr(), n, Ho, Wo, cin, _tap_major(w).data_ptr(), cout, b.data_ptr(), 1, out.data_ptr(), cout,
+                stride2=True)
+    ctx.sync()
+    assert _rel(out, ref) < 1e-5 * max(1.0, (9 * cin) ** 0.5 / 8)
+
+
+@pytest.mark.parametrize("H,W", [(64, 64), (48, 80), (256, 256), (16, 16)])
+def test_encode_matches_oracle(vae, H, W):
+    synth, Wt, v, oracle = vae
+    assert v.has_encoder()
+    img = np.random.default_rng(H + W).uniform(-1.0, 1.0, (3, H, W)).astype(np.float32)
+    want = oracle.encode(img)
+    got = v.encode(img)
+    assert got.shape == want.shape
+    rel = float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64)))
+    assert rel < 1e-2  # 16-bit operands through 20 convolutions; an order below the final-latent tolerance of 3e-2
+    assert np.array_equal(v.encode(img), got)
+
+
+def test_encode_then_decode_and_decoder_only_models(vae, fx, ctx):
+    synth, Wt, v, oracle = vae
+    img = np.random.default_rng(1).uniform(-1.0, 1.0, (3, 64, 96)).astype(np.float32)
+    lat = v.encode(img)
+    assert psnr(v.decode(lat), oracle.decode(oracle.encode(img))[0]) >= PSNR_MIN
+    dec_only = {k: a for k, a in Wt.items() if not k.startswith(("encoder.", "quant_conv."))}
+    v2 = fx.Vae.from_tensors(ctx, dec_only)
+    assert not v2.has_encoder()
+    with pytest.raises(fx.FluxCudaError):
+        v2.encode(img)
+    assert np.array_equal(v2.decode(lat), v.decode(lat))
+    v2.close()
+    half = dict(dec_only)
+    half["encoder.conv_in.weight"] = Wt["encoder.conv_in.weight"]
+    with pytest.raises(fx.FluxCudaError):
+        fx.Vae.from_tensors(ctx, half)
+    with pytest.raises(fx.FluxCudaError):
+        v.encode(np.zeros((3, 40, 64), dtype=np.float32))  # 40 is not a multiple of 16

@@ -33,3 +33,25 @@ def test_vae_oracle_matches_reference(fx, tmp_path, h, w):
     d = np.abs(got.astype(np.int32) - want.astype(np.int32))
     assert d.max() <= 1 and (d > 0).mean() < 0.02  # f32 summation order only: an occasional off-by-one after truncation
     assert psnr(got, want) > 55
+
+
+@pytest.mark.parametrize("H,W", [(64, 64), (48, 80)])
+def test_vae_oracle_encode_matches_reference(fx, tmp_path, H, W):
+    import flux2_c_b200.synth as synth
+    from oracle import ref_binding as rb
+    from oracle.vae_oracle import VaeOracle
+    kind = rb.best_kind()
+    if kind is None:
+        pytest.skip("the reference build (oracle/_ref) is not present")
+    Wt = synth.make_vae_weights(seed=5, rich=True)
+    path = str(tmp_path / "vae.safetensors")
+    synth.write_safetensors(path, Wt, dtype="F32")
+    lib = rb.RefLib(kind)
+    vae = lib.load_vae(path)
+    img = np.random.default_rng(H).uniform(-1.0, 1.0, (3, H, W)).astype(np.float32)
+    want = lib.vae_encode(vae, img)
+    got = VaeOracle(Wt).encode(img)
+    assert got.shape == want.shape == (128, H // 16, W // 16)
+    assert float(np.abs(want).mean()) > 0.05
+    rel = float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64)))
+    assert rel < 2e-4
