@@ -445,6 +445,69 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
                                 "d2h_bytes_per_image": int(rgb.numel()), "image_std": img_std}}
 
 
+# ---------------------------------------------------------------------------------------------- other configurations
+CONFIGS = {
+    1: dict(name="klein4b_256x256_4step_b1", h=16, w=16, steps=4, guidance=1.0, ref=None),
+    3: dict(name="klein4b_base_512x512_50step_cfg4_pair_as_batch2", h=32, w=32, steps=50, guidance=4.0, ref=None),
+    4: dict(name="klein4b_img2img_1024x1024_4step_1ref_8704tok", h=64, w=64, steps=4, guidance=1.0, ref=(64, 64, 10)),
+}
+
+
+def run_config(args):
+    """The other single-GPU configurations of the workload list (the default run is configuration 2): images/s with
+    the inputs resident, K images back to back, CUDA events on the engine's stream. One JSON line of its own."""
+    import numpy as np
+    import torch
+    fx = load_package()
+    import flux2_c_b200.synth as synth
+    c = CONFIGS[args.config]
+    dims = synth.Dims.klein4b()
+    ctx = fx.Context(0)
+    model = fx.Model.from_tensors(ctx, dims, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
+    h, w, steps, g = c["h"], c["w"], c["steps"], c["guidance"]
+    batch = 2 if g != 1.0 else 1
+    refs = [c["ref"]] if c["ref"] else []
+    z0 = torch.from_numpy(fx.init_noise(dims.latent_ch, h, w, 42)).pin_memory()
+    cc = torch.from_numpy(synth.make_context(1234, TXT, dims.text_dim)).pin_memory()
+    cu = torch.from_numpy(synth.make_context(4321, TXT, dims.text_dim)).pin_memory()
+    ref_lat = [torch.from_numpy(synth.make_latent(7, dims.latent_ch, r[0], r[1])).pin_memory() for r in refs]
+    sched = fx.official_schedule(steps, h * w)
+    sampler = fx.Sampler(model, h, w, TXT, ref_shapes=refs, batch=batch, max_steps=steps)
+    sampler.upload(z0.data_ptr(), cc.data_ptr(), cu.data_ptr() if batch == 2 else None, [t.data_ptr() for t in ref_lat])
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    for _ in range(max(1, min(3, args.warmup))):
+        sampler.run(sched, guidance=g)
+    ctx.sync()
+    clocks = ClockSampler(0)
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record()
+        for _ in range(args.steps):
+            sampler.run(sched, guidance=g)
+        e1.record()
+    ctx.sync()
+    ms = e0.elapsed_time(e1) / args.steps
+    clk = clocks.stop()
+    out = torch.zeros(dims.latent_ch * h * w, dtype=torch.float32).pin_memory()
+    sampler.download(out.data_ptr())
+    n_ref = sum(r[0] * r[1] for r in refs)
+    N = h * w + n_ref + TXT
+    hd, m = dims.hidden, dims.mlp
+    lin = dims.n_double * N * 2 * (4 * hd * hd + 3 * hd * m) + dims.n_single * N * 2 * (hd * (3 * hd + 2 * m) + (hd + m) * hd)
+    lin += 2 * (h * w + n_ref) * dims.latent_ch * hd + 2 * h * w * hd * dims.latent_ch
+    attn = (dims.n_double + dims.n_single) * 4 * N * N * hd
+    flops = batch * steps * (lin + attn) + batch * 2 * TXT * dims.text_dim * hd
+    print(json.dumps({"config": args.config, "workload": c["name"], "value": 1e3 / ms, "unit": "images/s",
+                      "ms_per_image": ms, "ms_per_dit_step": ms / steps, "dit_steps_per_image": steps, "batch": batch,
+                      "tokens": N, "model_tflops": flops / ms / 1e9, "attention_share_of_flops": batch * steps * attn / flops,
+                      "images_timed": args.steps, "finite": bool(torch.isfinite(out).all()), "clocks": clk,
+                      "dtype": "f16", "data": "synthetic"}))
+    sampler.close()
+    model.close()
+    return 0
+
+
 # ---------------------------------------------------------------------------------------------- main arm
 def run_ours(args):
     import numpy as np
@@ -661,6 +724,7 @@ def main():
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--size", type=int, default=512, help="image side for --micro vae")
+    ap.add_argument("--config", type=int, default=2, help="1, 3 or 4: another configuration of the workload list")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-text-encoder", action="store_true", help="skip the prompt -> latent leg")
     ap.add_argument("--dump-launches", default=None, help="write [ms, class] of every launch of one image to this file")
@@ -672,6 +736,8 @@ def main():
         return run_reference_arm(args)
     if args.micro:
         return run_micro(args)
+    if args.config in CONFIGS:
+        return run_config(args)
     return run_ours(args)
 
 
