@@ -458,12 +458,24 @@ def run_config(args):
     the inputs resident, K images back to back, CUDA events on the engine's stream. One JSON line of its own."""
     import numpy as np
     import torch
+    import torch.distributed as dist
     fx = load_package()
     import flux2_c_b200.synth as synth
     c = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pair = world == 2 and args.config == 3  # the guidance pair split across two GPUs, one exchange per step
+    if world > 1:
+        if not pair:
+            raise SystemExit("--config under torchrun: only configuration 3 on exactly two ranks (the guidance pair)")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dims = synth.Dims.klein4b()
-    ctx = fx.Context(0)
-    model = fx.Model.from_tensors(ctx, dims, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
+    ctx = fx.Context(local)
+    model = fx.Model.from_tensors(ctx, dims, synth.make_transformer_weights(dims, seed=0,
+                                                                            threads=max(1, os.cpu_count() // world)))
     h, w, steps, g = c["h"], c["w"], c["steps"], c["guidance"]
     batch = 2 if g != 1.0 else 1
     refs = [c["ref"]] if c["ref"] else []
@@ -472,23 +484,53 @@ def run_config(args):
     cu = torch.from_numpy(synth.make_context(4321, TXT, dims.text_dim)).pin_memory()
     ref_lat = [torch.from_numpy(synth.make_latent(7, dims.latent_ch, r[0], r[1])).pin_memory() for r in refs]
     sched = fx.official_schedule(steps, h * w)
-    sampler = fx.Sampler(model, h, w, TXT, ref_shapes=refs, batch=batch, max_steps=steps)
-    sampler.upload(z0.data_ptr(), cc.data_ptr(), cu.data_ptr() if batch == 2 else None, [t.data_ptr() for t in ref_lat])
     stream = torch.cuda.ExternalStream(ctx.stream)
+    if pair:
+        dp = importlib.import_module("flux2_c_b200.dp")
+        _, is_cond = dp.pair_of_rank(rank)
+        group = dp.pair_groups(world)
+        sampler = fx.Sampler(model, h, w, TXT, batch=1, max_steps=steps)
+        v_buf = torch.zeros(dims.latent_ch * h * w, dtype=torch.float32, device="cuda")
+        mine = cc if is_cond else cu
+
+        def one_image():
+            sampler.upload(z0.data_ptr(), mine.data_ptr())
+            with torch.cuda.stream(stream):
+                dp.sample_cfg_pair(sampler, sched, g, is_cond, v_buf, group)
+    else:
+        sampler = fx.Sampler(model, h, w, TXT, ref_shapes=refs, batch=batch, max_steps=steps)
+        sampler.upload(z0.data_ptr(), cc.data_ptr(), cu.data_ptr() if batch == 2 else None,
+                       [t.data_ptr() for t in ref_lat])
+
+        def one_image():
+            sampler.run(sched, guidance=g)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        ctx.sync()
+        torch.cuda.synchronize()
+
     for _ in range(max(1, min(3, args.warmup))):
-        sampler.run(sched, guidance=g)
-    ctx.sync()
-    clocks = ClockSampler(0)
-    clocks.start()
+        one_image()
+    sync_all()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record()
-        for _ in range(args.steps):
-            sampler.run(sched, guidance=g)
+    for _ in range(args.steps):
+        one_image()
+    with torch.cuda.stream(stream):
         e1.record()
-    ctx.sync()
+    sync_all()
     ms = e0.elapsed_time(e1) / args.steps
-    clk = clocks.stop()
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clk = clocks.stop() if rank == 0 else None
     out = torch.zeros(dims.latent_ch * h * w, dtype=torch.float32).pin_memory()
     sampler.download(out.data_ptr())
     n_ref = sum(r[0] * r[1] for r in refs)
@@ -498,13 +540,19 @@ def run_config(args):
     lin += 2 * (h * w + n_ref) * dims.latent_ch * hd + 2 * h * w * hd * dims.latent_ch
     attn = (dims.n_double + dims.n_single) * 4 * N * N * hd
     flops = batch * steps * (lin + attn) + batch * 2 * TXT * dims.text_dim * hd
-    print(json.dumps({"config": args.config, "workload": c["name"], "value": 1e3 / ms, "unit": "images/s",
-                      "ms_per_image": ms, "ms_per_dit_step": ms / steps, "dit_steps_per_image": steps, "batch": batch,
-                      "tokens": N, "model_tflops": flops / ms / 1e9, "attention_share_of_flops": batch * steps * attn / flops,
-                      "images_timed": args.steps, "finite": bool(torch.isfinite(out).all()), "clocks": clk,
-                      "dtype": "f16", "data": "synthetic"}))
+    if pair:
+        c = dict(c, name="klein4b_base_512x512_50step_cfg4_pair_split_across_2_gpus")
+    if rank == 0:
+        print(json.dumps({"config": args.config, "workload": c["name"], "value": 1e3 / ms, "unit": "images/s",
+                          "n_gpus": world, "ms_per_image": ms, "ms_per_dit_step": ms / steps,
+                          "dit_steps_per_image": steps, "batch": batch, "tokens": N, "model_tflops": flops / ms / 1e9,
+                          "attention_share_of_flops": batch * steps * attn / flops, "images_timed": args.steps,
+                          "finite": bool(torch.isfinite(out).all()), "clocks": clk, "dtype": "f16", "data": "synthetic"}))
     sampler.close()
     model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 
