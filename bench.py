@@ -302,21 +302,24 @@ def run_micro(args):
         synth = importlib.import_module("flux2_c_b200.synth")
         d = synth.QwenDims(layers=27)
         W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count())
-        enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=max(512, args.seq))
+        B = max(1, args.prompt_batch)
+        enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=max(512, args.seq) * B)
         del W
         seq = args.seq
-        ids = np.random.default_rng(0).integers(0, d.vocab, seq)
+        ids = np.random.default_rng(0).integers(0, d.vocab, (B, seq))
         for _ in range(max(3, args.warmup)):
-            out = enc.forward(ids, None)
+            out = enc.forward_batch(ids, None)
         t0 = time.perf_counter()
         for _ in range(iters):
-            out = enc.forward(ids, None)
-        ms = (time.perf_counter() - t0) * 1e3 / iters
+            out = enc.forward_batch(ids, None)
+        ms = (time.perf_counter() - t0) * 1e3 / iters / B
+        dev_ms = timed(lambda: enc.forward_batch(ids, None, device=True)) / B
         qd, kd = d.heads * d.head_dim, d.kv_heads * d.head_dim
         per_layer = 2.0 * seq * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter) + 2.0 * seq * seq * qd
         flops = 27 * per_layer
         wbytes = 27 * 2.0 * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter)
-        print(json.dumps({"micro": "qwen3", "seq": seq, "layers_run": 27, "ms_per_prompt_e2e": ms,
+        print(json.dumps({"micro": "qwen3", "seq": seq, "prompts_per_pass": B, "layers_run": 27, "ms_per_prompt_e2e": ms,
+                          "ms_per_prompt_device": dev_ms, "model_tflops_device": flops / dev_ms / 1e9,
                           "model_tflops": flops / ms / 1e9, "weight_gb_per_pass": wbytes / 1e9,
                           "weight_stream_ms_at_hbm_peak": wbytes / peaks["hbm_gbs"] / 1e6,
                           "d2h_bytes": int(out.nbytes), "finite": bool(np.isfinite(out).all()),
@@ -334,6 +337,7 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     import numpy as np
     import torch
     qd = synth.QwenDims(layers=27)
+    PB = max(1, args.prompt_batch)  # prompts per encoder pass: the weights are read once for the group
 
     def all_ok(ok):
         # every rank calls this the same number of times, whether its own part worked or not, so that a failure on
@@ -347,7 +351,7 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     enc, err = None, None
     if world == 1:
         enc = fx.TextEncoder.from_tensors(ctx, qd, synth.make_qwen_weights(qd, seed=0, threads=os.cpu_count()),
-                                          max_seq=TXT)
+                                          max_seq=TXT * PB)
     else:
         shm = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
         mdir = os.path.join(shm, "flux_bench_qwen_%s" % os.environ.get("MASTER_PORT", "0"))
@@ -359,7 +363,7 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
         wrote = all_ok(err is None)
         try:
             if wrote:
-                enc = fx.TextEncoder.load_dir(ctx, mdir, max_seq=TXT)
+                enc = fx.TextEncoder.load_dir(ctx, mdir, max_seq=TXT * PB)
         except Exception as e:
             err = e
         loaded = all_ok(wrote and enc is not None)
@@ -371,35 +375,42 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
                 enc.close()
             raise RuntimeError("text encoder set-up failed on some rank: %r" % (err,))
     rng = np.random.default_rng(1000 + rank)
-    ids = [rng.integers(0, qd.vocab, TXT).astype(np.int32) for _ in range(args.steps)]
+    ids = rng.integers(0, qd.vocab, (max(args.steps, PB), TXT)).astype(np.int32)
+    ctx_bytes = TXT * 3 * qd.hidden * 4
 
-    def one(i):
-        dev = enc.forward_device(ids[i % len(ids)])
-        sampler.upload(z0.data_ptr(), dev)
-        sampler.run(sched)
-        sampler.download(out.data_ptr())  # waits for the image
+    def run_images(n, per_image):
+        """n images: prompts are encoded PB at a time; the embeddings of prompt j of a group sit at dev + j * ctx_bytes
+        until the next group is encoded, which the stream orders after the uploads that read them."""
+        done = 0
+        while done < n:
+            g = min(PB, n - done)
+            dev = enc.forward_batch(ids[done:done + g], None, device=True)
+            for j in range(g):
+                sampler.upload(z0.data_ptr(), dev + j * ctx_bytes)
+                sampler.run(sched)
+                per_image()
+            done += g
 
-    for i in range(3):
-        one(i)
+    to_latent = lambda: sampler.download(out.data_ptr())  # waits for the image
+    run_images(max(3, PB), to_latent)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record()
-    for i in range(args.steps):
-        one(i)
+    run_images(args.steps, to_latent)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
-    # the encoder alone, device time
+    # the encoder alone, device time per prompt
     with torch.cuda.stream(stream):
         e0.record()
     for i in range(args.steps):
-        enc.forward_device(ids[i % len(ids)])
+        enc.forward_batch(ids[:PB], None, device=True)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
-    enc_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    enc_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps / PB
     finite = bool(torch.isfinite(out).all())
 
     # the same plus the VAE decoder: the latent goes from the sampler to the decoder on the device, the 512x512 RGB
@@ -407,18 +418,12 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     vae = fx.Vae.from_tensors(ctx, synth.make_vae_weights(seed=5, rich=True))
     rgb = torch.zeros(16 * H_LAT * 16 * W_LAT * 3, dtype=torch.uint8).pin_memory()
 
-    def one_image(i):
-        sampler.upload(z0.data_ptr(), enc.forward_device(ids[i % len(ids)]))
-        sampler.run(sched)
-        vae.decode_ptr(sampler.latent_device(), H_LAT, W_LAT, rgb.data_ptr())  # waits for the image
-
-    for i in range(3):
-        one_image(i)
+    to_image = lambda: vae.decode_ptr(sampler.latent_device(), H_LAT, W_LAT, rgb.data_ptr())  # waits for the image
+    run_images(max(3, PB), to_image)
     barrier()
     with torch.cuda.stream(stream):
         e0.record()
-    for i in range(args.steps):
-        one_image(i)
+    run_images(args.steps, to_image)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
@@ -435,8 +440,9 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     vae.close()
     enc.close()
     return {"workload": "per image: %d token ids -> Qwen3-4B-shaped encoder (27 of 36 layers: the ones the output "
-            "depends on) -> 4 DiT steps at 512x512 -> latent on the host" % TXT, "value": args.steps * world / (ms * 1e-3),
-            "unit": "images/s", "ms_per_image": ms / args.steps, "text_encoder_ms": enc_ms,
+            "depends on; %d prompts per encoder pass) -> 4 DiT steps at 512x512 -> latent on the host" % (TXT, PB), "value": args.steps * world / (ms * 1e-3),
+            "unit": "images/s", "ms_per_image": ms / args.steps, "text_encoder_ms_per_prompt": enc_ms,
+            "prompts_per_encoder_pass": PB,
             "h2d_bytes_per_image": int(TXT * 4 + z0.numel() * 4), "d2h_bytes_per_image": int(out.numel() * 4),
             "finite": finite,
             "prompt_to_image": {"workload": "the same, then the VAE decoder on the device; a 512x512 uint8 RGB image "
@@ -775,6 +781,7 @@ def main():
     ap.add_argument("--config", type=int, default=2, help="1, 3 or 4: another configuration of the workload list")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-text-encoder", action="store_true", help="skip the prompt -> latent leg")
+    ap.add_argument("--prompt-batch", type=int, default=4, help="prompts encoded per text-encoder pass")
     ap.add_argument("--dump-launches", default=None, help="write [ms, class] of every launch of one image to this file")
     ap.add_argument("--ncu-range", action="store_true", help="profile exactly one image (for ncu launch lists)")
     args = ap.parse_args()

@@ -115,6 +115,11 @@ def _declare(L):
                                        c_void_p, ctypes.c_float, c_int, c_int]
     L.flux_cuda_group_norm_noalloc.restype = c_int
     L.flux_cuda_group_norm_noalloc.argtypes = L.flux_cuda_group_norm.argtypes
+    L.flux_cuda_qwen3_forward_batch.restype = c_int
+    L.flux_cuda_qwen3_forward_batch.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int, fp]
+    L.flux_cuda_qwen3_forward_batch_device.restype = c_int
+    L.flux_cuda_qwen3_forward_batch_device.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
+                                                       ctypes.POINTER(c_void_p)]
     L.flux_cuda_qwen3_forward_device.restype = c_int
     L.flux_cuda_qwen3_forward_device.argtypes = [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
                                                  ctypes.POINTER(c_void_p)]
@@ -458,6 +463,27 @@ class TextEncoder:
         hdim = hidden or (self.dims.hidden if self.dims is not None else 2560)
         out = np.empty((len(ids), 3 * hdim), dtype=np.float32)
         check(lib().flux_cuda_qwen3_forward(self.handle, ids.ctypes.data_as(ip), mp, len(ids), _fp(out)))
+        return out
+
+    def forward_batch(self, ids, mask=None, hidden=None, device=False):
+        """ids, mask: int arrays [batch, seq]. Returns f32 [batch, seq, 3 * hidden], or with device=True the device
+        address of that array (queued, no wait, no copy)."""
+        np = _np()
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        batch, seq = ids.shape
+        ip = ctypes.POINTER(ctypes.c_int)
+        mp = None
+        if mask is not None:
+            mask = np.ascontiguousarray(mask, dtype=np.int32)
+            mp = mask.ctypes.data_as(ip)
+        if device:
+            dev = ctypes.c_void_p()
+            check(lib().flux_cuda_qwen3_forward_batch_device(self.handle, ids.ctypes.data_as(ip), mp, batch, seq,
+                                                             ctypes.byref(dev)))
+            return dev.value
+        hdim = hidden or (self.dims.hidden if self.dims is not None else 2560)
+        out = np.empty((batch, seq, 3 * hdim), dtype=np.float32)
+        check(lib().flux_cuda_qwen3_forward_batch(self.handle, ids.ctypes.data_as(ip), mp, batch, seq, _fp(out)))
         return out
 
     def forward_device(self, ids, mask=None):

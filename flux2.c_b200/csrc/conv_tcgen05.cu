@@ -40,9 +40,55 @@ __device__ __forceinline__ void tma_load_4d_pair(void *smem_dst, const CUtensorM
       : "memory");
 }
 
+// Sums over the warp's 32 rows of N values per lane in N - 1 + 5 - log2(N) shuffles: at every step a lane hands
+// one half of its values to its partner and adds the partner's other half, so the number of live values halves
+// while the number of rows folded into each doubles. Afterwards lane L holds the total of value L >> (5 - log2 N).
+template <int N>
+__device__ __forceinline__ float warp_multi_sum(float (&a)[N], int lane) {
+  int m = 16;
+#pragma unroll
+  for (int half = N / 2; half >= 1; half /= 2, m >>= 1) {
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int j = 0; j < half; ++j) {
+      const float send = up ? a[j] : a[j + half];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, m);
+      a[j] = (up ? a[j + half] : a[j]) + recv;
+    }
+  }
+  float t = a[0];
+  for (; m >= 1; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+  return t;
+}
+
+// v: this row's 32 consecutive output channels = 32 / CPG groups. Stores the warp's per-group sums and sums of
+// squares (rows outside the image count as zero) at dst[0 .. 64 / CPG).
+template <int CPG>
+__device__ __forceinline__ void gn_chunk_sums(const float (&v)[32], bool row_ok, float *dst) {
+  constexpr int NG = 32 / CPG, N = 2 * NG;
+  float a[N];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < CPG; ++j) {
+      const float x = v[g * CPG + j];
+      s += x;
+      ss += x * x;
+    }
+    a[g] = row_ok ? s : 0.f;
+    a[NG + g] = row_ok ? ss : 0.f;
+  }
+  const int lane = threadIdx.x & 31;
+  const float t = warp_multi_sum<N>(a, lane);
+  constexpr int SH = N == 16 ? 1 : (N == 8 ? 2 : 3);  // 5 - log2(N)
+  if ((lane & ((1 << SH) - 1)) == 0) dst[lane >> SH] = t;
+}
+
 // One epilogue thread = one output row (pixel): reads its TMEM lane 32 columns at a time.
 template <int BN>
-__device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, bool row_ok, int n0, uint32_t taddr) {
+__device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, bool row_ok, int n0, uint32_t taddr,
+                                              size_t warp_slot) {
   uint32_t r[32];
   const bool f16 = P.out_f16 != 0;
   if (P.mode == CONV_STORE_RGB8) {
@@ -64,7 +110,7 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
   for (int c = 0; c < BN / 32; ++c) {
     tc_ld_32x32(taddr + c * 32, r);
     tc_wait_ld();
-    if (!row_ok) continue;
+    if (!row_ok && !P.gn_partial) continue;
     const int col = n0 + c * 32;
     float v[32];
     if (P.bias) {
@@ -82,31 +128,38 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
     }
     if (P.mode == CONV_STORE_16) {
-      uint4 *d4 = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(P.out) + row * P.ld + col);
+      if (row_ok) {
+        uint4 *d4 = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(P.out) + row * P.ld + col);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 o;
-        o.x = pack_16x2(v[8 * j + 0], v[8 * j + 1], f16);
-        o.y = pack_16x2(v[8 * j + 2], v[8 * j + 3], f16);
-        o.z = pack_16x2(v[8 * j + 4], v[8 * j + 5], f16);
-        o.w = pack_16x2(v[8 * j + 6], v[8 * j + 7], f16);
-        d4[j] = o;
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_16x2(v[8 * j + 0], v[8 * j + 1], f16);
+          o.y = pack_16x2(v[8 * j + 2], v[8 * j + 3], f16);
+          o.z = pack_16x2(v[8 * j + 4], v[8 * j + 5], f16);
+          o.w = pack_16x2(v[8 * j + 6], v[8 * j + 7], f16);
+          d4[j] = o;
+        }
       }
-    } else {
+    } else if (row_ok) {
       float4 *d4 = reinterpret_cast<float4 *>(reinterpret_cast<float *>(P.out) + row * P.ld + col);
       const bool add = P.mode == CONV_ADD_F32;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float4 o = make_float4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         if (add) {
           const float4 h = d4[j];
-          o.x += h.x;
-          o.y += h.y;
-          o.z += h.z;
-          o.w += h.w;
+          v[4 * j + 0] += h.x;
+          v[4 * j + 1] += h.y;
+          v[4 * j + 2] += h.z;
+          v[4 * j + 3] += h.w;
         }
-        d4[j] = o;
+        d4[j] = make_float4(v[4 * j + 0], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
       }
+    }
+    if (P.gn_partial) {  // statistics of what was just written, for the GroupNorm that reads it next
+      float *dst = P.gn_partial + (warp_slot * (BN / 32) + c) * (64 / P.gn_cpg);
+      if (P.gn_cpg == 4) gn_chunk_sums<4>(v, row_ok, dst);
+      else if (P.gn_cpg == 8) gn_chunk_sums<8>(v, row_ok, dst);
+      else gn_chunk_sums<16>(v, row_ok, dst);
     }
   }
 }
@@ -264,7 +317,7 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      conv_epilogue<BN>(P, row, row_ok, n0, taddr);
+      conv_epilogue<BN>(P, row, row_ok, n0, taddr, (static_cast<size_t>(tile) * 2 + rank) * 4 + q);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
@@ -283,6 +336,54 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
+}
+
+// One block per group: folds the epilogue warps' partial sums in a fixed order (per thread ascending, then a fixed
+// shared-memory tree in double precision).
+__global__ void __launch_bounds__(256) conv_gn_finalize_kernel(const float *__restrict__ partial, int tiles_m, int bn,
+                                                               int cpg, long long pixels, float eps,
+                                                               float *__restrict__ stats) {
+  __shared__ double sa[256], sb[256];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int g = blockIdx.x;
+  const int col0 = g * cpg, tn = col0 / bn, c = (col0 % bn) / 32, gi = (col0 % 32) / cpg, ng = 32 / cpg;
+  const size_t per_slot = static_cast<size_t>(bn / 32) * 2 * ng;
+  const long long entries = static_cast<long long>(tiles_m) * 8;  // (tile, cta, warp) of the tiles covering this group
+  double a = 0.0, b = 0.0;
+  for (long long e = threadIdx.x; e < entries; e += 256) {
+    const size_t slot = static_cast<size_t>(tn) * tiles_m * 8 + e;
+    const float *p = partial + slot * per_slot + static_cast<size_t>(c) * 2 * ng;
+    a += static_cast<double>(__ldcg(p + gi));
+    b += static_cast<double>(__ldcg(p + ng + gi));
+  }
+  sa[threadIdx.x] = a;
+  sb[threadIdx.x] = b;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      sa[threadIdx.x] += sa[threadIdx.x + o];
+      sb[threadIdx.x] += sb[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const double n = static_cast<double>(pixels) * cpg;
+    const double mean = sa[0] / n;
+    double var = sb[0] / n - mean * mean;
+    if (var < 0.0) var = 0.0;
+    stats[2 * g] = static_cast<float>(mean);
+    stats[2 * g + 1] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
+  }
+}
+
+int conv_gn_finalize(const ConvParams &p, long long pixels, float eps, float *stats, cudaStream_t stream) {
+  if (!p.gn_partial || (p.gn_cpg != 4 && p.gn_cpg != 8 && p.gn_cpg != 16) || p.Cout != 32 * p.gn_cpg) return -5;
+  return launch_kernel(conv_gn_finalize_kernel, dim3(32), dim3(256), 0, stream, 1,
+                       static_cast<const float *>(p.gn_partial), p.tiles_m, p.bn, p.gn_cpg, pixels, eps, stats) ==
+                 cudaSuccess
+             ? 0
+             : -8;
 }
 
 // ---------------------------------------------------------------------------------------------- host
@@ -389,6 +490,9 @@ int conv_launch(ConvParams *p, int num_sms, cudaStream_t stream) {
   const int total = p->tiles_m * p->tiles_n;
   if (total < 1 || !p->out || !p->err) return -5;
   if (p->mode == CONV_STORE_RGB8 && p->tiles_n != 1) return -6;
+  if (p->gn_partial && (p->mode == CONV_STORE_RGB8 || p->Cout != 32 * p->gn_cpg ||
+                        (p->gn_cpg != 4 && p->gn_cpg != 8 && p->gn_cpg != 16)))
+    return -7;
   int pairs = num_sms / 2;
   if (total < pairs) pairs = total;
   cudaError_t e = p->bn == 256 ? launch_kernel(conv2_tn_kernel<256>, dim3(2 * pairs), dim3(C_THREADS), ConvCfg<256>::SMEM,

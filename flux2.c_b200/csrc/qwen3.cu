@@ -232,7 +232,7 @@ int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims,
   if (!rc) rc = q_alloc(m, &m->attn, S * qd);
   if (!rc) rc = q_alloc(m, &m->act, S * it);
   if (!rc) rc = q_alloc(m, &m->ids, S);
-  if (!rc) rc = q_alloc(m, &m->mask, (S + 31) / 32 + 4);
+  if (!rc) rc = q_alloc(m, &m->mask, S / 32 + S + 4);  // [batch, ceil(seq / 32)] words for any split of S tokens
   if (!rc) {
     std::vector<float> ones(h, 1.0f), cs(S * 64), sn(S * 64);
     for (size_t p = 0; p < S; ++p)
@@ -443,8 +443,10 @@ static int q_residual_gemm(flux_cuda_qwen3 *m, const void *X, long long ldx, con
 }
 
 // Queues the whole pass on the context's stream; the result is m->out ([seq, 3 * hidden] f32, device).
-static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq) {
-  if (!m || !input_ids || seq < 1) {
+// `batch` prompts of `seq` tokens each (ids and mask [batch, seq]); rows of all prompts go through the layers together,
+// attention sees each prompt on its own.
+static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, int batch) {
+  if (!m || !input_ids || seq < 1 || batch < 1) {
     set_error("qwen3_forward: bad argument");
     return FLUX_CUDA_ERR_ARG;
   }
@@ -452,8 +454,8 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
     set_error("qwen3_forward: model is not finalized");
     return FLUX_CUDA_ERR_MODEL;
   }
-  if (seq > m->max_seq) {
-    set_error("qwen3_forward: %d tokens exceed the capacity of %d", seq, m->max_seq);
+  if (static_cast<long long>(seq) * batch > m->max_seq) {
+    set_error("qwen3_forward: %d x %d tokens exceed the capacity of %d", batch, seq, m->max_seq);
     return FLUX_CUDA_ERR_ARG;
   }
   cudaSetDevice(m->ctx->device);
@@ -461,14 +463,16 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
   const flux_cuda_qwen3_dims &d = m->d;
   const int h = d.hidden, hd = d.head_dim, qd = d.heads * hd, kd = d.kv_heads * hd, it = d.inter;
   const int qkv_n = qd + 2 * kd, f16 = m->f16 ? 1 : 0;
+  const int rows = seq * batch;
   const int words = (seq + 31) / 32;
-  std::vector<uint32_t> bits(words, 0u);
-  for (int j = 0; j < seq; ++j)
-    if (!attention_mask || attention_mask[j]) bits[j >> 5] |= 1u << (j & 31);
-  int rc = check_cuda(cudaMemcpyAsync(m->ids, input_ids, seq * sizeof(int), cudaMemcpyHostToDevice, st), "upload ids");
-  if (!rc) rc = check_cuda(cudaMemcpyAsync(m->mask, bits.data(), words * 4, cudaMemcpyHostToDevice, st), "upload mask");
+  std::vector<uint32_t> bits(static_cast<size_t>(words) * batch, 0u);
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < seq; ++j)
+      if (!attention_mask || attention_mask[b * seq + j]) bits[static_cast<size_t>(b) * words + (j >> 5)] |= 1u << (j & 31);
+  int rc = check_cuda(cudaMemcpyAsync(m->ids, input_ids, rows * sizeof(int), cudaMemcpyHostToDevice, st), "upload ids");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(m->mask, bits.data(), bits.size() * 4, cudaMemcpyHostToDevice, st), "upload mask");
   if (rc) return rc;
-  embed_gather_kernel<<<seq, 256, 0, st>>>(m->embed, m->ids, m->hidden, h, d.vocab, f16);
+  embed_gather_kernel<<<rows, 256, 0, st>>>(m->embed, m->ids, m->hidden, h, d.vocab, f16);
 
   auto seg = [&](int mode, void *dst, long long ld, int col0, const float *gate) {
     EpiSeg s;
@@ -487,7 +491,7 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
   const long long pstride = static_cast<long long>(m->max_seq) * h;
   for (int l = 0; l < m->run_layers && !gr; ++l) {
     const QwenLayer &w = m->layers[l];
-    gr = launch_rmsnorm(m->hidden, m->norm, w.ln1, seq, h, f16, m->part, pending, pstride, st);
+    gr = launch_rmsnorm(m->hidden, m->norm, w.ln1, rows, h, f16, m->part, pending, pstride, st);
     pending = 0;
     if (gr) break;
     EpiSeg sq = seg(EPI_QKV_NORM_ROPE, m->qkv, qkv_n, 0, nullptr);
@@ -501,40 +505,40 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
     sq.qk.q_cols = qd;
     sq.qk.k_cols = kd;
     sq.qk.half_split = 1;
-    gr = q_gemm(m, m->norm, h, w.qkv, seq, qkv_n, h, sq);
+    gr = q_gemm(m, m->norm, h, w.qkv, rows, qkv_n, h, sq);
     if (gr) break;
     AttnParams A;
-    gr = attn2_make_params(&A, m->qkv, 1, seq, qkv_n, 0, qd, qd + kd, m->attn, qd, 0, d.heads, f16, m->ctx->err_dev);
+    gr = attn2_make_params(&A, m->qkv, batch, seq, qkv_n, 0, qd, qd + kd, m->attn, qd, 0, d.heads, f16, m->ctx->err_dev);
     if (gr) break;
     A.kv_group = d.heads / d.kv_heads;
     A.causal = 1;
     A.key_mask = m->mask;
     gr = attn2_launch(&A, st);
     if (gr) break;
-    pending = q_residual_gemm(m, m->attn, qd, w.o, seq, qd);
+    pending = q_residual_gemm(m, m->attn, qd, w.o, rows, qd);
     if (pending < 0) {
       gr = pending;
       break;
     }
-    gr = launch_rmsnorm(m->hidden, m->norm, w.ln2, seq, h, f16, m->part, pending, pstride, st);
+    gr = launch_rmsnorm(m->hidden, m->norm, w.ln2, rows, h, f16, m->part, pending, pstride, st);
     pending = 0;
     if (gr) break;
-    gr = q_gemm(m, m->norm, h, w.gateup, seq, 2 * it, h, seg(EPI_SWIGLU_BF16, m->act, it, 0, nullptr));
+    gr = q_gemm(m, m->norm, h, w.gateup, rows, 2 * it, h, seg(EPI_SWIGLU_BF16, m->act, it, 0, nullptr));
     if (gr) break;
-    pending = q_residual_gemm(m, m->act, it, w.down, seq, it);
+    pending = q_residual_gemm(m, m->act, it, w.down, rows, it);
     if (pending < 0) {
       gr = pending;
       break;
     }
     const bool collect = next_out < 3 && l == d.out_layers[next_out];
     if (pending > 0 && (collect || l + 1 == m->run_layers)) {  // nobody after this layer folds the slices: do it now
-      gr = launch_rmsnorm(m->hidden, nullptr, w.ln1, seq, h, f16, m->part, pending, pstride, st);
+      gr = launch_rmsnorm(m->hidden, nullptr, w.ln1, rows, h, f16, m->part, pending, pstride, st);
       pending = 0;
       if (gr) break;
     }
     if (collect) {
       rc = check_cuda(cudaMemcpy2DAsync(m->out + static_cast<size_t>(next_out) * h, 3 * h * sizeof(float), m->hidden,
-                                        h * sizeof(float), h * sizeof(float), seq, cudaMemcpyDeviceToDevice, st),
+                                        h * sizeof(float), h * sizeof(float), rows, cudaMemcpyDeviceToDevice, st),
                       "collect layer output");
       if (rc) return rc;
       ++next_out;
@@ -553,9 +557,18 @@ int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int 
     set_error("qwen3_forward: bad argument");
     return FLUX_CUDA_ERR_ARG;
   }
-  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq);
+  return flux_cuda_qwen3_forward_batch(m, input_ids, attention_mask, 1, seq, out);
+}
+
+int flux_cuda_qwen3_forward_batch(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int batch, int seq,
+                                  float *out) {
+  if (!out) {
+    set_error("qwen3_forward: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq, batch);
   if (rc) return rc;
-  rc = check_cuda(cudaMemcpyAsync(out, m->out, static_cast<size_t>(seq) * 3 * m->d.hidden * sizeof(float),
+  rc = check_cuda(cudaMemcpyAsync(out, m->out, static_cast<size_t>(seq) * batch * 3 * m->d.hidden * sizeof(float),
                                   cudaMemcpyDeviceToHost, m->ctx->stream),
                   "download embeddings");
   if (!rc) rc = ctx_sync_check(m->ctx);
@@ -568,8 +581,17 @@ int flux_cuda_qwen3_forward_device(flux_cuda_qwen3 *m, const int *input_ids, con
     set_error("qwen3_forward_device: bad argument");
     return FLUX_CUDA_ERR_ARG;
   }
+  return flux_cuda_qwen3_forward_batch_device(m, input_ids, attention_mask, 1, seq, out_dev);
+}
+
+int flux_cuda_qwen3_forward_batch_device(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int batch,
+                                         int seq, const float **out_dev) {
+  if (!out_dev) {
+    set_error("qwen3_forward_device: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
   *out_dev = nullptr;
-  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq);
+  int rc = qwen3_enqueue(m, input_ids, attention_mask, seq, batch);
   if (rc) return rc;
   *out_dev = m->out;
   return FLUX_CUDA_OK;

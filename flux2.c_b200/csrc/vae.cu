@@ -13,6 +13,7 @@
 // convolutions read the input as four parity planes written by one 16-bit conversion pass (conv.cuh).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <map>
@@ -79,6 +80,8 @@ struct flux_cuda_vae {
   size_t cap_elems = 0, cap_tok = 0;
   float *xa = nullptr, *xb = nullptr, *scores = nullptr, *stats = nullptr, *partial = nullptr, *lat = nullptr;
   float *img_in = nullptr;  // the encoder's input image [3, 16h, 16w]
+  float *gnp = nullptr;     // GroupNorm partial sums written by the convolution epilogues
+  bool fused_gn = true;     // FLUX_CUDA_VAE_FUSED_GN=0: statistics by a separate pass over the tensor
   uint16_t *a16 = nullptr, *h16 = nullptr, *qkv16 = nullptr, *vt16 = nullptr, *p16 = nullptr, *o16 = nullptr;
   unsigned int *counters = nullptr;
   uint8_t *img = nullptr;
@@ -182,6 +185,7 @@ int ensure_workspace(flux_cuda_vae *v, int h, int w) {
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->lat, static_cast<size_t>(128) * h * w);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->img, static_cast<size_t>(256) * h * w * 3);
   if (!rc && v->has_encoder) rc = v_alloc(v, v->ws_allocs, &v->img_in, static_cast<size_t>(256) * h * w * 3);
+  if (!rc) rc = v_alloc(v, v->ws_allocs, &v->gnp, static_cast<size_t>(512) * h * w + 8192);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->stats, GN_GROUPS * 2);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->partial, static_cast<size_t>(GN_MAX_BLOCKS) * 64);
   if (!rc) rc = v_alloc(v, v->ws_allocs, &v->counters, 4, true);
@@ -196,36 +200,43 @@ struct Runner {
   cudaStream_t st;
   int f16, sms;
   int rc = 0;
+  // statistics of the tensor the last convolution wrote, still to be folded (gn_next launches)
+  bool pending = false;
+  ConvParams lastP;
+  long long last_pixels = 0;
 
   void note(int r) {
     ++v->launches;
     if (r && !rc) rc = r;
   }
-  void conv3(const ConvW &c, const void *in16, int H, int W, int mode, void *out, long long ld) {
+  // gn_next: the tensor written is normalised by a GroupNorm next, so the epilogue also leaves its statistics
+  void conv3(const ConvW &c, const void *in16, int H, int W, int mode, void *out, long long ld, bool gn_next = false) {
     if (rc) return;
     ConvParams P;
     memset(&P, 0, sizeof(P));
     int r = conv_make_3x3(&P, in16, 1, H, W, c.cin_pad, c.w, c.cout_pad);
     if (r) return note(r);
-    finish(P, c, mode, out, ld);
+    finish(P, c, mode, out, ld, gn_next);
   }
-  void conv3_s2(const ConvW &c, const void *planes16, int Ho, int Wo, int mode, void *out, long long ld) {
+  void conv3_s2(const ConvW &c, const void *planes16, int Ho, int Wo, int mode, void *out, long long ld,
+                bool gn_next = false) {
     if (rc) return;
     ConvParams P;
     memset(&P, 0, sizeof(P));
     int r = conv_make_3x3_s2(&P, planes16, 1, Ho, Wo, c.cin_pad, c.w, c.cout_pad);
     if (r) return note(r);
-    finish(P, c, mode, out, ld);
+    finish(P, c, mode, out, ld, gn_next);
   }
-  void gemm(const ConvW &c, const void *in16, long long ldx, long long M, int mode, void *out, long long ld) {
+  void gemm(const ConvW &c, const void *in16, long long ldx, long long M, int mode, void *out, long long ld,
+            bool gn_next = false) {
     if (rc) return;
     ConvParams P;
     memset(&P, 0, sizeof(P));
     int r = conv_make_gemm(&P, in16, ldx, c.w, c.cin_pad, static_cast<int>(M), c.cout_pad, c.cin_pad, c.cout_pad);
     if (r) return note(r);
-    finish(P, c, mode, out, ld);
+    finish(P, c, mode, out, ld, gn_next);
   }
-  void finish(ConvParams &P, const ConvW &c, int mode, void *out, long long ld) {
+  void finish(ConvParams &P, const ConvW &c, int mode, void *out, long long ld, bool gn_next = false) {
     P.mode = mode;
     P.out = out;
     P.ld = ld;
@@ -233,11 +244,24 @@ struct Runner {
     P.out_f16 = f16;
     P.x_f16 = f16;
     P.err = v->ctx->err_dev;
+    const int cpg = c.cout / GN_GROUPS;
+    pending = false;
+    if (gn_next && v->fused_gn && c.cout == c.cout_pad && c.cout == cpg * GN_GROUPS && (cpg == 4 || cpg == 8 || cpg == 16)) {
+      P.gn_partial = v->gnp;
+      P.gn_cpg = cpg;
+      pending = true;
+      lastP = P;
+      last_pixels = P.M;
+    }
     note(conv_launch(&P, sms, st));
   }
   void gn(const void *x, int in16, long long pixels, int C, const float *g, const float *b, int swish, void *out16) {
     if (rc) return;
-    note(launch_gn_stats(x, in16, f16, 1, pixels, C, v->eps, v->partial, v->counters, v->stats, st));
+    if (pending && last_pixels == pixels && lastP.Cout == C)
+      note(conv_gn_finalize(lastP, pixels, v->eps, v->stats, st));
+    else
+      note(launch_gn_stats(x, in16, f16, 1, pixels, C, v->eps, v->partial, v->counters, v->stats, st));
+    pending = false;
     if (rc) return;
     note(launch_gn_apply(x, in16, out16, f16, 1, pixels, C, v->stats, g, b, swish, st));
   }
@@ -267,20 +291,20 @@ struct Runner {
       if (r) return note(r);
       finish(P, none, CONV_STORE_16, v->o16 + r0 * 512, 512);
     }
-    gemm(a.out, v->o16, 512, T, CONV_ADD_F32, x, 512);
+    gemm(a.out, v->o16, 512, T, CONV_ADD_F32, x, 512, true);
   }
   // x (f32 [P, cin]) -> x (f32 [P, cout]); returns the buffer that holds the result
   float *res(const ResW &r, float *x, float *other, int H, int W) {
     const long long P = static_cast<long long>(H) * W;
     gn(x, 0, P, r.cin, r.g1, r.b1, 1, v->a16);
-    conv3(r.c1, v->a16, H, W, CONV_STORE_16, v->h16, r.cout);
+    conv3(r.c1, v->a16, H, W, CONV_STORE_16, v->h16, r.cout, true);
     gn(v->h16, 1, P, r.cout, r.g2, r.b2, 1, v->a16);
     if (r.cin != r.cout) {
       if (!rc) note(launch_f32_to_bf16(x, v->h16, P * r.cin, f16, st));
       gemm(r.skip, v->h16, r.cin, P, CONV_STORE_F32, other, r.cout);
       x = other;
     }
-    conv3(r.c2, v->a16, H, W, CONV_ADD_F32, x, r.cout);
+    conv3(r.c2, v->a16, H, W, CONV_ADD_F32, x, r.cout, true);
     return x;
   }
 };
@@ -309,6 +333,7 @@ int flux_cuda_vae_create(flux_cuda_ctx *ctx, flux_cuda_vae **out) {
   flux_cuda_vae *v = new flux_cuda_vae();
   v->ctx = ctx;
   v->f16 = ctx->f16;
+  if (const char *e = getenv("FLUX_CUDA_VAE_FUSED_GN")) v->fused_gn = atoi(e) != 0;
   const int base = 128, mult[4] = {1, 2, 4, 4}, mid = base * mult[3];
   int rc = make_vec(v, &v->bn_mean, 128);
   if (!rc) rc = make_vec(v, &v->bn_var, 128);
@@ -533,7 +558,7 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
       x = now;
     }
   };
-  R.conv3(v->conv_in, v->a16, H, W, CONV_STORE_F32, x, 512);
+  R.conv3(v->conv_in, v->a16, H, W, CONV_STORE_F32, x, 512, true);
   swap_to(R.res(v->mid[0], x, other, H, W));
   R.attention(v->attn, x, T);
   swap_to(R.res(v->mid[1], x, other, H, W));
@@ -545,7 +570,7 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
       if (!R.rc) R.note(launch_upsample2x(x, v->a16, R.f16, 1, H, W, c.cin, st));
       H *= 2;
       W *= 2;
-      R.conv3(c, v->a16, H, W, CONV_STORE_F32, x, c.cout);
+      R.conv3(c, v->a16, H, W, CONV_STORE_F32, x, c.cout, true);
     }
   }
   R.gn(x, 0, static_cast<long long>(H) * W, 128, v->out_g, v->out_b, 1, v->a16);
@@ -589,7 +614,7 @@ static int vae_encode_enqueue(flux_cuda_vae *v, const float *image, int H, int W
       x = now;
     }
   };
-  R.conv3(v->e_conv_in, v->a16, H, W, CONV_STORE_F32, x, 128);
+  R.conv3(v->e_conv_in, v->a16, H, W, CONV_STORE_F32, x, 128, true);
   int ei = 0;
   for (int level = 0; level < 4; ++level) {
     for (int r = 0; r < 2; ++r) swap_to(R.res(v->e_res[ei++], x, other, H, W));
@@ -598,7 +623,7 @@ static int vae_encode_enqueue(flux_cuda_vae *v, const float *image, int H, int W
       if (!R.rc) R.note(launch_parity_planes(x, v->a16, R.f16, 1, H, W, c.cin, st));
       H /= 2;
       W /= 2;
-      R.conv3_s2(c, v->a16, H, W, CONV_STORE_F32, x, c.cout);
+      R.conv3_s2(c, v->a16, H, W, CONV_STORE_F32, x, c.cout, true);
     }
   }
   const long long T = static_cast<long long>(H) * W;

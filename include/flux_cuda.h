@@ -202,7 +202,8 @@ typedef struct flux_cuda_qwen3_dims {
 /* The Qwen3-4B shape the reference hard-codes (flux_qwen3.h:21-40): outputs after layers 8, 17, 26. */
 void flux_cuda_qwen3_dims_4b(flux_cuda_qwen3_dims *d);
 /* Loads `text_encoder/` (both model-0000{1,2}-of-00002.safetensors must exist, flux_qwen3.c:1341-1356). Only the
- * layers the output depends on are kept on the device (and only those must be present in the files). max_seq: largest token count of a later forward. */
+ * layers the output depends on are kept on the device (and only those must be present in the files). max_seq: largest
+ * token count of a later forward (batch * seq for a batched one). */
 int flux_cuda_qwen3_load_dir(flux_cuda_ctx *ctx, const char *model_dir, int max_seq, flux_cuda_qwen3 **out);
 int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims, int max_seq, flux_cuda_qwen3 **out);
 int flux_cuda_qwen3_set_tensor(flux_cuda_qwen3 *m, const char *name, const void *data, int dtype,
@@ -212,6 +213,13 @@ void flux_cuda_qwen3_free(flux_cuda_qwen3 *m);
 /* input_ids, attention_mask (may be NULL = all ones): host int[seq]; out: host f32 [seq, 3 * hidden]. Causal,
  * grouped-query attention with the key padding mask, as the reference's CPU path (flux_qwen3.c:313-452). */
 int flux_cuda_qwen3_forward(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int seq, float *out);
+/* Several prompts in one pass: input_ids and attention_mask are [batch, seq] (every prompt padded to the same seq),
+ * out is host f32 [batch, seq, 3 * hidden]; batch * seq must not exceed the max_seq given at creation. The projections
+ * of all prompts run as one GEMM each (the weights are read once for the batch), attention per prompt. */
+int flux_cuda_qwen3_forward_batch(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int batch, int seq,
+                                  float *out);
+int flux_cuda_qwen3_forward_batch_device(flux_cuda_qwen3 *m, const int *input_ids, const int *attention_mask, int batch,
+                                         int seq, const float **out_dev);
 /* The same pass, queued on the context's stream without waiting and without the device -> host copy: *out_dev is the
  * encoder's own device buffer, f32 [seq, 3 * hidden], valid (in stream order) until the next forward on this
  * encoder. Hand it to flux_cuda_sampler_upload as the context: prompt -> latent then never leaves the device. No

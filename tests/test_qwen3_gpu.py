@@ -74,6 +74,23 @@ def test_encoder_rejects_bad_calls(tiny_enc, fx, ctx):
         fx.TextEncoder.from_tensors(ctx, d, W)
 
 
+def test_batch_of_prompts_equals_single_prompts(tiny_enc):
+    """Three prompts with different padding in one pass: every prompt's rows equal its own single-prompt pass (up to
+    the summation order of the split-K projections, which depends on the row count)."""
+    synth, d, enc, oracle = tiny_enc
+    seq = 96
+    rng = np.random.default_rng(17)
+    ids = rng.integers(0, d.vocab, (3, seq))
+    mask = np.array([[1] * 96, [1] * 40 + [0] * 56, [1] * 77 + [0] * 19])
+    got = enc.forward_batch(ids, mask)
+    assert got.shape == (3, seq, 3 * d.hidden)
+    for b in range(3):
+        assert rel(got[b], enc.forward(ids[b], mask[b])) < 1e-4
+        assert rel(got[b], oracle.forward(ids[b], mask[b])) < TOL
+    with pytest.raises(Exception):
+        enc.forward_batch(rng.integers(0, d.vocab, (6, seq)), None)  # 576 tokens: more than the capacity of 512
+
+
 def test_embeddings_stay_on_the_device(tiny_enc, fx, ctx):
     """forward_device hands the sampler a device buffer: the latent equals the one obtained through host embeddings."""
     import torch

@@ -261,3 +261,24 @@ def test_encode_then_decode_and_decoder_only_models(vae, fx, ctx):
         fx.Vae.from_tensors(ctx, half)
     with pytest.raises(fx.FluxCudaError):
         v.encode(np.zeros((3, 40, 64), dtype=np.float32))  # 40 is not a multiple of 16
+
+
+def test_fused_statistics_match_the_separate_pass(vae, fx, ctx):
+    """GroupNorm statistics come from the producing convolution's epilogue; a decoder created with
+    FLUX_CUDA_VAE_FUSED_GN=0 recomputes them by a pass over the tensor. The two images may differ by rounding only."""
+    synth, W, v, oracle = vae
+    os.environ["FLUX_CUDA_VAE_FUSED_GN"] = "0"
+    try:
+        v2 = fx.Vae.from_tensors(ctx, W)
+    finally:
+        del os.environ["FLUX_CUDA_VAE_FUSED_GN"]
+    try:
+        for h, w in ((4, 4), (9, 7), (16, 16)):
+            lat = synth.make_latent(50 + h, 128, h, w)
+            a, b = v.decode(lat).astype(np.int32), v2.decode(lat).astype(np.int32)
+            assert np.abs(a - b).max() <= 2 and psnr(a, b) >= 55.0
+        img = np.random.default_rng(4).uniform(-1.0, 1.0, (3, 64, 80)).astype(np.float32)
+        la, lb = v.encode(img), v2.encode(img)
+        assert float(np.linalg.norm(la - lb) / np.linalg.norm(lb)) < 2e-3
+    finally:
+        v2.close()
