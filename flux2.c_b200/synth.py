@@ -315,3 +315,29 @@ def write_safetensors(path, tensors, dtype="BF16"):
         for arr in tensors.values():
             f.write(np.ascontiguousarray(arr).tobytes() if arr.size < (1 << 20) else memoryview(np.ascontiguousarray(arr)))
     return off + 8 + len(hj)
+
+
+def write_tokenizer_json(path):
+    """A minimal byte-level BPE tokenizer file in the layout the reference's loader reads (flux_qwen3_tokenizer.c:
+    317-600): "model": {"vocab": {token: id}, "merges": [[left, right], ...]}. The vocabulary is the 256 byte symbols
+    of the GPT-2 byte-to-unicode table (ids 0..255) plus a few merged pairs, so any prompt tokenizes; the chat
+    template's special tokens have fixed ids inside the loader (flux_qwen3_tokenizer.c:25-29) and need no entry."""
+    import os
+    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    sym = {b: chr(c) for b, c in zip(bs, cs)}
+    vocab = {sym[b]: b for b in range(256)}
+    merges = []
+    for left, right in (("t", "h"), ("a", "n"), (sym[32], "a"), ("i", "n"), ("th", "e"), (sym[32], "c")):
+        merges.append([left, right])
+        vocab[left + right] = len(vocab)
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump({"version": "1.0", "added_tokens": [], "model": {"type": "BPE", "vocab": vocab, "merges": merges}}, f,
+                  ensure_ascii=False)

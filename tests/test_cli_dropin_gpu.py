@@ -2,8 +2,9 @@
 
 oracle/Makefile (`make cli`) links the reference's main.c / flux.c / flux_cli.c / flux_vae.c / ... twice: once as the
 plain reference (`flux_ref_cli`, BLAS build) and once with flux_transformer.c + flux_sample.c replaced by the seam
-(`flux_cuda_cli`, which calls libflux_cuda.so). Both are run on the same synthetic model directory with the same
-external embeddings and noise; the decoded PNGs must agree to PSNR >= 30 dB.
+(`flux_cuda_cli`, which calls libflux_cuda.so; flux_qwen3.c is replaced too and the VAE's functions are redirected).
+Both are run on the same synthetic model directory, first with external embeddings and noise, then from a text
+prompt (tokenizer -> text encoder -> denoising -> VAE -> PNG); the decoded PNGs must agree to PSNR >= 30 dB.
 """
 import os
 import subprocess
@@ -62,47 +63,75 @@ def read_png_rgb(path):
     return out.reshape(h, w, ch)[:, :, :3].astype(np.float64)
 
 
-def test_reference_cli_runs_on_the_engine(fx, tmp_path):
+@pytest.fixture(scope="module")
+def model_dir(fx, tmp_path_factory):
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no GPU")
-    cuda_cli, ref_cli = os.path.join(REF, "flux_cuda_cli"), os.path.join(REF, "flux_ref_cli")
-    if not (os.path.exists(cuda_cli) and os.path.exists(ref_cli)):
+    if not (os.path.exists(os.path.join(REF, "flux_cuda_cli")) and os.path.exists(os.path.join(REF, "flux_ref_cli"))):
         pytest.skip("oracle/_ref CLIs not built (make -C oracle cli)")
+    import shutil
     import flux2_c_b200.synth as synth
-    base = "/dev/shm" if os.access("/dev/shm", os.W_OK) else str(tmp_path)
+    base = "/dev/shm" if os.access("/dev/shm", os.W_OK) else str(tmp_path_factory.mktemp("model"))
     mdir = os.path.join(base, "flux_synth_model_%d" % os.getpid())
-    os.makedirs(os.path.join(mdir, "transformer"), exist_ok=True)
-    os.makedirs(os.path.join(mdir, "vae"), exist_ok=True)
-    tpath = os.path.join(mdir, "transformer", "diffusion_pytorch_model.safetensors")
-    vpath = os.path.join(mdir, "vae", "diffusion_pytorch_model.safetensors")
     try:
         d = synth.Dims.klein4b()
-        synth.write_safetensors(tpath, synth.make_transformer_weights(d, seed=0, threads=os.cpu_count()))
-        synth.write_safetensors(vpath, synth.make_vae_weights(), dtype="F32")
+        synth.write_safetensors(os.path.join(_mk(mdir, "transformer"), "diffusion_pytorch_model.safetensors"),
+                                synth.make_transformer_weights(d, seed=0, threads=os.cpu_count()))
+        synth.write_safetensors(os.path.join(_mk(mdir, "vae"), "diffusion_pytorch_model.safetensors"),
+                                synth.make_vae_weights(), dtype="F32")
         open(os.path.join(mdir, "model_index.json"), "w").write('{"_class_name": "Flux2KleinPipeline", "is_distilled": true}')
-        emb, noise = str(tmp_path / "emb.bin"), str(tmp_path / "noise.bin")
-        synth.make_context(1234, 512, d.text_dim).tofile(emb)
-        fx.init_noise(128, 8, 8, 42).tofile(noise)
-        outs = {}
-        # the reference's BLAS build needs the OpenBLAS (and its libgfortran / libquadmath) bundled in the image's wheels
-        site = os.path.dirname(os.path.dirname(np.__file__))
-        libs = ":".join(os.path.join(site, d) for d in ("opencv_python_headless.libs", "scipy.libs"))
-        env = dict(os.environ, OPENBLAS_NUM_THREADS=str(os.cpu_count()),
-                   LD_LIBRARY_PATH=libs + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
-        for name, exe in (("cuda", cuda_cli), ("ref", ref_cli)):
-            out = str(tmp_path / ("out_%s.png" % name))
-            cmd = [exe, "-d", mdir, "-e", emb, "-n", noise, "-W", "128", "-H", "128", "-s", "4", "-S", "42", "-o", out,
-                   "-q", "--no-mmap"]
-            r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
-            assert r.returncode == 0, "%s failed:\n%s\n%s" % (name, r.stdout[-2000:], r.stderr[-2000:])
-            outs[name] = read_png_rgb(out)
+        yield synth, d, mdir
     finally:
-        for p in (tpath, vpath, os.path.join(mdir, "model_index.json")):
-            if os.path.exists(p):
-                os.remove(p)
+        shutil.rmtree(mdir, ignore_errors=True)
+
+
+def _mk(*parts):
+    p = os.path.join(*parts)
+    os.makedirs(p, exist_ok=True)
+    return p
+
+
+def _run_both(args, tmp_path, tag):
+    # the reference's BLAS build needs the OpenBLAS (and its libgfortran / libquadmath) bundled in the image's wheels
+    site = os.path.dirname(os.path.dirname(np.__file__))
+    libs = ":".join(os.path.join(site, d) for d in ("opencv_python_headless.libs", "scipy.libs"))
+    env = dict(os.environ, OPENBLAS_NUM_THREADS=str(os.cpu_count()),
+               LD_LIBRARY_PATH=libs + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    outs = {}
+    for name in ("cuda", "ref"):
+        out = str(tmp_path / ("out_%s_%s.png" % (tag, name)))
+        cmd = [os.path.join(REF, "flux_%s_cli" % name)] + args + ["-o", out, "-q", "--no-mmap"]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
+        assert r.returncode == 0, "%s failed:\n%s\n%s" % (name, r.stdout[-2000:], r.stderr[-2000:])
+        outs[name] = read_png_rgb(out)
     a, b = outs["cuda"], outs["ref"]
     assert a.shape == b.shape == (128, 128, 3)
     assert b.std() > 10
-    psnr = 10 * np.log10(255.0 ** 2 / max(((a - b) ** 2).mean(), 1e-12))
+    return 10 * np.log10(255.0 ** 2 / max(((a - b) ** 2).mean(), 1e-12))
+
+
+def test_reference_cli_runs_on_the_engine(fx, model_dir, tmp_path):
+    synth, d, mdir = model_dir
+    emb, noise = str(tmp_path / "emb.bin"), str(tmp_path / "noise.bin")
+    synth.make_context(1234, 512, d.text_dim).tofile(emb)
+    fx.init_noise(128, 8, 8, 42).tofile(noise)
+    psnr = _run_both(["-d", mdir, "-e", emb, "-n", noise, "-W", "128", "-H", "128", "-s", "4", "-S", "42"], tmp_path, "emb")
+    assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+
+
+def test_reference_cli_from_a_text_prompt(fx, model_dir, tmp_path):
+    """`flux -p "..."`: the reference's tokenizer feeds the text encoder, which runs on the GPU in one build and on the
+    CPU in the other; a byte-level tokenizer file and seeded Qwen3-4B-shaped weights stand in for the real ones."""
+    synth, d, mdir = model_dir
+    import shutil
+    qd = synth.QwenDims.qwen3_4b()
+    try:
+        synth.write_tokenizer_json(os.path.join(mdir, "tokenizer", "tokenizer.json"))
+        synth.write_qwen_shards(os.path.join(mdir, "text_encoder"), synth.make_qwen_weights(qd, seed=0,
+                                                                                            threads=os.cpu_count()))
+        psnr = _run_both(["-d", mdir, "-p", "a cat in the rain and the thin man", "-W", "128", "-H", "128", "-s", "4",
+                          "-S", "42"], tmp_path, "prompt")
+    finally:
+        shutil.rmtree(os.path.join(mdir, "text_encoder"), ignore_errors=True)
     assert psnr >= 30.0, "PSNR %.1f dB" % psnr
