@@ -205,9 +205,21 @@ def run_micro(args):
         out = torch.zeros(M, N, device="cuda", dtype=torch.float16)
         torch.cuda.synchronize()
         epi = fx.EPI_STORE_BF16 | fx.EPI_X_F16 | fx.EPI_OUT_F16
-        ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi, tile_n=args.tile_n))
+        if args.epi == "qkv":
+            # the fused [Q|K|V] projection with per-head RMSNorm and rotation in the epilogue (N = 3 * heads * 128)
+            wq = torch.randn(128, device="cuda")
+            ang = torch.rand(M, 64, device="cuda") * 6.28
+            cos = torch.cos(ang).repeat_interleave(2, dim=1).contiguous()
+            sin = torch.sin(ang).repeat_interleave(2, dim=1).contiguous()
+            torch.cuda.synchronize()
+            ms = timed(lambda: ctx.gemm_qkv_norm_rope(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N // 3, K,
+                                                      wq.data_ptr(), wq.data_ptr(), cos.data_ptr(), sin.data_ptr(), M,
+                                                      f16=True))
+        else:
+            ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
+                                             tile_n=args.tile_n))
         tf = 2.0 * M * N * K / ms / 1e9
-        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "ms": ms, "tflops": tf, "frac_of_burst_peak":
+        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "epilogue": args.epi, "ms": ms, "tflops": tf, "frac_of_burst_peak":
                           tf / peaks["bf16"], "peak_source": peaks["source"]}))
     elif args.micro == "attn":
         seq, heads = args.seq, 24
@@ -775,6 +787,7 @@ def main():
     ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "load"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
+    ap.add_argument("--epi", default="store", choices=["store", "qkv"], help="epilogue of --micro gemm")
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--size", type=int, default=512, help="image side for --micro vae")
