@@ -282,3 +282,13 @@ def test_fused_statistics_match_the_separate_pass(vae, fx, ctx):
         assert float(np.linalg.norm(la - lb) / np.linalg.norm(lb)) < 2e-3
     finally:
         v2.close()
+
+
+def test_decode_with_attention_in_row_chunks(vae):
+    """736 x 736: the mid block's attention has 8464 tokens, more than one chunk of 8192 score rows."""
+    synth, W, v, oracle = vae
+    lat = synth.make_latent(8, 128, 46, 46)
+    want, _ = oracle.decode(lat)
+    got = v.decode(lat)
+    assert got.shape == (736, 736, 3)
+    assert psnr(got, want) >= 40.0
