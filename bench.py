@@ -2,7 +2,7 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv|load [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv|gn|load [...]            # one kernel, small memory (for ncu captures)
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
 (1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
@@ -243,6 +243,21 @@ def run_micro(args):
         gbs = rows * hid * 6.0 / ms / 1e6
         print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
                           gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+    elif args.micro == "gn":
+        # K9: GroupNorm(32) + swish over a channels-last f32 tensor of --size x --size pixels x --shape[1] channels
+        # (statistics pass + normalise pass): algorithmic bytes = 2 reads of the f32 input + 1 write of the 16-bit output
+        side, C = args.size, args.shape[1]
+        x = torch.randn(1, side * side, C, device="cuda") * 2 + 0.5
+        g = torch.randn(C, device="cuda")
+        b = torch.randn(C, device="cuda")
+        out = torch.zeros(1, side * side, C, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        ms = timed(lambda: ctx.group_norm(x.data_ptr(), False, out.data_ptr(), 1, side * side, C, g.data_ptr(),
+                                          b.data_ptr(), 1e-4, True))
+        algo = side * side * C * (4 + 4 + 2)
+        print(json.dumps({"micro": "gn", "pixels": side * side, "channels": C, "ms": ms, "gbs": algo / ms / 1e6,
+                          "frac_of_hbm_peak": algo / ms / 1e6 / peaks["hbm_gbs"], "algorithmic_bytes": algo,
+                          "peak_source": peaks["source"]}))
     elif args.micro == "load":
         # Load time of the klein-4B-shaped transformer file (7.75 GB, bf16) through the engine's safetensors loader:
         # map, validate, copy, convert bf16 -> f16 and re-lay on the device. The file sits in RAM-backed storage, so
@@ -784,7 +799,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "load"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--epi", default="store", choices=["store", "qkv"], help="epilogue of --micro gemm")

@@ -192,10 +192,12 @@ __global__ void __launch_bounds__(256) gn_apply_kernel(const void *__restrict__ 
   const int cpg = C / GN_GROUPS;
   const size_t base = static_cast<size_t>(img) * pixels * C;
   const float *st = stats + img * GN_GROUPS * 2;
+  const unsigned cmask = static_cast<unsigned>(C) - 1u;  // C is a power of two (128 .. 1024)
+  const int gshift = __ffs(cpg) - 1;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const size_t e = static_cast<size_t>(i) * 8;  // element offset inside the image
-    const int c = static_cast<int>(e % C);
+    const int c = static_cast<int>(static_cast<unsigned>(e) & cmask);
     float v[8];
     if (IN16) {
       const uint4 u = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(xv) + base + e);
@@ -213,12 +215,12 @@ __global__ void __launch_bounds__(256) gn_apply_kernel(const void *__restrict__ 
     const float4 b0 = __ldg(reinterpret_cast<const float4 *>(beta + c)), b1 = __ldg(reinterpret_cast<const float4 *>(beta + c + 4));
     const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
     const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    const int ga = c / cpg, gb = (c + 4) / cpg;  // the two halves may sit in different groups when cpg == 4
+    const int ga = c >> gshift, gb = (c + 4) >> gshift;  // the two halves may sit in different groups when cpg == 4
     const float ma = __ldg(st + 2 * ga), ra = __ldg(st + 2 * ga + 1), mb = __ldg(st + 2 * gb), rb = __ldg(st + 2 * gb + 1);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float y = (v[j] - (j < 4 ? ma : mb)) * (j < 4 ? ra : rb) * gm[j] + bt[j];
-      if (swish) y = y / (1.0f + __expf(-y));
+      if (swish) y = __fdividef(y, 1.0f + __expf(-y));
       v[j] = y;
     }
     *reinterpret_cast<uint4 *>(out + base + e) =
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(256) gn_apply_kernel(const void *__restrict__ 
 
 int launch_gn_apply(const void *x, int in16, void *out16, int f16, int n_img, long long pixels, int C,
                     const float *stats, const float *gamma, const float *beta, int swish, cudaStream_t st) {
-  if (C % 128) return -1;
+  if (C < 128 || C > 1024 || (C & (C - 1))) return -1;
   const long long total8 = pixels * C / 8;
   long long nb = (total8 + 255) / 256;
   if (nb > 148 * 8) nb = 148 * 8;
