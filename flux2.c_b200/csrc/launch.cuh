@@ -19,6 +19,18 @@ inline bool pdl_enabled() {
   return on != 0;
 }
 
+// Launches made while a PdlOff object is alive on this thread do not ask for programmatic dependent launch.
+inline int &pdl_off_depth() {
+  static thread_local int depth = 0;
+  return depth;
+}
+struct PdlOff {
+  PdlOff() { ++pdl_off_depth(); }
+  ~PdlOff() { --pdl_off_depth(); }
+  PdlOff(const PdlOff &) = delete;
+  PdlOff &operator=(const PdlOff &) = delete;
+};
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                  int cluster_x, Args &&...args) {
@@ -29,7 +41,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   unsigned n = 0;
-  if (pdl_enabled()) {
+  if (pdl_enabled() && pdl_off_depth() == 0) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;

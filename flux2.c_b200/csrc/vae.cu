@@ -26,6 +26,7 @@
 #include "elementwise.cuh"
 #include "engine.cuh"
 #include "flux_cuda.h"
+#include "launch.cuh"
 #include "vae_kernels.cuh"
 
 using namespace fx;
@@ -546,6 +547,11 @@ static int vae_enqueue(flux_cuda_vae *v, const float *latent, int h, int w) {
   cudaStream_t st = v->ctx->stream;
   rc = check_cuda(cudaMemcpyAsync(v->lat, latent, static_cast<size_t>(128) * h * w * 4, cudaMemcpyDefault, st), "upload latent");
   if (rc) return rc;
+  // Plain stream-ordered launches for the VAE: with programmatic dependent launch, repeated back-to-back decodes
+  // whose GroupNorm statistics come from the convolution epilogue stopped making progress on the device in roughly
+  // one run out of three (never without it, never with the separate statistics pass); the overlap it buys here is
+  // below 1 % of a decode.
+  PdlOff no_pdl;
   Runner R{v, st, v->f16 ? 1 : 0, v->ctx->num_sms};
   v->launches = 0;
   int H = 2 * h, W = 2 * w;
@@ -604,6 +610,7 @@ static int vae_encode_enqueue(flux_cuda_vae *v, const float *image, int H, int W
   cudaStream_t st = v->ctx->stream;
   rc = check_cuda(cudaMemcpyAsync(v->img_in, image, static_cast<size_t>(3) * H * W * 4, cudaMemcpyDefault, st), "upload image");
   if (rc) return rc;
+  PdlOff no_pdl;  // see vae_enqueue
   Runner R{v, st, v->f16 ? 1 : 0, v->ctx->num_sms};
   v->launches = 0;
   R.note(launch_image_to_nhwc(v->img_in, v->a16, R.f16, H, W, st));
