@@ -317,7 +317,16 @@ def run_micro(args):
                  7 * c3(px[1], 512, 512) + c3(px[2], 512, 512) + c3(px[2], 512, 256) + 5 * c3(px[2], 256, 256) +
                  2.0 * px[2] * 512 * 256 + c3(px[3], 256, 256) + c3(px[3], 256, 128) + 5 * c3(px[3], 128, 128) +
                  2.0 * px[3] * 256 * 128 + c3(px[3], 128, 3))
+        # the encoder on an image of the same size (host f32 [3, H, W] in, host latent out)
+        rgbf = np.random.default_rng(0).uniform(-1.0, 1.0, (3, 16 * hl, 16 * hl)).astype(np.float32)
+        for _ in range(2):
+            vae.encode(rgbf)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            vae.encode(rgbf)
+        enc_ms = (time.perf_counter() - t0) * 1e3 / iters
         print(json.dumps({"micro": "vae", "image": [16 * hl, 16 * hl], "ms_device": ms, "ms_e2e": e2e,
+                          "encode_ms_e2e": enc_ms,
                           "launches": vae.last_launches(), "conv_tflops": flops / ms / 1e9,
                           "algorithmic_gflop": flops / 1e9, "image_std": float(img.std()),
                           "peak_source": peaks["source"]}))
