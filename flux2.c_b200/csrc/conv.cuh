@@ -36,15 +36,15 @@ struct alignas(64) ConvParams {
   const float *bias;  // [Cout] or null
   // Optional GroupNorm statistics of the tensor being written (modes 0-2; Cout = 32 groups of gn_cpg channels, gn_cpg
   // 4, 8 or 16): every epilogue warp stores the sums and sums of squares of its 32 rows, per group, at
-  // gn_partial[(((tile * 2 + cta) * 4 + warp) * (bn / 32) + chunk) * (64 / gn_cpg) + k], k < 32 / gn_cpg sums then
-  // as many sums of squares; conv_gn_finalize folds them. No atomics: the result does not depend on scheduling.
+  // gn_partial[(group * 2 + {0: sum, 1: sum of squares}) * slots + slot], slot = (row tile * 2 + cta) * 4 + warp,
+  // slots = tiles_m * 8; conv_gn_finalize folds them. No atomics: the result does not depend on scheduling.
   float *gn_partial;
   int gn_cpg;
   int *err;
 };
 // Floats of gn_partial a launch of `p` writes.
 inline size_t conv_gn_partial_floats(const ConvParams &p) {
-  return static_cast<size_t>(p.tiles_m) * p.tiles_n * 8 * (p.bn / 32) * (64 / (p.gn_cpg > 0 ? p.gn_cpg : 4));
+  return static_cast<size_t>(p.tiles_m) * 8 * 2 * 32;
 }
 // stats[g] = (mean, 1 / sqrt(var + eps)) of group g over `pixels` rows from the partial sums a launch of `p` wrote.
 int conv_gn_finalize(const ConvParams &p, long long pixels, float eps, float *stats, cudaStream_t stream);

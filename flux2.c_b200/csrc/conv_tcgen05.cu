@@ -62,9 +62,10 @@ __device__ __forceinline__ float warp_multi_sum(float (&a)[N], int lane) {
 }
 
 // v: this row's 32 consecutive output channels = 32 / CPG groups. Stores the warp's per-group sums and sums of
-// squares (rows outside the image count as zero) at dst[0 .. 64 / CPG).
+// squares (rows outside the image count as zero): group k of the chunk at dst[k * 2 * slots] (sum) and
+// dst[(k * 2 + 1) * slots] (sum of squares).
 template <int CPG>
-__device__ __forceinline__ void gn_chunk_sums(const float (&v)[32], bool row_ok, float *dst) {
+__device__ __forceinline__ void gn_chunk_sums(const float (&v)[32], bool row_ok, float *dst, size_t slots) {
   constexpr int NG = 32 / CPG, N = 2 * NG;
   float a[N];
 #pragma unroll
@@ -82,7 +83,11 @@ __device__ __forceinline__ void gn_chunk_sums(const float (&v)[32], bool row_ok,
   const int lane = threadIdx.x & 31;
   const float t = warp_multi_sum<N>(a, lane);
   constexpr int SH = N == 16 ? 1 : (N == 8 ? 2 : 3);  // 5 - log2(N)
-  if ((lane & ((1 << SH) - 1)) == 0) dst[lane >> SH] = t;
+  if ((lane & ((1 << SH) - 1)) == 0) {
+    const int k = lane >> SH;  // value index: k < NG sums, then NG sums of squares
+    const int g = k < NG ? k : k - NG;
+    dst[(static_cast<size_t>(g) * 2 + (k < NG ? 0 : 1)) * slots] = t;
+  }
 }
 
 // One epilogue thread = one output row (pixel): reads its TMEM lane 32 columns at a time.
@@ -156,10 +161,12 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
       }
     }
     if (P.gn_partial) {  // statistics of what was just written, for the GroupNorm that reads it next
-      float *dst = P.gn_partial + (warp_slot * (BN / 32) + c) * (64 / P.gn_cpg);
-      if (P.gn_cpg == 4) gn_chunk_sums<4>(v, row_ok, dst);
-      else if (P.gn_cpg == 8) gn_chunk_sums<8>(v, row_ok, dst);
-      else gn_chunk_sums<16>(v, row_ok, dst);
+      // group-major layout: [group][sum | sum of squares][row slot], so that the fold reads contiguous floats
+      const size_t slots = static_cast<size_t>(P.tiles_m) * 8;
+      float *dst = P.gn_partial + static_cast<size_t>(col / P.gn_cpg) * 2 * slots + warp_slot;
+      if (P.gn_cpg == 4) gn_chunk_sums<4>(v, row_ok, dst, slots);
+      else if (P.gn_cpg == 8) gn_chunk_sums<8>(v, row_ok, dst, slots);
+      else gn_chunk_sums<16>(v, row_ok, dst, slots);
     }
   }
 }
@@ -317,7 +324,7 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      conv_epilogue<BN>(P, row, row_ok, n0, taddr, (static_cast<size_t>(tile) * 2 + rank) * 4 + q);
+      conv_epilogue<BN>(P, row, row_ok, n0, taddr, (static_cast<size_t>(tile % P.tiles_m) * 2 + rank) * 4 + q);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
@@ -340,22 +347,19 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
 
 // One block per group: folds the epilogue warps' partial sums in a fixed order (per thread ascending, then a fixed
 // shared-memory tree in double precision).
-__global__ void __launch_bounds__(256) conv_gn_finalize_kernel(const float *__restrict__ partial, int tiles_m, int bn,
+__global__ void __launch_bounds__(256) conv_gn_finalize_kernel(const float *__restrict__ partial, int tiles_m,
                                                                int cpg, long long pixels, float eps,
                                                                float *__restrict__ stats) {
   __shared__ double sa[256], sb[256];
   pdl_launch_dependents();
   pdl_wait();
   const int g = blockIdx.x;
-  const int col0 = g * cpg, tn = col0 / bn, c = (col0 % bn) / 32, gi = (col0 % 32) / cpg, ng = 32 / cpg;
-  const size_t per_slot = static_cast<size_t>(bn / 32) * 2 * ng;
-  const long long entries = static_cast<long long>(tiles_m) * 8;  // (tile, cta, warp) of the tiles covering this group
+  const long long slots = static_cast<long long>(tiles_m) * 8;  // (row tile, cta, warp) of the tiles covering this group
+  const float *ps = partial + static_cast<size_t>(g) * 2 * slots, *pq = ps + slots;
   double a = 0.0, b = 0.0;
-  for (long long e = threadIdx.x; e < entries; e += 256) {
-    const size_t slot = static_cast<size_t>(tn) * tiles_m * 8 + e;
-    const float *p = partial + slot * per_slot + static_cast<size_t>(c) * 2 * ng;
-    a += static_cast<double>(__ldcg(p + gi));
-    b += static_cast<double>(__ldcg(p + ng + gi));
+  for (long long e = threadIdx.x; e < slots; e += 256) {
+    a += static_cast<double>(__ldcg(ps + e));
+    b += static_cast<double>(__ldcg(pq + e));
   }
   sa[threadIdx.x] = a;
   sb[threadIdx.x] = b;
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__(256) conv_gn_finalize_kernel(const float *__re
 int conv_gn_finalize(const ConvParams &p, long long pixels, float eps, float *stats, cudaStream_t stream) {
   if (!p.gn_partial || (p.gn_cpg != 4 && p.gn_cpg != 8 && p.gn_cpg != 16) || p.Cout != 32 * p.gn_cpg) return -5;
   return launch_kernel(conv_gn_finalize_kernel, dim3(32), dim3(256), 0, stream, 1,
-                       static_cast<const float *>(p.gn_partial), p.tiles_m, p.bn, p.gn_cpg, pixels, eps, stats) ==
+                       static_cast<const float *>(p.gn_partial), p.tiles_m, p.gn_cpg, pixels, eps, stats) ==
                  cudaSuccess
              ? 0
              : -8;
