@@ -51,3 +51,31 @@ def test_safetensors_layout(fx, tmp_path):
         assert meta["dtype"] == "BF16" and list(W[name].shape) == meta["shape"]
         got = np.frombuffer(raw[8 + hlen + b:8 + hlen + e], dtype=np.uint16).reshape(meta["shape"])
         assert np.array_equal(got, W[name])
+
+
+def test_synthetic_tokenizer_file_is_read_by_the_reference_tokenizer(fx, tmp_path):
+    """The byte-level tokenizer.json written for the prompt-driven CLI test must load in the reference's own loader and
+    tokenize a prompt into the chat template (special ids are constants of the loader, flux_qwen3_tokenizer.c:25-29)."""
+    import ctypes
+    import pytest
+    import flux2_c_b200.synth as synth
+    from oracle import ref_binding as rb
+    kind = rb.best_kind()
+    if kind is None:
+        pytest.skip("the reference build (oracle/_ref) is not present")
+    path = str(tmp_path / "tokenizer" / "tokenizer.json")
+    synth.write_tokenizer_json(path)
+    L = rb.RefLib(kind).L
+    L.qwen3_tokenizer_load.restype = ctypes.c_void_p
+    L.qwen3_tokenizer_load.argtypes = [ctypes.c_char_p]
+    L.qwen3_tokenize_chat.restype = ctypes.POINTER(ctypes.c_int)
+    L.qwen3_tokenize_chat.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    tok = L.qwen3_tokenizer_load(path.encode())
+    assert tok
+    n = ctypes.c_int()
+    ids = L.qwen3_tokenize_chat(tok, b"a cat in the rain", ctypes.byref(n), 512)
+    got = [ids[i] for i in range(n.value)]
+    assert got[0] == 151644 and 151645 in got and 151667 in got and 151668 in got
+    body = got[got.index(10) + 1:got.index(151645)]  # between "user\\n" and <|im_end|>
+    assert len(body) >= 8 and all(0 <= t < 262 for t in body)
+    assert 260 in body  # the merged pair "the" exists in the vocabulary and is used
