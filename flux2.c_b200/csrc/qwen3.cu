@@ -473,6 +473,8 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
   if (!rc) rc = check_cuda(cudaMemcpyAsync(m->mask, bits.data(), bits.size() * 4, cudaMemcpyHostToDevice, st), "upload mask");
   if (rc) return rc;
   embed_gather_kernel<<<rows, 256, 0, st>>>(m->embed, m->ids, m->hidden, h, d.vocab, f16);
+  rc = check_cuda(cudaGetLastError(), "embedding lookup");
+  if (rc) return rc;
 
   auto seg = [&](int mode, void *dst, long long ld, int col0, const float *gate) {
     EpiSeg s;
