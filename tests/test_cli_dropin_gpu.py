@@ -4,7 +4,8 @@ oracle/Makefile (`make cli`) links the reference's main.c / flux.c / flux_cli.c 
 plain reference (`flux_ref_cli`, BLAS build) and once with flux_transformer.c + flux_sample.c replaced by the seam
 (`flux_cuda_cli`, which calls libflux_cuda.so; flux_qwen3.c is replaced too and the VAE's functions are redirected).
 Both are run on the same synthetic model directory, first with external embeddings and noise, then from a text
-prompt (tokenizer -> text encoder -> denoising -> VAE -> PNG); the decoded PNGs must agree to PSNR >= 30 dB.
+prompt (tokenizer -> text encoder -> denoising -> VAE -> PNG) and from a prompt plus an input image (img2img: VAE
+encoder -> reference tokens); the decoded PNGs must agree to PSNR >= 30 dB.
 """
 import os
 import subprocess
@@ -132,6 +133,18 @@ def test_reference_cli_from_a_text_prompt(fx, model_dir, tmp_path):
                                                                                             threads=os.cpu_count()))
         psnr = _run_both(["-d", mdir, "-p", "a cat in the rain and the thin man", "-W", "128", "-H", "128", "-s", "4",
                           "-S", "42"], tmp_path, "prompt")
+        # img2img: the input image goes through the VAE encoder (GPU in one build, CPU in the other) and enters the
+        # denoising loop as reference tokens
+        rng = np.random.default_rng(3)
+        yy, xx = np.mgrid[0:128, 0:128]
+        pic = np.stack([128 + 100 * np.sin(xx / 9.0), 128 + 100 * np.cos(yy / 7.0), 40 + 1.5 * xx], axis=-1)
+        pic = np.clip(pic + rng.normal(0, 6, pic.shape), 0, 255).astype(np.uint8)
+        ppm = str(tmp_path / "input.ppm")
+        with open(ppm, "wb") as f:
+            f.write(b"P6\n128 128\n255\n" + pic.tobytes())
+        psnr_i2i = _run_both(["-d", mdir, "-p", "the man in the rain", "-i", ppm, "-W", "128", "-H", "128", "-s", "4",
+                              "-S", "7"], tmp_path, "img2img")
     finally:
         shutil.rmtree(os.path.join(mdir, "text_encoder"), ignore_errors=True)
     assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+    assert psnr_i2i >= 30.0, "img2img PSNR %.1f dB" % psnr_i2i
