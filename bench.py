@@ -32,6 +32,17 @@ WORKLOAD = "klein4b_512x512_4step_b1"
 METRIC = "images_per_sec_512x512_4step"
 
 
+_OUT = None  # the process's real stdout, once main() has pointed file descriptor 1 at stderr
+
+
+def emit(obj):
+    """Prints the result line. Libraries that write to stdout on their own (NCCL's version banner under NCCL_DEBUG=VERSION)
+    have had file descriptor 1 redirected to stderr by main(), so that stdout carries the JSON line and nothing else."""
+    out = _OUT if _OUT is not None else sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
+
 def load_package():
     name = "flux2_c_b200"
     if name in sys.modules:
@@ -137,7 +148,7 @@ def run_reference_arm(args):
     from oracle import ref_binding as rb
     kind = rb.best_kind()
     if kind is None:
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (run make -C oracle)"}))
+        emit({"impl": "reference", "unavailable": "oracle/_ref was not built (run make -C oracle)"})
         return 0
     dims = synth.Dims.klein4b()
     tmpdir = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
@@ -172,7 +183,7 @@ def run_reference_arm(args):
                              "sample": sample},
             "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0, "ms_per_dit_step": dt * 1e3}
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
@@ -219,8 +230,8 @@ def run_micro(args):
             ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
                                              tile_n=args.tile_n))
         tf = 2.0 * M * N * K / ms / 1e9
-        print(json.dumps({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "epilogue": args.epi, "ms": ms, "tflops": tf, "frac_of_burst_peak":
-                          tf / peaks["bf16"], "peak_source": peaks["source"]}))
+        emit({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "epilogue": args.epi, "ms": ms, "tflops": tf, "frac_of_burst_peak":
+                          tf / peaks["bf16"], "peak_source": peaks["source"]})
     elif args.micro == "attn":
         seq, heads = args.seq, 24
         hid = heads * 128
@@ -230,8 +241,8 @@ def run_micro(args):
         ms = timed(lambda: ctx.attention(qkv.data_ptr(), 1, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid,
                                          f16=True))
         tf = 4.0 * seq * seq * hid / ms / 1e9
-        print(json.dumps({"micro": "attn", "seq": seq, "heads": heads, "ms": ms, "tflops": tf,
-                          "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]}))
+        emit({"micro": "attn", "seq": seq, "heads": heads, "ms": ms, "tflops": tf,
+                          "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]})
     elif args.micro == "adaln":
         rows, hid = args.rows, 3072
         x = torch.randn(rows, hid, device="cuda")
@@ -241,8 +252,8 @@ def run_micro(args):
         torch.cuda.synchronize()
         ms = timed(lambda: ctx.adaln(x.data_ptr(), out.data_ptr(), rows, hid, sh.data_ptr(), sc.data_ptr()))
         gbs = rows * hid * 6.0 / ms / 1e6
-        print(json.dumps({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
-                          gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}))
+        emit({"micro": "adaln", "rows": rows, "ms": ms, "gbs": gbs, "frac_of_hbm_peak":
+                          gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]})
     elif args.micro == "gn":
         # K9: GroupNorm(32) + swish over a channels-last f32 tensor of --size x --size pixels x --shape[1] channels
         # (statistics pass + normalise pass): algorithmic bytes = 2 reads of the f32 input + 1 write of the 16-bit output
@@ -255,9 +266,9 @@ def run_micro(args):
         ms = timed(lambda: ctx.group_norm(x.data_ptr(), False, out.data_ptr(), 1, side * side, C, g.data_ptr(),
                                           b.data_ptr(), 1e-4, True))
         algo = side * side * C * (4 + 4 + 2)
-        print(json.dumps({"micro": "gn", "pixels": side * side, "channels": C, "ms": ms, "gbs": algo / ms / 1e6,
+        emit({"micro": "gn", "pixels": side * side, "channels": C, "ms": ms, "gbs": algo / ms / 1e6,
                           "frac_of_hbm_peak": algo / ms / 1e6 / peaks["hbm_gbs"], "algorithmic_bytes": algo,
-                          "peak_source": peaks["source"]}))
+                          "peak_source": peaks["source"]})
     elif args.micro == "load":
         # Load time of the klein-4B-shaped transformer file (7.75 GB, bf16) through the engine's safetensors loader:
         # map, validate, copy, convert bf16 -> f16 and re-lay on the device. The file sits in RAM-backed storage, so
@@ -278,7 +289,7 @@ def run_micro(args):
                 model.close()
         finally:
             os.remove(path)
-        print(json.dumps({"micro": "load", "file_gb": size / 1e9, "seconds": times, "best_gb_per_s": size / 1e9 / min(times)}))
+        emit({"micro": "load", "file_gb": size / 1e9, "seconds": times, "best_gb_per_s": size / 1e9 / min(times)})
     elif args.micro == "conv":
         # K8 alone: 3x3 convolution, --size x --size pixels, --shape[1] -> --shape[2] channels (shape[0] unused),
         # 16-bit channels-last in, f32 out (the upsampling convolutions of the VAE decoder).
@@ -292,9 +303,9 @@ def run_micro(args):
                                        out.data_ptr(), cout))
         tf = 2.0 * 9 * cin * cout * side * side / ms / 1e9
         algo = side * side * (cin * 2 + cout * 4) + w.numel() * 2
-        print(json.dumps({"micro": "conv", "pixels": [side, side], "cin": cin, "cout": cout, "ms": ms, "tflops": tf,
+        emit({"micro": "conv", "pixels": [side, side], "cin": cin, "cout": cout, "ms": ms, "tflops": tf,
                           "frac_of_burst_peak": tf / peaks["bf16"], "algorithmic_bytes": algo,
-                          "peak_source": peaks["source"]}))
+                          "peak_source": peaks["source"]})
     elif args.micro == "vae":
         # The VAE decoder on a --size x --size image (latent size/16): device time with the latent resident, and the
         # host-buffer call (latent in, uint8 RGB out).
@@ -325,11 +336,11 @@ def run_micro(args):
         for _ in range(iters):
             vae.encode(rgbf)
         enc_ms = (time.perf_counter() - t0) * 1e3 / iters
-        print(json.dumps({"micro": "vae", "image": [16 * hl, 16 * hl], "ms_device": ms, "ms_e2e": e2e,
+        emit({"micro": "vae", "image": [16 * hl, 16 * hl], "ms_device": ms, "ms_e2e": e2e,
                           "encode_ms_e2e": enc_ms,
                           "launches": vae.last_launches(), "conv_tflops": flops / ms / 1e9,
                           "algorithmic_gflop": flops / 1e9, "image_std": float(img.std()),
-                          "peak_source": peaks["source"]}))
+                          "peak_source": peaks["source"]})
         vae.close()
     elif args.micro == "qwen3":
         # The text encoder at the Qwen3-4B shape (only the 27 layers the output depends on are built), one prompt
@@ -354,12 +365,12 @@ def run_micro(args):
         per_layer = 2.0 * seq * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter) + 2.0 * seq * seq * qd
         flops = 27 * per_layer
         wbytes = 27 * 2.0 * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter)
-        print(json.dumps({"micro": "qwen3", "seq": seq, "prompts_per_pass": B, "layers_run": 27, "ms_per_prompt_e2e": ms,
+        emit({"micro": "qwen3", "seq": seq, "prompts_per_pass": B, "layers_run": 27, "ms_per_prompt_e2e": ms,
                           "ms_per_prompt_device": dev_ms, "model_tflops_device": flops / dev_ms / 1e9,
                           "model_tflops": flops / ms / 1e9, "weight_gb_per_pass": wbytes / 1e9,
                           "weight_stream_ms_at_hbm_peak": wbytes / peaks["hbm_gbs"] / 1e6,
                           "d2h_bytes": int(out.nbytes), "finite": bool(np.isfinite(out).all()),
-                          "peak_source": peaks["source"]}))
+                          "peak_source": peaks["source"]})
         enc.close()
     return 0
 
@@ -585,11 +596,11 @@ def run_config(args):
     if pair:
         c = dict(c, name="klein4b_base_512x512_50step_cfg4_pair_split_across_2_gpus")
     if rank == 0:
-        print(json.dumps({"config": args.config, "workload": c["name"], "value": 1e3 / ms, "unit": "images/s",
+        emit({"config": args.config, "workload": c["name"], "value": 1e3 / ms, "unit": "images/s",
                           "n_gpus": world, "ms_per_image": ms, "ms_per_dit_step": ms / steps,
                           "dit_steps_per_image": steps, "batch": batch, "tokens": N, "model_tflops": flops / ms / 1e9,
                           "attention_share_of_flops": batch * steps * attn / flops, "images_timed": args.steps,
-                          "finite": bool(torch.isfinite(out).all()), "clocks": clk, "dtype": "f16", "data": "synthetic"}))
+                          "finite": bool(torch.isfinite(out).all()), "clocks": clk, "dtype": "f16", "data": "synthetic"})
     sampler.close()
     model.close()
     if world > 1:
@@ -666,7 +677,7 @@ def run_ours(args):
         sampler.run(sched)
         ctx.sync()
         torch.cuda.profiler.stop()
-        print(json.dumps({"ncu_range": "one image", "launches": sampler.last_run()[1]}))
+        emit({"ncu_range": "one image", "launches": sampler.last_run()[1]})
         return 0
 
     # ---- device-resident timing: inputs already in HBM, K images back to back
@@ -790,7 +801,7 @@ def run_ours(args):
         def give_up():
             if rank == 0:
                 line["prompt_to_latent"] = {"error": "did not finish within %d s" % args.leg_timeout}
-                print(json.dumps(line), flush=True)
+                emit(line)
             os._exit(0)
 
         watchdog = threading.Timer(args.leg_timeout, give_up)
@@ -804,7 +815,7 @@ def run_ours(args):
             line["prompt_to_latent"] = {"error": repr(e)}
         watchdog.cancel()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     sampler.close()
     model.close()
     if world > 1:
@@ -834,6 +845,10 @@ def main():
     ap.add_argument("--dump-launches", default=None, help="write [ms, class] of every launch of one image to this file")
     ap.add_argument("--ncu-range", action="store_true", help="profile exactly one image (for ncu launch lists)")
     args = ap.parse_args()
+    global _OUT
+    sys.stdout.flush()
+    _OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         if args.steps == 10:
             args.steps, args.warmup = 2, 1
