@@ -43,6 +43,16 @@ def emit(obj):
     out.flush()
 
 
+def bench_config(world):
+    """The `config` object of the result line; both arms print the same one (the reference's CPU path computes in f32,
+    which its `dtype` says)."""
+    return {"workload": WORKLOAD, "tokens": H_LAT * W_LAT + TXT, "dit_steps_per_image": STEPS_PER_IMAGE,
+            "inputs": "image i: noise seed i, 512-token N(0,1) context of seed 10000 + i; image i on rank i % N",
+            "operands": "f16 x f16 (weights converted from bf16 at load), f32 accumulate",
+            "parallelism": "replica_dp%d" % world, "l2": "inputs larger than L2: 7.75 GB of weights per DiT step",
+            "accumulate": "f32", "residual_stream": "f32"}
+
+
 def load_package():
     name = "flux2_c_b200"
     if name in sys.modules:
@@ -137,6 +147,32 @@ def cpu_port_baseline(synth, weights, dims, z0, ctx, sched):
             "ms_per_dit_step": dt * 1e3}
 
 
+def cpu_reference_baseline(synth, weights, dims, z0, ctx, sched):
+    """The reference's own CPU build (oracle/_ref) timed on the host cores: ONE DiT forward of the 512x512 workload,
+    images/s = 1 / (4 x that). Returns None when the build did not travel with the repository."""
+    sys.path.insert(0, ROOT)
+    from oracle import ref_binding as rb
+    kind = rb.best_kind()
+    if kind is None:
+        return None
+    tmpdir = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
+    path = os.path.join(tmpdir, "flux_bench_cpu_%d.safetensors" % os.getpid())
+    try:
+        synth.write_safetensors(path, weights)
+        lib = rb.RefLib(kind)
+        tf = lib.load_transformer(path)
+    finally:
+        if os.path.exists(path):
+            os.remove(path)
+    t0 = time.perf_counter()
+    tf.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
+    dt = time.perf_counter() - t0
+    tf.close()
+    return {"value": 1.0 / (STEPS_PER_IMAGE * dt), "unit": "images/s", "cores": lib.blas_threads, "kind": "reference",
+            "sample": "1 of the 4 DiT forwards of one 512x512 image (%.1f s), x4; the reference's %s build, %d BLAS "
+                      "threads" % (dt, kind, lib.blas_threads), "ms_per_dit_step": dt * 1e3}
+
+
 def run_reference_arm(args):
     """--impl reference: the reference's own CPU code (oracle/_ref) on the same workload, host cores only."""
     rank = int(os.environ.get("RANK", "0"))
@@ -165,7 +201,9 @@ def run_reference_arm(args):
     z0 = lib.init_noise(dims.latent_ch, H_LAT, W_LAT, 42)
     ctx = synth.make_context(1234, TXT, dims.text_dim)
     sched = lib.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
-    # one "step" of this arm = a bounded sample of one image: its first DiT forward, scaled by the 4 forwards
+    # one "step" of this arm = a bounded sample of one image: ONE of its four DiT forwards (the reference's CPU path
+    # needs ~20 s per forward on 16 cores, so a whole image per step would not end within minutes). images/s =
+    # 1 / (forwards_per_image x the mean forward time); ms_per_step is the time of what a step really ran.
     for _ in range(args.warmup):
         tf.forward(z0, H_LAT, W_LAT, ctx, float(sched[0]))
     t0 = time.perf_counter()
@@ -174,11 +212,13 @@ def run_reference_arm(args):
     dt = (time.perf_counter() - t0) / args.steps
     value = 1.0 / (STEPS_PER_IMAGE * dt)
     threads = lib.blas_threads
-    sample = "per step: 1 of the 4 DiT forwards of one 512x512 image, x4 (%s build, %d BLAS threads)" % (kind, threads)
+    sample = ("per step: 1 of the 4 DiT forwards of one 512x512 image; images/s = 1 / (4 x ms_per_step) "
+              "(%s build, %d BLAS threads)" % (kind, threads))
     line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": STEPS_PER_IMAGE * dt * 1e3, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": WORKLOAD, "tokens": H_LAT * W_LAT + TXT, "dit_steps_per_image": STEPS_PER_IMAGE},
+            "config": bench_config(args.gpus), "forwards_per_step": 1, "forwards_per_image": STEPS_PER_IMAGE,
+            "ms_per_image": STEPS_PER_IMAGE * dt * 1e3,
             "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": "reference",
                              "sample": sample},
             "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -376,14 +416,22 @@ def run_micro(args):
 
 
 # ---------------------------------------------------------------------------------------------- text encoder leg
-def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream, barrier, max_over_ranks, rank, world,
-                          dist):
-    """Images/s when each image starts from 512 token ids: text-encoder forward (Qwen3-4B shape; the 27 layers the
-    output depends on - later layers are neither generated nor run, as in the reference's device path), embeddings
-    handed to the sampler on the device, 4 DiT steps, latent read back. Host -> device per image: ids + noise."""
+SWEEP_IMAGES = 64
+
+
+def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, stream, barrier, all_ranks, rank, world, dist):
+    """The throughput-sweep configuration: SWEEP_IMAGES independent images split over the ranks (image i on rank
+    i % world), each from its own 512 token ids (seed 20000 + i) and its own noise (seed i). Per image: text-encoder
+    forward (Qwen3-4B shape; the 27 layers the output depends on - later layers are neither generated nor run, as in
+    the reference's device path), embeddings handed to the sampler on the device, 4 DiT steps, latent read back.
+    Host -> device per image: ids + noise. A fixed number of images: strong scaling; the job's time is the slowest
+    rank's."""
+    import importlib
     import numpy as np
     import torch
+    dp = importlib.import_module("flux2_c_b200.dp")
     qd = synth.QwenDims(layers=27)
+    dims = synth.Dims.klein4b()
     PB = max(1, args.prompt_batch)  # prompts per encoder pass: the weights are read once for the group
 
     def all_ok(ok):
@@ -396,6 +444,7 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
         return bool(t.item() > 0.5)
 
     enc, err = None, None
+    t_setup = time.perf_counter()
     if world == 1:
         enc = fx.TextEncoder.from_tensors(ctx, qd, synth.make_qwen_weights(qd, seed=0, threads=os.cpu_count()),
                                           max_seq=TXT * PB)
@@ -421,43 +470,57 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
             if enc is not None:
                 enc.close()
             raise RuntimeError("text encoder set-up failed on some rank: %r" % (err,))
-    rng = np.random.default_rng(1000 + rank)
-    ids = rng.integers(0, qd.vocab, (max(args.steps, PB), TXT)).astype(np.int32)
+    setup_s = time.perf_counter() - t_setup
+    mine = dp.images_of_rank(SWEEP_IMAGES, rank, world)
+    n = len(mine)
+    ids = np.stack([np.random.default_rng(20000 + i).integers(0, qd.vocab, TXT) for i in mine]).astype(np.int32)
+    n_lat = dims.latent_ch * H_LAT * W_LAT
+    z = torch.stack([torch.from_numpy(fx.init_noise(dims.latent_ch, H_LAT, W_LAT, i)).reshape(-1)
+                     for i in mine]).pin_memory()
+    out = torch.zeros(n, n_lat, dtype=torch.float32).pin_memory()
     ctx_bytes = TXT * 3 * qd.hidden * 4
 
-    def run_images(n, per_image):
-        """n images: prompts are encoded PB at a time; the embeddings of prompt j of a group sit at dev + j * ctx_bytes
-        until the next group is encoded, which the stream orders after the uploads that read them."""
+    def run_images(count, per_image):
+        """The first `count` of this rank's images: prompts are encoded PB at a time; the embeddings of prompt j of a
+        group sit at dev + j * ctx_bytes until the next group is encoded, which the stream orders after the uploads
+        that read them."""
         done = 0
-        while done < n:
-            g = min(PB, n - done)
+        while done < count:
+            g = min(PB, count - done)
             dev = enc.forward_batch(ids[done:done + g], None, device=True)
             for j in range(g):
-                sampler.upload(z0.data_ptr(), dev + j * ctx_bytes)
+                sampler.upload(z[done + j].data_ptr(), dev + j * ctx_bytes)
                 sampler.run(sched)
-                per_image()
+                per_image(done + j)
             done += g
 
-    to_latent = lambda: sampler.download(out.data_ptr())  # waits for the image
-    run_images(max(3, PB), to_latent)
+    def timed(count, per_image):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+        run_images(count, per_image)
+        with torch.cuda.stream(stream):
+            e1.record()
+        barrier()
+        return all_ranks(e0.elapsed_time(e1))
+
+    to_latent = lambda j: sampler.download(out[j].data_ptr())  # waits for the image
+    run_images(min(n, max(3, PB)), to_latent)
+    rank_ms = timed(n, to_latent)
+    ms = max(rank_ms)
+    # the encoder alone, device time per prompt
+    reps = max(2, min(10, args.steps))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record()
-    run_images(args.steps, to_latent)
+    for i in range(reps):
+        enc.forward_batch(ids[:min(PB, n)], None, device=True)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    # the encoder alone, device time per prompt
-    with torch.cuda.stream(stream):
-        e0.record()
-    for i in range(args.steps):
-        enc.forward_batch(ids[:PB], None, device=True)
-    with torch.cuda.stream(stream):
-        e1.record()
-    barrier()
-    enc_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps / PB
+    enc_ms = max(all_ranks(e0.elapsed_time(e1))) / reps / min(PB, n)
     finite = bool(torch.isfinite(out).all())
 
     # the same plus the VAE decoder: the latent goes from the sampler to the decoder on the device, the 512x512 RGB
@@ -465,37 +528,37 @@ def prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
     vae = fx.Vae.from_tensors(ctx, synth.make_vae_weights(seed=5, rich=True))
     rgb = torch.zeros(16 * H_LAT * 16 * W_LAT * 3, dtype=torch.uint8).pin_memory()
 
-    to_image = lambda: vae.decode_ptr(sampler.latent_device(), H_LAT, W_LAT, rgb.data_ptr())  # waits for the image
-    run_images(max(3, PB), to_image)
+    to_image = lambda j: vae.decode_ptr(sampler.latent_device(), H_LAT, W_LAT, rgb.data_ptr())  # waits for the image
+    run_images(min(n, max(3, PB)), to_image)
+    img_rank_ms = timed(n, to_image)
+    img_ms = max(img_rank_ms)
     barrier()
     with torch.cuda.stream(stream):
         e0.record()
-    run_images(args.steps, to_image)
-    with torch.cuda.stream(stream):
-        e1.record()
-    barrier()
-    img_ms = max_over_ranks(e0.elapsed_time(e1))
-    with torch.cuda.stream(stream):
-        e0.record()
-    for i in range(args.steps):
+    for i in range(reps):
         vae.decode_device(sampler.latent_device(), H_LAT, W_LAT)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
-    vae_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    vae_ms = max(all_ranks(e0.elapsed_time(e1))) / reps
     img_std = float(rgb.float().std())
     vae.close()
     enc.close()
-    return {"workload": "per image: %d token ids -> Qwen3-4B-shaped encoder (27 of 36 layers: the ones the output "
-            "depends on; %d prompts per encoder pass) -> 4 DiT steps at 512x512 -> latent on the host" % (TXT, PB), "value": args.steps * world / (ms * 1e-3),
-            "unit": "images/s", "ms_per_image": ms / args.steps, "text_encoder_ms_per_prompt": enc_ms,
-            "prompts_per_encoder_pass": PB,
-            "h2d_bytes_per_image": int(TXT * 4 + z0.numel() * 4), "d2h_bytes_per_image": int(out.numel() * 4),
-            "finite": finite,
+    return {"workload": "%d images over %d GPU(s), image i on rank i %% N; per image: %d token ids (seed 20000 + i) -> "
+            "Qwen3-4B-shaped encoder (27 of 36 layers: the ones the output depends on; %d prompts per encoder pass) -> "
+            "4 DiT steps at 512x512 from noise seed i -> latent on the host" % (SWEEP_IMAGES, world, TXT, PB),
+            "images_total": SWEEP_IMAGES, "scaling": "strong", "value": SWEEP_IMAGES / (ms * 1e-3),
+            "unit": "images/s", "ms_per_image": ms / max(1, -(-SWEEP_IMAGES // world)),
+            "per_rank_ms": {"min": min(rank_ms), "max": max(rank_ms)},
+            "text_encoder_ms_per_prompt": enc_ms, "prompts_per_encoder_pass": PB,
+            "h2d_bytes_per_image": int(TXT * 4 + n_lat * 4), "d2h_bytes_per_image": int(n_lat * 4),
+            "finite": finite, "encoder_setup_s": setup_s,
             "prompt_to_image": {"workload": "the same, then the VAE decoder on the device; a 512x512 uint8 RGB image "
-                                "returns to the host", "value": args.steps * world / (img_ms * 1e-3), "unit": "images/s",
-                                "ms_per_image": img_ms / args.steps, "vae_decode_ms": vae_ms,
-                                "d2h_bytes_per_image": int(rgb.numel()), "image_std": img_std}}
+                                "returns to the host", "value": SWEEP_IMAGES / (img_ms * 1e-3), "unit": "images/s",
+                                "ms_per_image": img_ms / max(1, -(-SWEEP_IMAGES // world)),
+                                "per_rank_ms": {"min": min(img_rank_ms), "max": max(img_rank_ms)},
+                                "vae_decode_ms": vae_ms, "d2h_bytes_per_image": int(rgb.numel()),
+                                "image_std": img_std}}
 
 
 # ---------------------------------------------------------------------------------------------- other configurations
@@ -631,9 +694,12 @@ def run_ours(args):
     ctx = fx.Context(local)
 
     # ---- model: rank 0 generates the seeded weights once; other ranks read the same file through the loader
+    # (all of this is set-up, outside every timed region; its duration is reported as setup_s)
+    t_setup = time.perf_counter()
     W = None
     if world == 1:
         W = synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count())
+        t_weights = time.perf_counter() - t_setup
         model = fx.Model.from_tensors(ctx, dims, W)
     else:
         shm = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
@@ -641,19 +707,29 @@ def run_ours(args):
         if rank == 0:
             synth.write_safetensors(path, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
         dist.barrier()
+        t_weights = time.perf_counter() - t_setup
         model = fx.Model.load_safetensors(ctx, path)
         dist.barrier()
         if rank == 0:
             os.remove(path)
+    t_load = time.perf_counter() - t_setup - t_weights
 
-    # ---- inputs: every rank denoises its own image (seed 42 + rank), pinned host buffers
+    # ---- inputs: `steps` images per rank (weak scaling). Image i of the job has noise seed i and the context of
+    # seed 10000 + i and runs on rank i % world. Pinned host copies for the end-to-end region, device copies for the
+    # device-resident one.
+    dp = importlib.import_module("flux2_c_b200.dp")
+    mine = dp.images_of_rank(args.steps * world, rank, world)
     n_lat = dims.latent_ch * H_LAT * W_LAT
-    z0 = torch.from_numpy(fx.init_noise(dims.latent_ch, H_LAT, W_LAT, 42 + rank)).pin_memory()
-    cemb = torch.from_numpy(synth.make_context(1234 + rank, TXT, dims.text_dim)).pin_memory()
-    out = torch.zeros(n_lat, dtype=torch.float32).pin_memory()
+    z_host = torch.stack([torch.from_numpy(fx.init_noise(dims.latent_ch, H_LAT, W_LAT, i)).reshape(-1)
+                          for i in mine]).pin_memory()
+    c_host = torch.stack([torch.from_numpy(synth.make_context(10000 + i, TXT, dims.text_dim)).reshape(-1)
+                          for i in mine]).pin_memory()
+    z_dev, c_dev = z_host.cuda(), c_host.cuda()
+    out = torch.zeros(len(mine), n_lat, dtype=torch.float32).pin_memory()
     sched = fx.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
     sampler = fx.Sampler(model, H_LAT, W_LAT, TXT, batch=1, max_steps=STEPS_PER_IMAGE)
     stream = torch.cuda.ExternalStream(ctx.stream)
+    torch.cuda.synchronize()
 
     def barrier():
         if world > 1:
@@ -668,21 +744,38 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    sampler.upload(z0.data_ptr(), cemb.data_ptr())
+    def all_ranks(ms):
+        if world == 1:
+            return [ms]
+        t = torch.tensor([ms], device="cuda")
+        got = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(got, t)
+        return [float(x.item()) for x in got]
+
+    def resident(j):  # inputs of image j are already in HBM: a device-to-device copy into the sampler's buffers
+        sampler.upload(z_dev[j].data_ptr(), c_dev[j].data_ptr())
+        sampler.run(sched)
+
+    def end_to_end(j):  # pinned host inputs in, latent out on the host; download waits for the image
+        sampler.upload(z_host[j].data_ptr(), c_host[j].data_ptr())
+        sampler.run(sched)
+        sampler.download(out[j].data_ptr())
+
     if args.ncu_range:
         # one warm image, then exactly one image between cudaProfilerStart/Stop (ncu --profile-from-start off)
-        sampler.run(sched)
+        resident(0)
         ctx.sync()
         torch.cuda.profiler.start()
-        sampler.run(sched)
+        resident(0)
         ctx.sync()
         torch.cuda.profiler.stop()
         emit({"ncu_range": "one image", "launches": sampler.last_run()[1]})
         return 0
 
     # ---- device-resident timing: inputs already in HBM, K images back to back
-    for _ in range(max(3, args.warmup)):
-        sampler.run(sched)
+    K = len(mine)
+    for w_i in range(max(3, args.warmup)):
+        resident(w_i % K)
     barrier()
     clocks = ClockSampler(local)
     if rank == 0:
@@ -690,34 +783,35 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record()
-        for _ in range(args.steps):
-            sampler.run(sched)
+        for j in range(K):
+            resident(j)
         e1.record()
     barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    launches = sampler.last_run()[1] * args.steps
-    sampler.download(out.data_ptr())
-    finite = bool(torch.isfinite(out).all())
+    my_ms = e0.elapsed_time(e1)
+    rank_ms = all_ranks(my_ms)
+    ms_total = max(rank_ms)
+    launches = sampler.last_run()[1] * K
 
     # ---- end to end through the host-buffer API: H2D of the inputs and D2H of the latent inside the region
-    for _ in range(2):
-        sampler.upload(z0.data_ptr(), cemb.data_ptr())
-        sampler.run(sched)
-        sampler.download(out.data_ptr())
+    for j in range(2):
+        end_to_end(j % K)
     barrier()
     t0 = time.perf_counter()
     with torch.cuda.stream(stream):
         e0.record()
-    for _ in range(args.steps):
-        sampler.upload(z0.data_ptr(), cemb.data_ptr())
-        sampler.run(sched)
-        sampler.download(out.data_ptr())  # waits for the image
+    for j in range(K):
+        end_to_end(j)
     with torch.cuda.stream(stream):
         e1.record()
     barrier()
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), 0.0))
     e2e_wall_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
     clk = clocks.stop() if rank == 0 else None
+    finite = bool(torch.isfinite(out).all()) and float(out.std()) > 0.0
+    distinct = K < 2 or not torch.equal(out[0], out[1])  # different seeds must give different images
+    saturated = ctx.saturated_stores()
+    z0, cemb = z_host[0], c_host[0]
+    sampler.upload(z_dev[0].data_ptr(), c_dev[0].data_ptr())
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): per-class CUDA-event times of the same loop
     fl = step_flops(H_LAT * W_LAT, TXT, dims)
@@ -764,9 +858,10 @@ def run_ours(args):
                     "[%d x %d] . [%d x %d]" % (n_tok, dims.hidden, dims.hidden, 3 * dims.hidden + 2 * dims.mlp),
                     "achieved": a1, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                     "frac": a1 / peaks["bf16_sustained"],
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this very shape
-                    # (profiles/gemm2_bf16_tn_1536x27648x3072.md); algorithmic bytes 264.2 MB
-                    "traffic": 242.3e6, "launches": len(lin1), "avg_launch_ms": ms1,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this very shape under ncu: a
+                    # figure quoted from the committed capture, not measured by this run; algorithmic bytes 264.2 MB
+                    "traffic": 242.3e6, "traffic_source": "profiles/gemm2_bf16_tn_1536x27648x3072.md (ncu, one launch)",
+                    "launches": len(lin1), "avg_launch_ms": ms1,
                     "flops_per_launch": f1, "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                     "frac_of_burst_peak": a1 / peaks["bf16"]}
     images = args.steps * world
@@ -775,22 +870,26 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens": H_LAT * W_LAT + TXT, "dit_steps_per_image": STEPS_PER_IMAGE,
-                   "operands": "f16 x f16 (weights converted from bf16 at load), f32 accumulate", "parallelism": "replica_dp%d" % world, "l2": "inputs larger than L2: 7.75 GB of weights per DiT step",
-                   "accumulate": "f32", "residual_stream": "f32"},
+        "config": bench_config(world),
         "ms_per_dit_step": ms_total / args.steps / STEPS_PER_IMAGE,
         "model_tflops": (STEPS_PER_IMAGE * (fl["gemm"] + fl["attn"]) + fl["ctx_embed_once"]) * args.steps /
                         (ms_total * 1e-3) / 1e12,
         "e2e": {"value": images / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(z0.numel() * 4 +
-                cemb.numel() * 4), "d2h_bytes_per_step": int(out.numel() * 4), "wall_ms_per_step":
+                cemb.numel() * 4), "d2h_bytes_per_step": int(n_lat * 4), "wall_ms_per_step":
                 e2e_wall_ms / args.steps},
-        "gpu_launches": int(launches), "finite": finite, "clocks": clk, "roofline": roof or roof_all,
-        "roofline_all_gemm": roof_all, "prompt_to_latent": None,
+        "gpu_launches": int(launches), "finite": finite, "distinct_images": distinct,
+        "saturated_f16_stores": int(saturated), "clocks": clk, "roofline": roof or roof_all,
+        "roofline_all_gemm": roof_all,
+        "per_rank_ms_per_step": {"min": min(rank_ms) / args.steps, "max": max(rank_ms) / args.steps},
+        "setup_s": {"weights_generated_and_written": t_weights, "model_load": t_load},
+        "prompt_to_latent": None, "leg_timeout": False,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            line["cpu_baseline"] = cpu_port_baseline(synth, W, dims, z0.numpy().reshape(dims.latent_ch, H_LAT, W_LAT),
-                                                     cemb.numpy(), sched)
+            zc = z0.numpy().reshape(dims.latent_ch, H_LAT, W_LAT)
+            cc = cemb.numpy().reshape(TXT, dims.text_dim)
+            base = cpu_reference_baseline(synth, W, dims, zc, cc, sched)
+            line["cpu_baseline"] = base if base is not None else cpu_port_baseline(synth, W, dims, zc, cc, sched)
         except Exception as e:  # the baseline must never take the GPU numbers down with it
             line["cpu_baseline"] = {"error": repr(e)}
 
@@ -799,18 +898,20 @@ def run_ours(args):
     # extra leg: if it raises, or does not come back within its time limit, the line above is printed without it.
     if not args.no_text_encoder:
         def give_up():
+            # the headline numbers above were measured before this leg started: print them, say that the leg did not
+            # come back, and end the process with a failure status so that the stall shows in the run's record
             if rank == 0:
                 line["prompt_to_latent"] = {"error": "did not finish within %d s" % args.leg_timeout}
+                line["leg_timeout"] = True
                 emit(line)
-            os._exit(0)
+            os._exit(3)
 
         watchdog = threading.Timer(args.leg_timeout, give_up)
         watchdog.daemon = True
         watchdog.start()
         try:
-            line["prompt_to_latent"] = prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, z0, out, stream,
-                                                             barrier, max_over_ranks, rank, world,
-                                                             dist if world > 1 else None)
+            line["prompt_to_latent"] = prompt_to_latent_pass(args, fx, synth, ctx, sampler, sched, stream, barrier,
+                                                             all_ranks, rank, world, dist if world > 1 else None)
         except Exception as e:
             line["prompt_to_latent"] = {"error": repr(e)}
         watchdog.cancel()

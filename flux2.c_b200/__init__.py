@@ -171,8 +171,14 @@ def _declare(L):
     L.flux_cuda_sampler_set_profiling.argtypes = [c_void_p, c_int]
     L.flux_cuda_sampler_profile.restype = c_int
     L.flux_cuda_sampler_profile.argtypes = [c_void_p, fp, ctypes.POINTER(c_ll)]
+    L.flux_cuda_sampler_profile_groups.restype = c_int
+    L.flux_cuda_sampler_profile_groups.argtypes = [c_void_p, fp]
     L.flux_cuda_sampler_profile_launches.restype = c_int
     L.flux_cuda_sampler_profile_launches.argtypes = [c_void_p, fp, ctypes.POINTER(c_int), c_int, ctypes.POINTER(c_int)]
+    L.flux_cuda_ctx_saturated_stores.restype = c_int
+    L.flux_cuda_ctx_saturated_stores.argtypes = [c_void_p, ctypes.POINTER(c_ll), c_int]
+    L.flux_cuda_selftest_wait_timeout.restype = c_int
+    L.flux_cuda_selftest_wait_timeout.argtypes = [c_void_p, c_ll, c_void_p]
     L.flux_cuda_official_schedule.restype = None
     L.flux_cuda_official_schedule.argtypes = [c_int, c_int, fp]
     L.flux_cuda_linear_schedule.restype = None
@@ -225,6 +231,15 @@ class Context:
 
     def sync(self):
         check(lib().flux_cuda_ctx_sync(self.handle))
+
+    def saturated_stores(self, reset=False):
+        """f16 stores that hit the +-65504 clamp, as seen by the synchronising calls so far."""
+        n = ctypes.c_longlong()
+        check(lib().flux_cuda_ctx_saturated_stores(self.handle, ctypes.byref(n), int(reset)))
+        return n.value
+
+    def selftest_wait_timeout(self, limit_cycles, waited_ptr=None):
+        check(lib().flux_cuda_selftest_wait_timeout(self.handle, limit_cycles, waited_ptr))
 
     def set_half_format(self, name):
         """'f16' (default) or 'bf16': storage format of models created afterwards."""
@@ -636,6 +651,12 @@ class Sampler:
         n = (ctypes.c_longlong * 5)()
         check(lib().flux_cuda_sampler_profile(self.handle, ms, n))
         return {k: {"ms": ms[i], "n": n[i]} for i, k in enumerate(("gemm", "attn", "adaln", "qknorm", "other"))}
+
+    def profile_groups(self):
+        """Device ms of the last profiled run per part of the forward (the reference's timing globals' split)."""
+        ms = (ctypes.c_float * 4)()
+        check(lib().flux_cuda_sampler_profile_groups(self.handle, ms))
+        return dict(zip(("edges", "double_blocks", "single_blocks", "final_layer"), [ms[i] for i in range(4)]))
 
     def profile_launches(self, capacity=8192):
         """[(ms, class index)] of the last profiled run, in launch order."""

@@ -15,6 +15,7 @@
 #include "engine.cuh"
 #include "conv.cuh"
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "vae_kernels.cuh"
 
 namespace fx {
@@ -32,13 +33,19 @@ int check_cuda(cudaError_t e, const char *what) {
   return FLUX_CUDA_ERR_CUDA;
 }
 int ctx_sync_check(flux_cuda_ctx *ctx) {
-  int rc = check_cuda(cudaMemcpyAsync(ctx->err_host, ctx->err_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream),
+  // word 0: first kernel error code; word 1: f16 stores that saturated since the last read
+  int rc = check_cuda(cudaMemcpyAsync(ctx->err_host, ctx->err_dev, 2 * sizeof(int), cudaMemcpyDeviceToHost,
+                                      ctx->stream),
                       "read kernel error word");
   if (rc) return rc;
   rc = check_cuda(cudaStreamSynchronize(ctx->stream), "stream synchronize");
   if (rc) return rc;
-  if (*ctx->err_host != 0) {
-    const int code = *ctx->err_host;
+  if (ctx->err_host[1] != 0) {
+    ctx->saturated += static_cast<unsigned int>(ctx->err_host[1]);
+    cudaMemsetAsync(ctx->err_dev + 1, 0, sizeof(int), ctx->stream);
+  }
+  if (ctx->err_host[0] != 0) {
+    const int code = ctx->err_host[0];
     cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), ctx->stream);
     set_error("a kernel gave up on a bounded wait (code %d)", code);
     return FLUX_CUDA_ERR_KERNEL;
@@ -78,16 +85,16 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
   c->device = device;
   c->num_sms = prop.multiProcessorCount;
   if ((rc = check_cuda(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "cudaStreamCreate")) ||
-      (rc = check_cuda(cudaMalloc(&c->err_dev, sizeof(int)), "cudaMalloc")) ||
-      (rc = check_cuda(cudaMallocHost(&c->err_host, sizeof(int)), "cudaMallocHost")) ||
-      (rc = check_cuda(cudaMemset(c->err_dev, 0, sizeof(int)), "cudaMemset"))) {
+      (rc = check_cuda(cudaMalloc(&c->err_dev, 2 * sizeof(int)), "cudaMalloc")) ||
+      (rc = check_cuda(cudaMallocHost(&c->err_host, 2 * sizeof(int)), "cudaMallocHost")) ||
+      (rc = check_cuda(cudaMemset(c->err_dev, 0, 2 * sizeof(int)), "cudaMemset"))) {
     flux_cuda_ctx_destroy(c);
     return rc;
   }
   if (const char *e = getenv("FLUX_CUDA_GEMM_PAIR")) c->gemm_pair = atoi(e) != 0;
   if (const char *e = getenv("FLUX_CUDA_BF16")) c->f16 = atoi(e) == 0;
-  if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 1 ? 1 : 2;
-  if (gemm_init() != 0 || gemm2_init() != 0 || attn_init() != 0 || attn2_init() != 0 || elementwise_init() != 0 ||
+  if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 2 ? 2 : 3;
+  if (gemm_init() != 0 || gemm2_init() != 0 || attn2_init() != 0 || attn3_init() != 0 || elementwise_init() != 0 ||
       conv_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
     flux_cuda_ctx_destroy(c);
@@ -116,6 +123,13 @@ int flux_cuda_ctx_sync(flux_cuda_ctx *ctx) {
 }
 
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int flux_cuda_ctx_saturated_stores(flux_cuda_ctx *ctx, long long *count, int reset) {
+  if (!ctx || !count) return FLUX_CUDA_ERR_ARG;
+  *count = ctx->saturated;
+  if (reset) ctx->saturated = 0;
+  return FLUX_CUDA_OK;
+}
 
 int flux_cuda_ctx_set_half_format(flux_cuda_ctx *ctx, int dtype) {
   if (!ctx || (dtype != FLUX_CUDA_F16 && dtype != FLUX_CUDA_BF16)) return FLUX_CUDA_ERR_ARG;
@@ -229,14 +243,13 @@ int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq,
                         int v_col, int heads, void *out, long long out_ld, int out_col, int f16) {
   if (!ctx || !qkv || !out) return FLUX_CUDA_ERR_ARG;
   AttnParams A;
-  const bool v2 = ctx->attn_version == 2;
-  int rc = (v2 ? attn2_make_params : attn_make_params)(&A, qkv, batch, seq, ld, q_col, k_col, v_col, out, out_ld,
-                                                        out_col, heads, f16, ctx->err_dev);
+  int rc = attn2_make_params(&A, qkv, batch, seq, ld, q_col, k_col, v_col, out, out_ld, out_col, heads, f16,
+                             ctx->err_dev);
   if (rc) {
     set_error("attention: unsupported shape/alignment (rc %d)", rc);
     return FLUX_CUDA_ERR_ARG;
   }
-  rc = v2 ? attn2_launch(&A, ctx->stream) : attn_launch(&A, ctx->stream);
+  rc = attn_launch_version(ctx->attn_version, &A, ctx->stream);
   if (rc) {
     set_error("attention: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return FLUX_CUDA_ERR_CUDA;
@@ -247,7 +260,8 @@ int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq,
 int flux_cuda_adaln(flux_cuda_ctx *ctx, const float *x, void *out, int rows, int hidden, const float *shift,
                     const float *scale, int f16) {
   if (!ctx || !x || !out || !shift || !scale) return FLUX_CUDA_ERR_ARG;
-  int rc = launch_adaln(x, out, 0, rows, hidden, rows > 0 ? rows : 1, 0, f16, shift, scale, shift, scale, ctx->stream);
+  int rc = launch_adaln(x, out, 0, rows, hidden, rows > 0 ? rows : 1, 0, f16, shift, scale, shift, scale, ctx->stream,
+                        ctx->err_dev + 1);
   if (rc) {
     set_error("adaln: unsupported hidden size %d or launch failure", hidden);
     return rc == -1 ? FLUX_CUDA_ERR_ARG : FLUX_CUDA_ERR_CUDA;
@@ -267,6 +281,7 @@ static int conv_finish(flux_cuda_ctx *ctx, ConvParams &P, const float *bias, int
   P.bias = bias;
   P.out_f16 = P.x_f16 = f16 ? 1 : 0;
   P.err = ctx->err_dev;
+  PdlOff plain_launches;  // plain stream order, as the VAE itself launches this kernel
   if (conv_launch(&P, ctx->num_sms, ctx->stream) != 0) {
     set_error("%s: launch failed: %s", what, cudaGetErrorString(cudaGetLastError()));
     return FLUX_CUDA_ERR_CUDA;
@@ -315,8 +330,17 @@ int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, cons
 
 int flux_cuda_group_norm(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels, int C,
                          const float *gamma, const float *beta, float eps, int swish, int f16) {
-  if (!ctx || !x || !out16 || !gamma || !beta || n_img < 1 || n_img > 8) return FLUX_CUDA_ERR_ARG;
+  if (!ctx || !x || !out16 || !gamma || !beta || n_img < 1 || n_img > 8 || pixels < 1) {
+    set_error("group_norm: bad argument (1 <= n_img <= 8)");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out16) | reinterpret_cast<uintptr_t>(gamma) |
+       reinterpret_cast<uintptr_t>(beta)) & 15) {
+    set_error("group_norm: x, out16, gamma and beta must be 16-byte aligned");
+    return FLUX_CUDA_ERR_ARG;
+  }
   cudaSetDevice(ctx->device);
+  PdlOff plain_launches;  // plain stream order, as the VAE itself launches these kernels
   const size_t part = static_cast<size_t>(8) * GN_MAX_BLOCKS * 64, stats = 8 * GN_GROUPS * 2;
   if (!ctx->gn_scratch) {
     int rc = check_cuda(cudaMalloc(&ctx->gn_scratch, (part + stats + 8) * 4), "cudaMalloc");
@@ -484,6 +508,10 @@ int flux_cuda_sampler_set_profiling(flux_cuda_sampler *s, int on) {
 }
 int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class) {
   return sampler_profile(s, ms_by_class, launches_by_class);
+}
+
+int flux_cuda_sampler_profile_groups(flux_cuda_sampler *s, float *ms_by_group) {
+  return sampler_profile_groups(s, ms_by_group);
 }
 
 int flux_cuda_sampler_profile_launches(flux_cuda_sampler *s, float *ms, int *kernel_class, int capacity, int *count) {

@@ -9,10 +9,11 @@ struct flux_cuda_ctx {
   int device = 0;
   int num_sms = 0;
   cudaStream_t stream = nullptr;  // owned
-  int *err_dev = nullptr;         // device word, 0 = no kernel reported a failed wait
-  int *err_host = nullptr;        // pinned mirror
+  int *err_dev = nullptr;         // two device words: [0] first kernel error (0 = none), [1] saturated f16 stores
+  int *err_host = nullptr;        // pinned mirror of both
+  long long saturated = 0;        // saturated f16 stores seen by the synchronisations so far
   bool f16 = true;                // 16-bit tensors (weights and activations) are f16; false: bf16
-  int attn_version = 2;           // 1: attention.cu, 2: attention2.cu
+  int attn_version = 3;           // 3: attention3.cu (default), 2: attention2.cu (FLUX_CUDA_ATTN=2)
   bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
   float *gn_scratch = nullptr;    // lazily allocated scratch of the kernel-level GroupNorm entry point
 };

@@ -96,6 +96,7 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
                                               size_t warp_slot) {
   uint32_t r[32];
   const bool f16 = P.out_f16 != 0;
+  float mx = 0.f;
   if (P.mode == CONV_STORE_RGB8) {
     tc_ld_32x32(taddr, r);
     tc_wait_ld();
@@ -138,10 +139,10 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 o;
-          o.x = pack_16x2(v[8 * j + 0], v[8 * j + 1], f16);
-          o.y = pack_16x2(v[8 * j + 2], v[8 * j + 3], f16);
-          o.z = pack_16x2(v[8 * j + 4], v[8 * j + 5], f16);
-          o.w = pack_16x2(v[8 * j + 6], v[8 * j + 7], f16);
+          o.x = pack_16x2_t(v[8 * j + 0], v[8 * j + 1], f16, mx);
+          o.y = pack_16x2_t(v[8 * j + 2], v[8 * j + 3], f16, mx);
+          o.z = pack_16x2_t(v[8 * j + 4], v[8 * j + 5], f16, mx);
+          o.w = pack_16x2_t(v[8 * j + 6], v[8 * j + 7], f16, mx);
           d4[j] = o;
         }
       }
@@ -169,6 +170,7 @@ __device__ __forceinline__ void conv_epilogue(const ConvParams &P, size_t row, b
       else gn_chunk_sums<16>(v, row_ok, dst, slots);
     }
   }
+  sat_report(P.err + 1, f16 && P.mode == CONV_STORE_16, mx);
 }
 
 template <int BN>

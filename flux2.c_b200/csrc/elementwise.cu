@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
                                                     const float *__restrict__ shift_txt,
                                                     const float *__restrict__ scale_txt,
                                                     const float *__restrict__ shift_img,
-                                                    const float *__restrict__ scale_img) {
+                                                    const float *__restrict__ scale_img, int *sat) {
   pdl_launch_dependents();
   pdl_wait();
   const int local = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
   const float4 *sh4 = reinterpret_cast<const float4 *>(shift);
   const float4 *sc4 = reinterpret_cast<const float4 *>(scale);
   uint2 *o2 = reinterpret_cast<uint2 *>(out + static_cast<size_t>(row) * hidden);
+  float mx = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const float4 sh = __ldg(sh4 + i * 32 + lane);
@@ -58,19 +59,20 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
     const float b = fmaf((v[i].y - mean) * rstd, 1.f + sc.y, sh.y);
     const float c = fmaf((v[i].z - mean) * rstd, 1.f + sc.z, sh.z);
     const float d = fmaf((v[i].w - mean) * rstd, 1.f + sc.w, sh.w);
-    o2[i * 32 + lane] = make_uint2(pack_16x2(a, b, f16 != 0), pack_16x2(c, d, f16 != 0));
+    o2[i * 32 + lane] = make_uint2(pack_16x2_t(a, b, f16 != 0, mx), pack_16x2_t(c, d, f16 != 0, mx));
   }
+  sat_report(sat, f16 != 0, mx);
 }
 
 int launch_adaln(const float *x, void *out, int row0, int rows, int hidden, int seq, int n_txt, int f16,
                  const float *shift_txt, const float *scale_txt, const float *shift_img, const float *scale_img,
-                 cudaStream_t st) {
+                 cudaStream_t st, int *sat) {
   if (rows <= 0) return 0;
   const int grid = (rows + 3) / 4;
   __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
 #define FX_ADALN(V)                                                                                             \
   launch_kernel(adaln_kernel<V>, dim3(grid), dim3(128), 0, st, 1, x, o, row0, rows, hidden, seq, n_txt, f16, \
-                shift_txt, scale_txt, shift_img, scale_img)
+                shift_txt, scale_txt, shift_img, scale_img, sat)
   switch (hidden) {
     case 3072: FX_ADALN(24); break;
     case 256: FX_ADALN(2); break;
@@ -225,7 +227,8 @@ int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int
 // K7  edges: channel-major f32 latents -> token-major bf16 (the NCHW -> NLC transpose of
 // flux_transformer.c:3156-3161 / 3650-3664 fused with the cast), and f32 -> bf16 for the context.
 // ------------------------------------------------------------------------------------------------
-__global__ void pack_tokens_kernel(const float *__restrict__ z, uint16_t *__restrict__ tok, int C, int n, int f16) {
+__global__ void pack_tokens_kernel(const float *__restrict__ z, uint16_t *__restrict__ tok, int C, int n, int f16,
+                                   int *sat) {
   __shared__ float tile[32][33];
   pdl_launch_dependents();
   pdl_wait();
@@ -241,32 +244,36 @@ __global__ void pack_tokens_kernel(const float *__restrict__ z, uint16_t *__rest
     if (p < n && c < C) {
       const float v = tile[tx][i];
       tok[static_cast<size_t>(p) * C + c] = static_cast<uint16_t>(pack_16x2(v, 0.f, f16 != 0) & 0xFFFFu);
+      sat_report(sat, f16 != 0, fabsf(v));
     }
   }
 }
 
-int launch_pack_tokens(const float *z, void *tok, int C, int n, int f16, cudaStream_t st) {
+int launch_pack_tokens(const float *z, void *tok, int C, int n, int f16, cudaStream_t st, int *sat) {
   dim3 grid((n + 31) / 32, (C + 31) / 32);
   return launch_kernel(pack_tokens_kernel, grid, dim3(32, 8), 0, st, 1, z, reinterpret_cast<uint16_t *>(tok), C, n,
-                       f16) == cudaSuccess
+                       f16, sat) == cudaSuccess
              ? 0
              : -8;
 }
 
-__global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4, int f16) {
+__global__ void f32_to_bf16_kernel(const float4 *__restrict__ in, uint2 *__restrict__ out, long long n4, int f16,
+                                   int *sat) {
+  float mx = 0.f;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float4 v = in[i];
-    out[i] = make_uint2(pack_16x2(v.x, v.y, f16 != 0), pack_16x2(v.z, v.w, f16 != 0));
+    out[i] = make_uint2(pack_16x2_t(v.x, v.y, f16 != 0, mx), pack_16x2_t(v.z, v.w, f16 != 0, mx));
   }
+  sat_report(sat, f16 != 0, mx);
 }
 
-int launch_f32_to_bf16(const float *in, void *out, long long n, int f16, cudaStream_t st) {
+int launch_f32_to_bf16(const float *in, void *out, long long n, int f16, cudaStream_t st, int *sat) {
   if (n % 4) return -1;
   const long long n4 = n / 4;
   const int grid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
   f32_to_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float4 *>(in), reinterpret_cast<uint2 *>(out), n4,
-                                           f16);
+                                           f16, sat);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

@@ -16,6 +16,7 @@
 #include "elementwise.cuh"
 #include "flux_cuda.h"
 #include "gemm.cuh"
+#include "launch.cuh"
 
 namespace fx {
 
@@ -516,6 +517,7 @@ struct Launcher {
   Workspace *ws;
   cudaStream_t st;
   int rc = 0;
+  int group = BG_EDGE;  // part of the forward the next launches belong to
 
   void fail(const char *what, int code) {
     if (!rc) {
@@ -532,8 +534,10 @@ struct Launcher {
       ws->prof_events.push_back(a);
       ws->prof_events.push_back(b);
       ws->prof_class.push_back(cls);
+      ws->prof_group.push_back(group);
     }
     ws->prof_class[ws->prof_used] = cls;
+    ws->prof_group[ws->prof_used] = group;
     cudaEventRecord(ws->prof_events[ws->prof_used * 2], st);
     open = true;
   }
@@ -612,8 +616,12 @@ struct Launcher {
   void adaln(int row0, int rows, const float *sh_t, const float *sc_t, const float *sh_i, const float *sc_i) {
     if (rc) return;
     begin(KC_ADALN);
+    // This launch always follows a paired (cluster) GEMM. A small grid launched with programmatic dependent launch
+    // directly behind such a kernel is the one pattern a device stall was ever traced to (in the VAE, cause not
+    // found), so it goes out in plain stream order; the GEMM behind it still overlaps its prologue with this kernel.
+    PdlOff plain_launch;
     int r = launch_adaln(ws->hs, ws->norm, row0, rows, m->d.hidden, ws->N, ws->n_txt, ACT_F16, sh_t, sc_t, sh_i, sc_i,
-                         st);
+                         st, m->ctx->err_dev + 1);
     count();
     if (r) return fail("adaln", r);
   }
@@ -630,12 +638,11 @@ struct Launcher {
     if (rc) return;
     const int h = m->d.hidden;
     AttnParams A;
-    const bool v2 = m->ctx->attn_version == 2;
-    int r = (v2 ? attn2_make_params : attn_make_params)(&A, ws->qkv, ws->B, ws->N, 3 * h, 0, h, 2 * h, ws->cat,
-                                                        h + m->d.mlp, 0, m->d.heads, ACT_F16, m->ctx->err_dev);
+    int r = attn2_make_params(&A, ws->qkv, ws->B, ws->N, 3 * h, 0, h, 2 * h, ws->cat, h + m->d.mlp, 0, m->d.heads,
+                              ACT_F16, m->ctx->err_dev);
     if (r) return fail("attn_make_params", r);
     begin(KC_ATTN);
-    r = v2 ? attn2_launch(&A, st) : attn_launch(&A, st);
+    r = attn_launch_version(m->ctx->attn_version, &A, st);
     count();
     if (r) return fail("attn_launch", r);
   }
@@ -654,7 +661,7 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
 
   // target tokens of the current latent: NCHW f32 -> NLC bf16 (reference tokens were packed once per sample)
   L.begin(KC_OTHER);
-  if (launch_pack_tokens(ws->z, ws->tok, C, ws->n_img, ACT_F16, st)) L.fail("pack_tokens", -8);
+  if (launch_pack_tokens(ws->z, ws->tok, C, ws->n_img, ACT_F16, st, m->ctx->err_dev + 1)) L.fail("pack_tokens", -8);
   L.count();
   // embedders: image tokens every step; the text projection is step-invariant and was computed once
   {
@@ -670,6 +677,7 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
   }
 
   // ---- double-stream blocks (flux_transformer.c:1774-1986)
+  L.group = BG_DOUBLE;
   for (int blk = 0; blk < d.n_double; ++blk) {
     const DoubleW &w = m->dbl[blk];
     Launcher::Prob pr[4];
@@ -705,6 +713,7 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
   }
 
   // ---- single-stream blocks (flux_transformer.c:2992-3109)
+  L.group = BG_SINGLE;
   for (int blk = 0; blk < d.n_single; ++blk) {
     const SingleW &w = m->sgl[blk];
     L.adaln(0, B * N, ms, ms + h, ms, ms + h);
@@ -719,6 +728,7 @@ static int forward_step(flux_cuda_model *m, Workspace *ws, int step, cudaStream_
   }
 
   // ---- final layer on the target tokens only: modulation is (scale, shift) (flux_transformer.c:3523-3552)
+  L.group = BG_FINAL;
   {
     Launcher::Prob pr[2];
     for (int b = 0; b < B; ++b) {
@@ -740,7 +750,7 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   Launcher L{m, ws, st};
   const long long ctx_n = static_cast<long long>(ws->B) * ws->n_txt * d.text_dim;
   L.begin(KC_OTHER);
-  if (launch_f32_to_bf16(ws->ctx_in, ws->ctx_bf, ctx_n, ACT_F16, st)) L.fail("f32_to_bf16", -8);
+  if (launch_f32_to_bf16(ws->ctx_in, ws->ctx_bf, ctx_n, ACT_F16, st, m->ctx->err_dev + 1)) L.fail("f32_to_bf16", -8);
   L.count();
   Launcher::Prob pc{ws->ctx_bf, d.text_dim, m->ctx_emb, ws->B * ws->n_txt, h, d.text_dim,
                     L.seg(EPI_STORE_F32, ws->txt0, h, 0), 0, {}};
@@ -749,7 +759,8 @@ static int prepare(flux_cuda_model *m, Workspace *ws, int num_steps, cudaStream_
   for (const RefSpec &r : ws->refs) {
     const int n = r.h * r.w;
     L.begin(KC_OTHER);
-    if (launch_pack_tokens(ws->ref_in + off * C, ws->tok + (ws->n_img + off) * C, C, n, ACT_F16, st))
+    if (launch_pack_tokens(ws->ref_in + off * C, ws->tok + (ws->n_img + off) * C, C, n, ACT_F16, st,
+                           m->ctx->err_dev + 1))
       L.fail("pack refs", -8);
     L.count();
     off += n;
@@ -896,6 +907,21 @@ int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launche
     }
     ms_by_class[ws->prof_class[i]] += ms;
     launches_by_class[ws->prof_class[i]]++;
+  }
+  return 0;
+}
+
+int sampler_profile_groups(flux_cuda_sampler *s, float *ms_by_group) {
+  if (!s || !ms_by_group) return FLUX_CUDA_ERR_ARG;
+  Workspace *ws = s->ws;
+  for (int g = 0; g < BG_COUNT; ++g) ms_by_group[g] = 0.f;
+  for (size_t i = 0; i < ws->prof_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ws->prof_events[2 * i], ws->prof_events[2 * i + 1]) != cudaSuccess) {
+      set_error("profile: events not complete (synchronize first)");
+      return FLUX_CUDA_ERR_CUDA;
+    }
+    ms_by_group[ws->prof_group[i]] += ms;
   }
   return 0;
 }

@@ -95,10 +95,14 @@ struct Workspace {
   bool profiling = false;
   std::vector<cudaEvent_t> prof_events;  // pairs: [2i] before, [2i+1] after launch i
   std::vector<int> prof_class;
+  std::vector<int> prof_group;  // BlockGroup of each profiled launch
   size_t prof_used = 0;
 };
 
 enum KernelClass : int { KC_GEMM = 0, KC_ATTN = 1, KC_ADALN = 2, KC_QKNORM = 3, KC_OTHER = 4, KC_COUNT = 5 };
+// Which part of the forward a launch belongs to: the reference keeps wall-clock totals per part
+// (flux_timing_transformer_double / _single / _final, flux_sample.c:22-39).
+enum BlockGroup : int { BG_EDGE = 0, BG_DOUBLE = 1, BG_SINGLE = 2, BG_FINAL = 3, BG_COUNT = 4 };
 
 int model_create(flux_cuda_ctx *ctx, const ModelDims &d, flux_cuda_model **out);
 int model_set_tensor(flux_cuda_model *m, const char *name, const void *data, int dtype, const long long *shape,
@@ -131,5 +135,7 @@ int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int 
 int sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
 // Sums the event pairs of the last profiled run per kernel class (call after a sync).
 int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
+// The same event pairs summed per BlockGroup.
+int sampler_profile_groups(flux_cuda_sampler *s, float *ms_by_group);
 
 }  // namespace fx

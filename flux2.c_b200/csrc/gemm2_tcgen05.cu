@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * P_BN + (static_cast<uint32_t>(q * 32) << 16);
-      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane);
+      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane, P.err + 1);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));

@@ -9,13 +9,15 @@ namespace fx {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 template <int BN>
-__device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row) {
+__device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row,
+                                              int *sat_counter) {
   const bool second = n0 >= pb.n_split;
   const EpiSeg &sg = second ? pb.seg[1] : pb.seg[0];
   const int nrel = n0 - (second ? pb.n_split : 0);  // segment-relative first column of this tile
   const int row = m0 + lane_row;
   const bool row_ok = row < pb.M;
   const bool f16 = sg.out_f16 != 0;
+  float mx = 0.f;  // largest magnitude this thread converted to 16 bits (f16 stores saturate at 65504)
   uint32_t r[32];
 
   switch (sg.mode) {
@@ -30,10 +32,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 v;
-            v.x = pack_16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16);
-            v.y = pack_16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16);
-            v.z = pack_16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16);
-            v.w = pack_16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16);
+            v.x = pack_16x2_t(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16, mx);
+            v.y = pack_16x2_t(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16, mx);
+            v.z = pack_16x2_t(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16, mx);
+            v.w = pack_16x2_t(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16, mx);
             d4[j] = v;
           }
         }
@@ -94,10 +96,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
               for (int e = 0; e < 8; ++e)
                 o[e] = silu_f(__uint_as_float(r[8 * j + e])) * __uint_as_float(u[8 * j + e]);
               uint4 v;
-              v.x = pack_16x2(o[0], o[1], f16);
-              v.y = pack_16x2(o[2], o[3], f16);
-              v.z = pack_16x2(o[4], o[5], f16);
-              v.w = pack_16x2(o[6], o[7], f16);
+              v.x = pack_16x2_t(o[0], o[1], f16, mx);
+              v.y = pack_16x2_t(o[2], o[3], f16, mx);
+              v.z = pack_16x2_t(o[4], o[5], f16, mx);
+              v.w = pack_16x2_t(o[6], o[7], f16, mx);
               d4[j] = v;
             }
           }
@@ -169,8 +171,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
                     ya[k] = x0 * cc - x1 * ss;
                     yb[k] = x0 * ss + x1 * cc;
                   }
-                  oa[e] = pack_16x2(ya[0], ya[1], f16);
-                  ob[e] = pack_16x2(yb[0], yb[1], f16);
+                  oa[e] = pack_16x2_t(ya[0], ya[1], f16, mx);
+                  ob[e] = pack_16x2_t(yb[0], yb[1], f16, mx);
                 }
                 da[j] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
                 db[j] = make_uint4(ob[0], ob[1], ob[2], ob[3]);
@@ -201,8 +203,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
                   const float x1 = __uint_as_float(r[8 * j + 4 * e + 1]) * rinv * ww.y;
                   const float x2 = __uint_as_float(r[8 * j + 4 * e + 2]) * rinv * ww.z;
                   const float x3 = __uint_as_float(r[8 * j + 4 * e + 3]) * rinv * ww.w;
-                  o[2 * e + 0] = pack_16x2(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x, f16);
-                  o[2 * e + 1] = pack_16x2(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z, f16);
+                  o[2 * e + 0] = pack_16x2_t(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x, f16, mx);
+                  o[2 * e + 1] = pack_16x2_t(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z, f16, mx);
                 }
                 d4[j] = make_uint4(o[0], o[1], o[2], o[3]);
               }
@@ -210,10 +212,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 v;
-                v.x = pack_16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16);
-                v.y = pack_16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16);
-                v.z = pack_16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16);
-                v.w = pack_16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16);
+                v.x = pack_16x2_t(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]), f16, mx);
+                v.y = pack_16x2_t(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), f16, mx);
+                v.z = pack_16x2_t(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), f16, mx);
+                v.w = pack_16x2_t(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), f16, mx);
                 d4[j] = v;
               }
             }
@@ -224,6 +226,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
     default:
       break;
   }
+  sat_report(sat_counter, f16, mx);
 }
 
 }  // namespace fx

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      epilogue_tile<BN>(P.p[prob], m0, n0, taddr, q * 32 + lane);
+      epilogue_tile<BN>(P.p[prob], m0, n0, taddr, q * 32 + lane, P.err + 1);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);

@@ -4,15 +4,21 @@
 // Some hosts cannot afford that: a server that has handed every byte of the device to its own pool at start-up and
 // treats a later driver allocation as a fault, or a latency-critical loop in which an allocation (which may
 // synchronise the whole device) is not acceptable. For them the same two kernels run here on scratch that is part of
-// the library image itself: a fixed, file-scope __device__ array, so the entry point below performs no allocation of
-// any kind, on the device or through a library.
+// the library image itself: a fixed, file-scope __device__ array, so that once the library image is on the device the
+// entry point below performs no allocation of any kind, on the device or through a library. The one exception is the
+// first call on a device: the CUDA runtime loads this file's module (its code and the 641 KB array) lazily, at that
+// first cudaGetSymbolAddress, and that load takes device memory from the driver. A host that is about to give the
+// remaining memory to its own pool makes one warm-up call first.
 //
 // The price is a fixed capacity and shared state: the array is one per device, every call on that device uses it, and
 // two calls that overlap in time (different streams or threads) race on it.
 #include <cuda_runtime.h>
 
+#include <stdint.h>
+
 #include "context.cuh"
 #include "flux_cuda.h"
+#include "launch.cuh"
 #include "vae_kernels.cuh"
 
 namespace {
@@ -36,6 +42,11 @@ extern "C" int flux_cuda_group_norm_noalloc(flux_cuda_ctx *ctx, const void *x, i
   using namespace fx;
   if (!ctx || !x || !out16 || !gamma || !beta || n_img < 1 || pixels < 1) {
     set_error("group_norm_noalloc: bad argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out16) | reinterpret_cast<uintptr_t>(gamma) |
+       reinterpret_cast<uintptr_t>(beta)) & 15) {
+    set_error("group_norm_noalloc: x, out16, gamma and beta must be 16-byte aligned");
     return FLUX_CUDA_ERR_ARG;
   }
   if (n_img > NA_MAX_IMAGES) {
@@ -65,6 +76,7 @@ extern "C" int flux_cuda_group_norm_noalloc(flux_cuda_ctx *ctx, const void *x, i
   // that was cut short
   rc = check_cuda(cudaMemsetAsync(counters, 0, NA_COUNTERS * sizeof(unsigned int), ctx->stream), "clear counters");
   if (rc) return rc;
+  PdlOff plain_launches;  // plain stream order, as the VAE itself launches these kernels
   int lr = launch_gn_stats(x, in16, f16, n_img, pixels, C, eps, partial, counters, stats, ctx->stream);
   if (!lr) lr = launch_gn_apply(x, in16, out16, f16, n_img, pixels, C, stats, gamma, beta, swish, ctx->stream);
   if (lr) {

@@ -95,6 +95,9 @@ static int launch_rmsnorm(float *x, void *out, const float *w, int rows, int hid
   const dim3 grid((rows + 3) / 4), block(128);
   uint16_t *o = reinterpret_cast<uint16_t *>(out);
   cudaError_t e;
+  // Plain stream order: this small grid always follows a paired (cluster) GEMM, and a small grid launched with
+  // programmatic dependent launch directly behind such a kernel is the one pattern a device stall was traced to.
+  PdlOff plain_launch;
 #define RMS_LAUNCH(V) launch_kernel(rmsnorm_kernel<V>, grid, block, 0, st, 1, x, o, w, rows, hidden, f16, part, nsplit, pstride)
   switch (hidden) {
     case 2560: e = RMS_LAUNCH(20); break;
@@ -515,7 +518,7 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
     A.kv_group = d.heads / d.kv_heads;
     A.causal = 1;
     A.key_mask = m->mask;
-    gr = attn2_launch(&A, st);
+    gr = attn_launch_version(m->ctx->attn_version, &A, st);
     if (gr) break;
     pending = q_residual_gemm(m, m->attn, qd, w.o, rows, qd);
     if (pending < 0) {

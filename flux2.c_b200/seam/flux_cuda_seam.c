@@ -171,6 +171,25 @@ float *flux_transformer_forward_with_refs(flux_transformer_t *tf, const float *i
 }
 
 /* ------------------------------------------------------------------------------------------ samplers */
+/* Adds the last run's device time per block group to the reference's timing globals (only when profiling is on). */
+static void add_group_times(flux_cuda_sampler *s) {
+  float g[FLUX_CUDA_BLOCK_GROUPS];
+  if (!flux_verbose || flux_cuda_sampler_profile_groups(s, g) != FLUX_CUDA_OK) return;
+  flux_timing_transformer_double += g[1];
+  flux_timing_transformer_single += g[2];
+  flux_timing_transformer_final += g[3];
+}
+
+/* The engine stores activations as f16 by default; a checkpoint whose activations leave that range is clamped, and
+ * says so here instead of silently producing a wrong picture. */
+static void warn_if_saturated(void) {
+  long long n = 0;
+  if (g_ctx && flux_cuda_ctx_saturated_stores(g_ctx, &n, 1) == FLUX_CUDA_OK && n > 0)
+    fprintf(stderr,
+            "flux_cuda: warning: %lld 16-bit stores were clamped to the f16 range (+-65504); "
+            "run with FLUX_CUDA_BF16=1 for this checkpoint\n", n);
+}
+
 static float *sample_common(flux_transformer_t *tf, const float *z, int batch, int channels, int h, int w,
                             const flux_ref_t *refs, int num_refs, const float *emb_cond, int seq_cond,
                             const float *emb_uncond, int seq_uncond, float guidance, const float *schedule,
@@ -199,10 +218,14 @@ static float *sample_common(flux_transformer_t *tf, const float *z, int batch, i
   const int observed = flux_step_callback || progress_callback || flux_substep_callback ||
                        (flux_step_image_callback && flux_step_image_vae);
   double step_ms[FLUX_MAX_STEPS];
+  /* -v: the reference prints wall-clock time per block group (flux_sample.c:270-287); here the same split comes
+   * from CUDA events around every launch, which costs a few percent and is therefore off otherwise */
+  if (!rc && flux_verbose) rc = flux_cuda_sampler_set_profiling(s, 1);
   if (!rc && !observed) {
     /* nobody watches the steps: the whole loop stays on the device */
     rc = flux_cuda_sampler_run(s, schedule, num_steps, guidance, 0, 1);
     if (!rc) rc = flux_cuda_sampler_download(s, out, NULL);
+    if (!rc) add_group_times(s);
   } else {
     for (int step = 0; !rc && step < num_steps; step++) {
       const double t0 = now_ms();
@@ -210,6 +233,7 @@ static float *sample_common(flux_transformer_t *tf, const float *z, int batch, i
       rc = flux_cuda_sampler_run_steps(s, schedule, num_steps, step, 1, guidance, 0);
       if (!rc) rc = flux_cuda_sampler_download(s, out, NULL); /* waits for the step; out = current latent */
       if (rc) break;
+      add_group_times(s);
       fire_substeps(tf);
       if (emb_uncond) fire_substeps(tf); /* the reference runs two forwards per guided step */
       if (step < FLUX_MAX_STEPS) step_ms[step] = now_ms() - t0;
@@ -231,7 +255,19 @@ static float *sample_common(flux_transformer_t *tf, const float *z, int batch, i
         fprintf(stderr, "  Step %d: %.1f ms\n", step + 1, step_ms[step]);
     fprintf(stderr, "  Total denoising: %.1f ms (%.2f s)\n", flux_timing_transformer_total,
             flux_timing_transformer_total / 1000.0);
+    if (flux_timing_transformer_double > 0 || flux_timing_transformer_single > 0) {
+      const double tot = flux_timing_transformer_total;
+      fprintf(stderr, "  Transformer breakdown (device time):\n");
+      fprintf(stderr, "    Double blocks: %.1f ms (%.1f%%)\n", flux_timing_transformer_double,
+              100.0 * flux_timing_transformer_double / tot);
+      fprintf(stderr, "    Single blocks: %.1f ms (%.1f%%)\n", flux_timing_transformer_single,
+              100.0 * flux_timing_transformer_single / tot);
+      fprintf(stderr, "    Final layer:   %.1f ms (%.1f%%)\n", flux_timing_transformer_final,
+              100.0 * flux_timing_transformer_final / tot);
+      fprintf(stderr, "    Total:         %.1f ms\n", tot);
+    }
   }
+  warn_if_saturated();
   flux_cuda_sampler_free(s);
   if (rc) {
     fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());

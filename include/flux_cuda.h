@@ -35,6 +35,25 @@ void flux_cuda_ctx_destroy(flux_cuda_ctx *ctx);
 int flux_cuda_ctx_sync(flux_cuda_ctx *ctx);
 /* The context's cudaStream_t, for callers that time with their own CUDA events. */
 void *flux_cuda_ctx_stream(flux_cuda_ctx *ctx);
+/*
+ * Range check of the f16 format. Every 16-bit store saturates at +-65504 instead of overflowing; the GEMM and
+ * convolution epilogues, AdaLN, the context conversion and the token packing count the threads that clamped a value,
+ * and every synchronising call (flux_cuda_ctx_sync, the sampler / encoder / VAE calls that return host data) adds
+ * that count to the context. *count = saturating stores seen so far (0 = the f16 range held); reset != 0 clears it.
+ * A non-zero count with a real checkpoint means: switch to FLUX_CUDA_BF16. No counterpart in the reference, which
+ * computes in f32.
+ */
+int flux_cuda_ctx_saturated_stores(flux_cuda_ctx *ctx, long long *count, int reset);
+
+/*
+ * Exercises the failure path of the kernels' bounded waits without touching a tensor kernel: queues a one-warp kernel
+ * that waits on a barrier nobody arrives on, gives up after limit_cycles SM clock cycles (1 .. 2e9; 2e6 is about a
+ * millisecond), records the failure in the context's error word and returns normally. The next flux_cuda_ctx_sync
+ * therefore returns FLUX_CUDA_ERR_KERNEL once, and the context stays usable. waited_cycles_dev (device pointer, may
+ * be NULL) receives the cycles the wait really took. No counterpart in the reference (a CPU path has no waits to
+ * bound).
+ */
+int flux_cuda_selftest_wait_timeout(flux_cuda_ctx *ctx, long long limit_cycles, long long *waited_cycles_dev);
 
 /*
  * 16-bit storage format of models created afterwards from this context: FLUX_CUDA_F16 (default) or FLUX_CUDA_BF16
@@ -172,6 +191,11 @@ int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kerne
 #define FLUX_CUDA_KERNEL_CLASSES 5
 int flux_cuda_sampler_set_profiling(flux_cuda_sampler *s, int on);
 int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
+/* The same event pairs summed per part of the forward: 0 input/output edges, 1 double-stream blocks, 2 single-stream
+ * blocks, 3 final layer - the split of the reference's flux_timing_transformer_double / _single / _final
+ * (flux_sample.c:22-39; accumulated at flux_transformer.c:3558-3564), as device time instead of wall-clock time. */
+#define FLUX_CUDA_BLOCK_GROUPS 4
+int flux_cuda_sampler_profile_groups(flux_cuda_sampler *s, float *ms_by_group);
 /* The same per launch, in launch order: ms[i] and kernel_class[i] for up to `capacity` launches. */
 int flux_cuda_sampler_profile_launches(flux_cuda_sampler *s, float *ms, int *kernel_class, int capacity, int *count);
 
@@ -329,16 +353,22 @@ int flux_cuda_conv3x3_stride2(flux_cuda_ctx *ctx, const void *planes16, int n_im
 int flux_cuda_gemm_bias(flux_cuda_ctx *ctx, const void *x16, long long ldx, const void *w16, long long ldw, int M, int N,
                         int K, int w_rows, const float *bias, int mode, void *out, long long ld, int f16);
 /* GroupNorm with 32 groups over channels-last x [n_img, pixels, C] (f32, or 16-bit when in16 != 0), optional swish,
- * 16-bit result (flux_group_norm, flux_kernels.c:511-553; swish_inplace, flux_vae.c:174-177). n_img <= 8. */
+ * 16-bit result (flux_group_norm, flux_kernels.c:511-553; swish_inplace, flux_vae.c:174-177). n_img <= 8; x, out16,
+ * gamma and beta 16-byte aligned (else FLUX_CUDA_ERR_ARG); x and out16 must hold n_img * pixels * C elements - the
+ * call cannot check the extent of the caller's buffers. */
 int flux_cuda_group_norm(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels, int C,
                          const float *gamma, const float *beta, float eps, int swish, int f16);
 /* The same operation for callers that must not allocate: hosts that gave all device memory to their own pool at
  * start-up, or loops that cannot tolerate an allocation's device-wide synchronisation. No counterpart in the
  * reference (it has no device memory to manage). The reduction scratch is a fixed array inside the library image
- * (641 KB per device), so this call performs no allocation at all, on the device or through any library.
- * Limits: n_img <= 4 per call (larger is rejected with FLUX_CUDA_ERR_ARG); the scratch is one per device and shared by
- * every call on it, so calls that overlap in time (other streams or threads) race - serialise them. The first call on
- * a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream capture begins. */
+ * (641 KB per device), so after the first call on a device this call performs no allocation, on the device or
+ * through any library. The FIRST call on a device is different: it looks the array's address up
+ * (cudaGetSymbolAddress), which makes the CUDA runtime load this part of the library image - code plus the 641 KB
+ * array - and that load takes device memory from the driver. Make one warm-up call per device before the host hands
+ * the remaining memory to its own pool and before any stream capture begins.
+ * Limits: n_img <= 4 per call (larger is rejected with FLUX_CUDA_ERR_ARG); pointers 16-byte aligned as above; the
+ * scratch is one per device and shared by every call on it, so calls that overlap in time (other streams or threads)
+ * race - serialise them. */
 int flux_cuda_group_norm_noalloc(flux_cuda_ctx *ctx, const void *x, int in16, void *out16, int n_img, long long pixels,
                                  int C, const float *gamma, const float *beta, float eps, int swish, int f16);
 /* apply_qk_norm + apply_rope_2d (flux_transformer.c:1052-1106, 719-741) in place on bf16 Q and K. */

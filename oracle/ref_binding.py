@@ -13,7 +13,28 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
-OB_DIR = "/opt/prime-rl/.venv/lib/python3.12/site-packages/opencv_python_headless.libs"
+
+
+def _openblas_dir():
+    """Directory of the wheel-bundled OpenBLAS the BLAS build links: FLUX_REF_OPENBLAS_DIR, else the
+    opencv_python_headless.libs folder of whichever site-packages holds it."""
+    env = os.environ.get("FLUX_REF_OPENBLAS_DIR")
+    if env:
+        return env
+    import site
+    import sysconfig
+    roots = [sysconfig.get_paths().get("purelib"), sysconfig.get_paths().get("platlib")]
+    try:
+        roots += site.getsitepackages()
+    except AttributeError:
+        pass
+    for r in roots:
+        if r and os.path.isdir(os.path.join(r, "opencv_python_headless.libs")):
+            return os.path.join(r, "opencv_python_headless.libs")
+    return os.path.join(roots[0] or "", "opencv_python_headless.libs")
+
+
+OB_DIR = _openblas_dir()
 
 c_float_p = ctypes.POINTER(ctypes.c_float)
 
@@ -99,6 +120,18 @@ class RefLib:
         L.flux_power_schedule.argtypes = [ci, cf]
         L.flux_init_noise.restype = vp
         L.flux_init_noise.argtypes = [ci, ci, ci, ci, ctypes.c_int64]
+        # exported by flux_sample.c, called from nowhere in the reference (flux_sample.c:75-116, 697-821, 891-919)
+        L.flux_sigmoid_schedule.restype = vp
+        L.flux_sigmoid_schedule.argtypes = [ci, cf]
+        L.flux_resolution_schedule.restype = vp
+        L.flux_resolution_schedule.argtypes = [ci, ci, ci]
+        L.flux_sample_heun.restype = vp
+        L.flux_sample_heun.argtypes = [vp, c_float_p, ci, ci, ci, ci, c_float_p, ci, c_float_p, ci, vp]
+        L.flux_sample_euler_ancestral.restype = vp
+        L.flux_sample_euler_ancestral.argtypes = [vp, c_float_p, ci, ci, ci, ci, c_float_p, ci, c_float_p, ci, cf, vp]
+        L.flux_generate_latent.restype = vp
+        L.flux_generate_latent.argtypes = [vp, c_float_p, ci, ci, ci, ci, ctypes.c_int64, vp]
+        L.flux_rng_seed.argtypes = [ctypes.c_uint64]
         L.flux_patchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
         L.flux_unpatchify.argtypes = [c_float_p, c_float_p, ci, ci, ci, ci, ci]
         L.qwen3_model_load.restype = vp
@@ -147,6 +180,12 @@ class RefLib:
 
     def power_schedule(self, steps, alpha):
         return self._take(self.L.flux_power_schedule(steps, alpha), steps + 1)
+
+    def sigmoid_schedule(self, steps, shift):
+        return self._take(self.L.flux_sigmoid_schedule(steps, shift), steps + 1)
+
+    def resolution_schedule(self, steps, height, width):
+        return self._take(self.L.flux_resolution_schedule(steps, height, width), steps + 1)
 
     def init_noise(self, channels, h, w, seed):
         return self._take(self.L.flux_init_noise(1, channels, h, w, seed), channels * h * w).reshape(channels, h, w)
@@ -264,6 +303,32 @@ class RefTransformer:
             p = L.flux_sample_euler(self.h, None, _fp(z0), 1, C, h, w, _fp(ctx), ctx.shape[0], _fp(sch),
                                     len(sch) - 1, None)
         return self.lib._take(p, z0.size).reshape(z0.shape)
+
+    def sample_heun(self, z0, h, w, ctx, schedule):
+        """flux_sample_heun (flux_sample.c:760-821)."""
+        z0 = np.ascontiguousarray(z0, dtype=np.float32).copy()
+        ctx = np.ascontiguousarray(ctx, dtype=np.float32)
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        p = self.lib.L.flux_sample_heun(self.h, _fp(z0), 1, z0.shape[0], h, w, _fp(ctx), ctx.shape[0], _fp(sch),
+                                        len(sch) - 1, None)
+        return self.lib._take(p, z0.size).reshape(z0.shape)
+
+    def sample_euler_ancestral(self, z0, h, w, ctx, schedule, eta, rng_seed):
+        """flux_sample_euler_ancestral (flux_sample.c:697-749); the library's global generator (flux_kernels.c:68) is
+        seeded first so that the injected noise is reproducible."""
+        z0 = np.ascontiguousarray(z0, dtype=np.float32).copy()
+        ctx = np.ascontiguousarray(ctx, dtype=np.float32)
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        self.lib.L.flux_rng_seed(rng_seed)
+        p = self.lib.L.flux_sample_euler_ancestral(self.h, _fp(z0), 1, z0.shape[0], h, w, _fp(ctx), ctx.shape[0],
+                                                   _fp(sch), len(sch) - 1, eta, None)
+        return self.lib._take(p, z0.size).reshape(z0.shape)
+
+    def generate_latent(self, ctx, height, width, steps, seed):
+        """flux_generate_latent (flux_sample.c:891-919): seeded noise, linear schedule, plain Euler loop."""
+        ctx = np.ascontiguousarray(ctx, dtype=np.float32)
+        p = self.lib.L.flux_generate_latent(self.h, _fp(ctx), ctx.shape[0], height, width, steps, seed, None)
+        return self.lib._take(p, 128 * (height // 16) * (width // 16)).reshape(128, height // 16, width // 16)
 
     def sample_euler_cfg(self, z0, h, w, ctx_c, ctx_u, guidance, schedule):
         z0 = np.ascontiguousarray(z0, dtype=np.float32).copy()

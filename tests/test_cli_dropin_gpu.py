@@ -93,7 +93,7 @@ def _mk(*parts):
     return p
 
 
-def _run_both(args, tmp_path, tag):
+def _run_both(args, tmp_path, tag, cuda_flags=("-q", "--no-mmap"), stderr_of=None):
     # the reference's BLAS build needs the OpenBLAS (and its libgfortran / libquadmath) bundled in the image's wheels
     site = os.path.dirname(os.path.dirname(np.__file__))
     libs = ":".join(os.path.join(site, d) for d in ("opencv_python_headless.libs", "scipy.libs"))
@@ -102,9 +102,12 @@ def _run_both(args, tmp_path, tag):
     outs = {}
     for name in ("cuda", "ref"):
         out = str(tmp_path / ("out_%s_%s.png" % (tag, name)))
-        cmd = [os.path.join(REF, "flux_%s_cli" % name)] + args + ["-o", out, "-q", "--no-mmap"]
+        flags = list(cuda_flags) if name == "cuda" else ["-q", "--no-mmap"]
+        cmd = [os.path.join(REF, "flux_%s_cli" % name)] + args + ["-o", out] + flags
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
         assert r.returncode == 0, "%s failed:\n%s\n%s" % (name, r.stdout[-2000:], r.stderr[-2000:])
+        if stderr_of is not None:
+            stderr_of[name] = r.stderr
         outs[name] = read_png_rgb(out)
     a, b = outs["cuda"], outs["ref"]
     assert a.shape == b.shape == (128, 128, 3)
@@ -119,6 +122,26 @@ def test_reference_cli_runs_on_the_engine(fx, model_dir, tmp_path):
     fx.init_noise(128, 8, 8, 42).tofile(noise)
     psnr = _run_both(["-d", mdir, "-e", emb, "-n", noise, "-W", "128", "-H", "128", "-s", "4", "-S", "42"], tmp_path, "emb")
     assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+
+
+def test_reference_cli_default_call_path(fx, model_dir, tmp_path):
+    """The CLI as it runs when nothing is switched off: the memory-mapped loader, whose file the transformer then owns
+    (main.c:304, 429-432; flux.c:310-313), and the step / sub-step progress callbacks (main.c:147-154), which make the
+    seam run the loop step by step. -v adds the timing breakdown (flux_sample.c:270-287). Same picture as the
+    reference's CPU build, and the progress line the callbacks draw: five d, four s (one per five single blocks), F."""
+    synth, d, mdir = model_dir
+    emb, noise = str(tmp_path / "emb.bin"), str(tmp_path / "noise.bin")
+    synth.make_context(1234, 512, d.text_dim).tofile(emb)
+    fx.init_noise(128, 8, 8, 42).tofile(noise)
+    err = {}
+    psnr = _run_both(["-d", mdir, "-e", emb, "-n", noise, "-W", "128", "-H", "128", "-s", "4", "-S", "42"], tmp_path,
+                     "default", cuda_flags=("-v",), stderr_of=err)
+    assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+    log = err["cuda"]
+    assert "Denoising (d=double block" in log
+    for step in range(1, 5):
+        assert "Step %d/4 dddddssssF" % step in log, log[-1500:]
+    assert "Denoising timing breakdown" in log and "Single blocks:" in log
 
 
 def test_reference_cli_from_a_text_prompt(fx, model_dir, tmp_path):

@@ -34,6 +34,27 @@ def test_attention_matches_torch(fx, ctx, batch, seq, heads, sharp, dtype):
     assert _rel(out[:, :hid].float(), ref) < (2e-3 if dtype == torch.float16 else 1e-2)  # 16-bit P and output
 
 
+@pytest.mark.parametrize("batch,seq,heads", [(1, 300, 3), (1, 1536, 24), (2, 200, 2)])
+def test_attention_previous_generation_matches_torch(fx, batch, seq, heads, monkeypatch):
+    """FLUX_CUDA_ATTN=2 selects the kernel with four softmax warps per query tile (attention2.cu), kept as the
+    yardstick the current one is measured against."""
+    monkeypatch.setenv("FLUX_CUDA_ATTN", "2")
+    c2 = fx.Context(0)
+    try:
+        hid = heads * 128
+        g = torch.Generator(device="cuda").manual_seed(seq + heads)
+        qkv = torch.randn(batch * seq, 3 * hid, device="cuda", generator=g).half()
+        out = torch.zeros(batch * seq, hid, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        c2.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid, 0, f16=True)
+        c2.sync()
+        q, k, v = [t.float().reshape(batch, seq, heads, 128).transpose(1, 2) for t in qkv.split(hid, dim=1)]
+        ref = (torch.softmax((q @ k.transpose(-1, -2)) / math.sqrt(128.0), dim=-1) @ v).transpose(1, 2)
+        assert _rel(out.float(), ref.reshape(batch * seq, hid)) < 2e-3
+    finally:
+        c2.close()
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,hidden", [(1, 256), (37, 256), (1536, 3072), (1000, 1024)])
 def test_adaln_matches_torch(fx, ctx, rows, hidden, dtype):

@@ -129,14 +129,26 @@ def test_qwen3_4b_matches_reference(fx, ctx):
     chk = float(np.abs(synth.bf16_bits_to_f32(W["model.layers.0.self_attn.q_norm.weight"]).astype(np.float64)).sum() +
                 np.abs(synth.bf16_bits_to_f32(W["model.layers.26.mlp.down_proj.weight"][:64]).astype(np.float64)).sum())
     assert abs(chk - float(g["weights_checksum"])) < 1e-6 * chk
-    enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=512)
+    enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=2048)
     del W
     try:
         got = enc.forward(g["ids"], g["mask"])
         assert rel(got[:, ::4], g["out_sub"]) < TOL
-        # the benchmark's length: 512 tokens, all valid; checked for finiteness and scale here, for parity above
-        ids512 = np.random.default_rng(0).integers(0, d.vocab, 512)
-        out512 = enc.forward(ids512, None)
-        assert out512.shape == (512, 7680) and np.isfinite(out512).all()
+        # the benchmark's length: 512 tokens, all valid, against the reference's output for the same ids
+        p512 = os.path.join(GOLDEN, "reference_qwen3_512.npz")
+        if os.path.exists(p512):
+            g512 = np.load(p512)
+            out512 = enc.forward(g512["ids"], None)
+            assert out512.shape == (512, 7680) and np.isfinite(out512).all()
+            assert rel(out512[:, ::4], g512["out_sub"]) < TOL
+            assert abs(np.sqrt((out512.astype(np.float64) ** 2).mean()) / float(g512["out_rms"]) - 1.0) < 1e-2
+            # four prompts per pass (the throughput mode of the prompt-to-image leg): same rows for every copy
+            ids4 = np.stack([g512["ids"], g512["ids"][::-1], g512["ids"], g512["ids"][::-1]])
+            out4 = enc.forward_batch(ids4, None)
+            assert rel(out4[0][:, ::4], g512["out_sub"]) < TOL and rel(out4[2], out4[0]) < 1e-6
+        else:
+            ids512 = np.random.default_rng(0).integers(0, d.vocab, 512)
+            out512 = enc.forward(ids512, None)
+            assert out512.shape == (512, 7680) and np.isfinite(out512).all()
     finally:
         enc.close()

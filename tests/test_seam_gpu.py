@@ -128,3 +128,169 @@ def test_seam_vae_encode_is_served_by_the_engine(seam, scratch):
         assert rel(got, VaeOracle(W).encode(img)) < 1e-2
     finally:
         seam.L.flux_vae_free(vae)
+
+
+# ------------------------------------------------------------------------------------------------ observers, ownership
+def _mapped(path):
+    with open("/proc/self/maps") as f:
+        return any(line.rstrip().endswith(path) for line in f)
+
+
+def test_seam_callbacks_fire_in_the_reference_order(seam, scratch, fx, capfd):
+    """What the reference's CLI installs unless it is told to be quiet (main.c:147-154): the step callback before a
+    step, one sub-step event per double block, single block and final layer, the progress callback after the step, the
+    step-image callback with a decoded picture after every step but the last (flux_sample.c:229-266,
+    flux_transformer.c:3253, 3488, 3566). The observed loop runs step by step; its latent must be the one the
+    unobserved loop (a single CUDA-graph replay) produces. With flux_verbose the per-group timing globals are filled."""
+    import ctypes
+    import flux2_c_b200.synth as synth
+    from oracle import ref_binding as rb
+    L = seam.L
+    d = synth.Dims.tiny()
+    W = synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08)
+    path = os.path.join(scratch, "tiny_cb.safetensors")
+    synth.write_safetensors(path, W)
+    vpath = os.path.join(scratch, "vae_cb.safetensors")
+    synth.write_safetensors(vpath, synth.make_vae_weights(seed=5, rich=True), dtype="F32")
+    tf = seam.load_transformer(path)
+    vae = seam.load_vae(vpath)
+    events = []
+    STEP = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int)
+    SUB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_int)
+    IMG = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.POINTER(rb.FluxImage))
+    step_cb = STEP(lambda s, n: events.append(("step", s, n)))
+    sub_cb = SUB(lambda t, i, n: events.append(("sub", t, i, n)))
+    prog_cb = STEP(lambda s, n: events.append(("progress", s, n)))
+    img_cb = IMG(lambda s, n, im: events.append(("image", s, n, im.contents.width, im.contents.height)))
+
+    def slot(name):
+        return ctypes.c_void_p.in_dll(L, name)
+
+    h, w, steps = 4, 3, 3
+    z = synth.make_latent(1, d.latent_ch, h, w)
+    c = synth.make_context(2, 24, d.text_dim)
+    sch = np.ascontiguousarray(fx.official_schedule(steps, h * w), dtype=np.float32)
+    fp = ctypes.POINTER(ctypes.c_float)
+
+    def run(progress):
+        zz, cc = z.copy(), c.copy()
+        p = L.flux_sample_euler(tf.h, None, zz.ctypes.data_as(fp), 1, d.latent_ch, h, w, cc.ctypes.data_as(fp),
+                                cc.shape[0], sch.ctypes.data_as(fp), steps, progress)
+        return seam._take(p, z.size).reshape(z.shape)
+
+    quiet = run(None)  # nobody observes: one graph replay on the device
+    assert events == []
+    verbose = ctypes.c_int.in_dll(L, "flux_verbose")
+    try:
+        slot("flux_step_callback").value = ctypes.cast(step_cb, ctypes.c_void_p).value
+        slot("flux_substep_callback").value = ctypes.cast(sub_cb, ctypes.c_void_p).value
+        slot("flux_step_image_callback").value = ctypes.cast(img_cb, ctypes.c_void_p).value
+        slot("flux_step_image_vae").value = vae
+        verbose.value = 1
+        observed = run(ctypes.cast(prog_cb, ctypes.c_void_p))
+    finally:
+        for name in ("flux_step_callback", "flux_substep_callback", "flux_step_image_callback", "flux_step_image_vae"):
+            slot(name).value = None
+        verbose.value = 0
+    want = []
+    for s in range(1, steps + 1):
+        want.append(("step", s, steps))
+        want += [("sub", 0, i, d.n_double) for i in range(d.n_double)]
+        want += [("sub", 1, i, d.n_single) for i in range(d.n_single)]
+        want.append(("sub", 2, 0, 1))
+        want.append(("progress", s, steps))
+        if s < steps:
+            want.append(("image", s, steps, 16 * w, 16 * h))
+    assert events == want
+    assert np.array_equal(observed, quiet)
+    err = capfd.readouterr().err
+    assert "Denoising timing breakdown" in err and "Step 3:" in err and "Double blocks:" in err
+    dbl = ctypes.c_double.in_dll(L, "flux_timing_transformer_double").value
+    sgl = ctypes.c_double.in_dll(L, "flux_timing_transformer_single").value
+    fin = ctypes.c_double.in_dll(L, "flux_timing_transformer_final").value
+    tot = ctypes.c_double.in_dll(L, "flux_timing_transformer_total").value
+    assert dbl > 0 and sgl > 0 and fin > 0 and dbl + sgl + fin <= tot
+    # the single forward fires its sub-step events too (flux_denoise_step, flux.c:1109-1122)
+    events.clear()
+    try:
+        slot("flux_substep_callback").value = ctypes.cast(sub_cb, ctypes.c_void_p).value
+        tf.forward(z, h, w, c, 0.5)
+    finally:
+        slot("flux_substep_callback").value = None
+    assert len(events) == d.n_double + d.n_single + 1
+    tf.close()
+    seam.L.flux_vae_free(vae)
+
+
+def test_seam_mmap_loader_owns_the_file(seam, scratch, fx):
+    """flux_transformer_load_safetensors_mmap takes the open file over and flux_transformer_free closes it
+    (flux.c:310-313, flux_transformer.c:4306-4309); the plain loader leaves it to the caller (flux.c:315-316). This is
+    the loader the reference's CLI uses by default (main.c:304, 429-432)."""
+    import ctypes
+    import flux2_c_b200.synth as synth
+    L = seam.L
+    L.flux_transformer_load_safetensors_mmap.restype = ctypes.c_void_p
+    L.flux_transformer_load_safetensors_mmap.argtypes = [ctypes.c_void_p]
+    d = synth.Dims.tiny()
+    W = synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08)
+    path = os.path.join(scratch, "tiny_mmap.safetensors")
+    synth.write_safetensors(path, W)
+    z = synth.make_latent(1, d.latent_ch, 4, 4)
+    c = synth.make_context(2, 16, d.text_dim)
+
+    sf = L.safetensors_open(path.encode())
+    assert sf and _mapped(path)
+    h = L.flux_transformer_load_safetensors_mmap(sf)
+    assert h
+    from oracle import ref_binding as rb
+    tf = rb.RefTransformer(seam, h)
+    v_mmap = tf.forward(z, 4, 4, c, 0.6)
+    assert _mapped(path)      # still the transformer's
+    tf.close()                # flux_transformer_free
+    assert not _mapped(path)  # ... which closed it
+
+    sf = L.safetensors_open(path.encode())
+    tf2 = rb.RefTransformer(seam, L.flux_transformer_load_safetensors(sf))
+    L.safetensors_close(sf)   # the caller's to close, right after loading; the weights are resident
+    assert not _mapped(path)
+    assert np.array_equal(tf2.forward(z, 4, 4, c, 0.6), v_mmap)
+    tf2.close()
+    L.flux_transformer_free(None)  # NULL-safe
+
+
+def test_seam_unused_sampler_exports_match_reference(seam, scratch, fx):
+    """The exports nothing in the reference calls - flux_sample_heun, flux_sample_euler_ancestral,
+    flux_generate_latent, flux_sigmoid_schedule, flux_resolution_schedule (flux_sample.c:75-116, 697-821, 891-919) -
+    against the reference's own outputs at the klein shape (4 x 4 latent, 32 text tokens)."""
+    import flux2_c_b200.synth as synth
+    path = os.path.join(GOLDEN, "reference_samplers.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference_samplers.npz missing")
+    g = np.load(path)
+    for key in g.files:
+        if key.startswith("sigmoid_"):
+            _, n, shift = key.split("_")
+            assert np.allclose(seam.sigmoid_schedule(int(n), float(shift)), g[key], atol=2e-6), key
+        elif key.startswith("resolution_"):
+            _, n, hh, ww = key.split("_")
+            assert np.allclose(seam.resolution_schedule(int(n), int(hh), int(ww)), g[key], atol=2e-6), key
+    d = synth.Dims.klein4b()
+    wpath = os.path.join(scratch, "klein_sharp.safetensors")
+    synth.write_safetensors(wpath, synth.make_transformer_weights(d, seed=0, sharp=True, threads=os.cpu_count()))
+    tf = seam.load_transformer(wpath)
+    os.remove(wpath)
+    try:
+        h = w = 4
+        z0 = fx.init_noise(128, h, w, 42)
+        c = synth.make_context(1234, 32, d.text_dim)
+        sch = g["sched"]
+        assert rel(tf.sample_euler(z0, h, w, c, sch), g["euler_final"]) < LATENT_TOL
+        assert rel(tf.sample_heun(z0, h, w, c, sch), g["heun_final"]) < LATENT_TOL
+        assert rel(tf.sample_euler_ancestral(z0, h, w, c, sch, 0.0, 777), g["ancestral_eta0_final"]) < LATENT_TOL
+        got = tf.sample_euler_ancestral(z0, h, w, c, sch, 0.5, 777)
+        assert rel(got, g["ancestral_final"]) < LATENT_TOL
+        # the injected noise is part of the result: another seed of the library's generator must move it
+        assert rel(tf.sample_euler_ancestral(z0, h, w, c, sch, 0.5, 778), g["ancestral_final"]) > 5 * LATENT_TOL
+        assert rel(tf.generate_latent(c, 64, 64, 2, 5), g["generate_final"]) < LATENT_TOL
+    finally:
+        tf.close()

@@ -27,9 +27,14 @@ def test_noalloc_group_norm_equals_the_allocating_entry_point(fx, ctx, n, pixels
     for call in range(2):
         got = torch.full((n, pixels, C), float("nan"), device="cuda", dtype=torch.float16)
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         ctx.group_norm_noalloc(x.data_ptr(), in16, got.data_ptr(), n, pixels, C, gamma.data_ptr(), beta.data_ptr(), 1e-4,
                                swish)
         ctx.sync()
+        if call == 1:
+            # the array's module was loaded by the first call at the latest: this one takes nothing from the device
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, "the second call changed the free device memory"
         assert torch.equal(got, want), "call %d differs from flux_cuda_group_norm" % call
         err = (got.float().double() - ref.double()).norm() / ref.double().norm()
         assert err.item() < 6e-4
@@ -43,3 +48,8 @@ def test_noalloc_group_norm_rejects_what_does_not_fit(fx, ctx):
         ctx.group_norm_noalloc(x.data_ptr(), False, o.data_ptr(), 5, 8, 128, w.data_ptr(), w.data_ptr(), 1e-4, False)
     with pytest.raises(fx.FluxCudaError):
         ctx.group_norm_noalloc(x.data_ptr(), False, o.data_ptr(), 1, 8, 96, w.data_ptr(), w.data_ptr(), 1e-4, False)
+    # a pointer that is not 16-byte aligned is refused on the host, before anything is launched
+    for entry in (ctx.group_norm_noalloc, ctx.group_norm):
+        with pytest.raises(fx.FluxCudaError, match="16-byte aligned"):
+            entry(x.data_ptr() + 4, False, o.data_ptr(), 1, 8, 128, w.data_ptr(), w.data_ptr(), 1e-4, False)
+    ctx.sync()
