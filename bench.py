@@ -266,12 +266,45 @@ def run_micro(args):
             ms = timed(lambda: ctx.gemm_qkv_norm_rope(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N // 3, K,
                                                       wq.data_ptr(), wq.data_ptr(), cos.data_ptr(), sin.data_ptr(), M,
                                                       f16=True))
+        elif args.epi == "gated":
+            # the gated residual update of the f32 stream: out_f32 += gate * acc (read-modify-write epilogue)
+            res = torch.randn(M, N, device="cuda")
+            gate = torch.randn(N, device="cuda")
+            torch.cuda.synchronize()
+            ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K,
+                                             fx.EPI_GATED_RES_F32 | fx.EPI_X_F16, gate_ptr=gate.data_ptr(),
+                                             tile_n=args.tile_n))
+        elif args.epi == "f32":
+            res = torch.zeros(M, N, device="cuda")
+            torch.cuda.synchronize()
+            ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K,
+                                             fx.EPI_STORE_F32 | fx.EPI_X_F16, tile_n=args.tile_n))
         else:
             ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
                                              tile_n=args.tile_n))
         tf = 2.0 * M * N * K / ms / 1e9
-        emit({"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "epilogue": args.epi, "ms": ms, "tflops": tf, "frac_of_burst_peak":
-                          tf / peaks["bf16"], "peak_source": peaks["source"]})
+        line = {"micro": "gemm", "shape": [M, N, K], "tile_n": args.tile_n, "epilogue": args.epi, "ms": ms,
+                "tflops": tf, "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]}
+        if args.trace and args.tile_n == 512:
+            # timeline of the first CTA of one more launch, in SM clock cycles since that CTA's entry
+            stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+            torch.cuda.synchronize()
+            ctx.set_gemm_trace(stamps.data_ptr())
+            if args.epi == "gated":
+                ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K, fx.EPI_GATED_RES_F32 | fx.EPI_X_F16,
+                              gate_ptr=gate.data_ptr(), tile_n=512)
+            elif args.epi == "f32":
+                ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K, fx.EPI_STORE_F32 | fx.EPI_X_F16,
+                              tile_n=512)
+            else:
+                ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi, tile_n=512)
+            ctx.sync()
+            ctx.set_gemm_trace(None)
+            st = stamps.cpu().tolist()
+            names = ["entry", "prologue_done", "first_operands", "last_mma_issued", "first_accumulator_ready",
+                     "last_epilogue_done", "before_teardown", "tmem_freed"]
+            line["trace_cycles_since_entry"] = {n: int(v - st[0]) for n, v in zip(names, st)}
+        emit(line)
     elif args.micro == "attn":
         seq, heads = args.seq, 24
         hid = heads * 128
@@ -281,8 +314,21 @@ def run_micro(args):
         ms = timed(lambda: ctx.attention(qkv.data_ptr(), 1, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid,
                                          f16=True))
         tf = 4.0 * seq * seq * hid / ms / 1e9
-        emit({"micro": "attn", "seq": seq, "heads": heads, "ms": ms, "tflops": tf,
-                          "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]})
+        line = {"micro": "attn", "seq": seq, "heads": heads, "ms": ms, "tflops": tf,
+                "frac_of_burst_peak": tf / peaks["bf16"], "peak_source": peaks["source"]}
+        if args.trace:
+            # timeline of CTA (0, 0, 0) of one more launch: 16 SM-clock stamps per key tile, relative to the first
+            T = (seq + 127) // 128
+            stamps = torch.zeros(16 * T, dtype=torch.int64, device="cuda")
+            torch.cuda.synchronize()
+            ctx.set_gemm_trace(stamps.data_ptr())
+            ctx.attention(qkv.data_ptr(), 1, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid, f16=True)
+            ctx.sync()
+            ctx.set_gemm_trace(None)
+            st = stamps.cpu().view(T, 16)
+            base = int(st[st > 0].min())
+            line["trace_cycles"] = [[int(v - base) if v > 0 else None for v in row] for row in st.tolist()]
+        emit(line)
     elif args.micro == "adaln":
         rows, hid = args.rows, 3072
         x = torch.randn(rows, hid, device="cuda")
@@ -934,7 +980,8 @@ def main():
     ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
-    ap.add_argument("--epi", default="store", choices=["store", "qkv"], help="epilogue of --micro gemm")
+    ap.add_argument("--epi", default="store", choices=["store", "qkv", "gated", "f32"], help="epilogue of --micro gemm")
+    ap.add_argument("--trace", action="store_true", help="--micro gemm --tile-n 512: timeline of the first CTA")
     ap.add_argument("--seq", type=int, default=1536)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--size", type=int, default=512, help="image side for --micro vae")

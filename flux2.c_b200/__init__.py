@@ -175,10 +175,37 @@ def _declare(L):
     L.flux_cuda_sampler_profile_groups.argtypes = [c_void_p, fp]
     L.flux_cuda_sampler_profile_launches.restype = c_int
     L.flux_cuda_sampler_profile_launches.argtypes = [c_void_p, fp, ctypes.POINTER(c_int), c_int, ctypes.POINTER(c_int)]
+    L.flux_cuda_ctx_set_gemm_trace.restype = c_int
+    L.flux_cuda_ctx_set_gemm_trace.argtypes = [c_void_p, c_void_p]
     L.flux_cuda_ctx_saturated_stores.restype = c_int
     L.flux_cuda_ctx_saturated_stores.argtypes = [c_void_p, ctypes.POINTER(c_ll), c_int]
     L.flux_cuda_selftest_wait_timeout.restype = c_int
     L.flux_cuda_selftest_wait_timeout.argtypes = [c_void_p, c_ll, c_void_p]
+    L.flux_cuda_group_create.restype = c_int
+    L.flux_cuda_group_create.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_void_p)]
+    L.flux_cuda_group_destroy.restype = None
+    L.flux_cuda_group_destroy.argtypes = [c_void_p]
+    L.flux_cuda_group_size.restype = c_int
+    L.flux_cuda_group_size.argtypes = [c_void_p]
+    L.flux_cuda_group_context.restype = c_void_p
+    L.flux_cuda_group_context.argtypes = [c_void_p, c_int]
+    L.flux_cuda_group_load_safetensors.restype = c_int
+    L.flux_cuda_group_load_safetensors.argtypes = [c_void_p, c_char_p]
+    L.flux_cuda_group_set_models.restype = c_int
+    L.flux_cuda_group_set_models.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_group_sample_batch.restype = c_int
+    L.flux_cuda_group_sample_batch.argtypes = [c_void_p, ctypes.POINTER(CSampleParams), c_int, ctypes.POINTER(fp),
+                                               ctypes.POINTER(fp), ctypes.POINTER(fp)]
+    L.flux_cuda_group_sample_cfg_pair.restype = c_int
+    L.flux_cuda_group_sample_cfg_pair.argtypes = [c_void_p, ctypes.POINTER(CSampleParams), fp, fp]
+    L.flux_cuda_rendezvous_create.restype = c_int
+    L.flux_cuda_rendezvous_create.argtypes = [c_int, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_rendezvous_destroy.restype = None
+    L.flux_cuda_rendezvous_destroy.argtypes = [c_void_p]
+    L.flux_cuda_rendezvous_arrive_and_wait.restype = c_int
+    L.flux_cuda_rendezvous_arrive_and_wait.argtypes = [c_void_p, c_int, c_ll, c_int]
+    L.flux_cuda_rendezvous_abandon.restype = None
+    L.flux_cuda_rendezvous_abandon.argtypes = [c_void_p, c_int]
     L.flux_cuda_official_schedule.restype = None
     L.flux_cuda_official_schedule.argtypes = [c_int, c_int, fp]
     L.flux_cuda_linear_schedule.restype = None
@@ -244,6 +271,9 @@ class Context:
     def set_half_format(self, name):
         """'f16' (default) or 'bf16': storage format of models created afterwards."""
         check(lib().flux_cuda_ctx_set_half_format(self.handle, {"f16": 1, "bf16": 2}[name]))
+
+    def set_gemm_trace(self, stamps_ptr):
+        check(lib().flux_cuda_ctx_set_gemm_trace(self.handle, stamps_ptr))
 
     def set_gemm_pair(self, on):
         check(lib().flux_cuda_ctx_set_gemm_pair(self.handle, int(on)))
@@ -583,6 +613,89 @@ class Vae:
         if self.handle:
             lib().flux_cuda_vae_free(self.handle)
             self.handle = ctypes.c_void_p()
+
+
+class _BorrowedContext(Context):
+    """A context owned by a Group: usable like any other, never destroyed from here."""
+
+    def __init__(self, handle, device):
+        self.handle = ctypes.c_void_p(handle)
+        self.device = device
+
+    def close(self):
+        self.handle = ctypes.c_void_p()
+
+
+class Group:
+    """Several GPUs of one machine driven from one process (flux_cuda_group_*): replicas for independent images, and
+    the guidance pair of the base model split over members 0 and 1."""
+
+    def __init__(self, devices):
+        devices = list(devices)
+        arr = (ctypes.c_int * len(devices))(*devices)
+        self.handle = ctypes.c_void_p()
+        check(lib().flux_cuda_group_create(len(devices), arr, ctypes.byref(self.handle)))
+        self.devices = devices
+        self.models = []
+
+    def context(self, member):
+        return _BorrowedContext(lib().flux_cuda_group_context(self.handle, member), self.devices[member])
+
+    def load_safetensors(self, path):
+        check(lib().flux_cuda_group_load_safetensors(self.handle, path.encode()))
+
+    def set_models(self, models):
+        self.models = list(models)  # keep them alive
+        arr = (ctypes.c_void_p * len(models))(*[m.handle for m in models])
+        check(lib().flux_cuda_group_set_models(self.handle, arr))
+
+    @staticmethod
+    def _params(h, w, schedule, txt_seq, ctx_emb=None, ctx_uncond=None, guidance=1.0, refs=()):
+        np = _np()
+        sch = np.ascontiguousarray(schedule, dtype=np.float32)
+        p = CSampleParams()
+        p.h, p.w, p.num_steps, p.schedule, p.txt_seq, p.guidance = h, w, len(sch) - 1, _fp(sch), txt_seq, guidance
+        keep = [sch]
+        if ctx_emb is not None:
+            ctx_emb = np.ascontiguousarray(ctx_emb, dtype=np.float32)
+            p.ctx = _fp(ctx_emb)
+            keep.append(ctx_emb)
+        if ctx_uncond is not None:
+            ctx_uncond = np.ascontiguousarray(ctx_uncond, dtype=np.float32)
+            p.ctx_uncond = _fp(ctx_uncond)
+            keep.append(ctx_uncond)
+        arr, k2 = Model._refs(refs)
+        p.refs, p.num_refs = arr, len(refs)
+        return p, keep + [arr, k2]
+
+    def sample_batch(self, z0s, ctxs, h, w, schedule, refs=()):
+        """Independent images: z0s[i] [C, h, w], ctxs[i] [txt_seq, text_dim]; image i runs on member i % n."""
+        np = _np()
+        z0s = [np.ascontiguousarray(z, dtype=np.float32) for z in z0s]
+        ctxs = [np.ascontiguousarray(c, dtype=np.float32) for c in ctxs]
+        outs = [np.empty_like(z) for z in z0s]
+        p, keep = self._params(h, w, schedule, ctxs[0].shape[0] if ctxs else 0, refs=refs)
+        n = len(z0s)
+        fpp = ctypes.POINTER(ctypes.c_float)
+        za, ca, oa = (fpp * max(1, n))(*[_fp(z) for z in z0s]), (fpp * max(1, n))(*[_fp(c) for c in ctxs]), \
+            (fpp * max(1, n))(*[_fp(o) for o in outs])
+        check(lib().flux_cuda_group_sample_batch(self.handle, ctypes.byref(p), n, za, ca, oa))
+        return outs
+
+    def sample_cfg_pair(self, z0, h, w, ctx_cond, ctx_uncond, guidance, schedule, refs=()):
+        np = _np()
+        z0 = np.ascontiguousarray(z0, dtype=np.float32)
+        ctx_cond = np.ascontiguousarray(ctx_cond, dtype=np.float32)
+        p, keep = self._params(h, w, schedule, ctx_cond.shape[0], ctx_cond, ctx_uncond, guidance, refs)
+        out = np.empty_like(z0)
+        check(lib().flux_cuda_group_sample_cfg_pair(self.handle, ctypes.byref(p), _fp(z0), _fp(out)))
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().flux_cuda_group_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+        self.models = []
 
 
 class Sampler:

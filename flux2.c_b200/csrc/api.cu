@@ -47,6 +47,10 @@ int ctx_sync_check(flux_cuda_ctx *ctx) {
   if (ctx->err_host[0] != 0) {
     const int code = ctx->err_host[0];
     cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), ctx->stream);
+    if (code == 9) {  // KERR_PEER_TIMEOUT
+      set_error("the other GPU of the pair did not deliver its half of a step within the kernel's wait limit");
+      return FLUX_CUDA_ERR_PEER_TIMEOUT;
+    }
     set_error("a kernel gave up on a bounded wait (code %d)", code);
     return FLUX_CUDA_ERR_KERNEL;
   }
@@ -93,7 +97,7 @@ int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
   }
   if (const char *e = getenv("FLUX_CUDA_GEMM_PAIR")) c->gemm_pair = atoi(e) != 0;
   if (const char *e = getenv("FLUX_CUDA_BF16")) c->f16 = atoi(e) == 0;
-  if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 2 ? 2 : 3;
+  if (const char *e = getenv("FLUX_CUDA_ATTN")) c->attn_version = atoi(e) == 3 ? 3 : 2;
   if (gemm_init() != 0 || gemm2_init() != 0 || attn2_init() != 0 || attn3_init() != 0 || elementwise_init() != 0 ||
       conv_init() != 0) {
     set_error("could not resolve cuTensorMapEncodeTiled / configure shared memory");
@@ -137,6 +141,12 @@ int flux_cuda_ctx_set_half_format(flux_cuda_ctx *ctx, int dtype) {
   return FLUX_CUDA_OK;
 }
 
+int flux_cuda_ctx_set_gemm_trace(flux_cuda_ctx *ctx, long long *stamps_dev) {
+  if (!ctx) return FLUX_CUDA_ERR_ARG;
+  ctx->gemm_trace = stamps_dev;
+  return FLUX_CUDA_OK;
+}
+
 int flux_cuda_ctx_set_gemm_pair(flux_cuda_ctx *ctx, int on) {
   if (!ctx) return FLUX_CUDA_ERR_ARG;
   ctx->gemm_pair = on != 0;
@@ -167,6 +177,7 @@ int flux_cuda_gemm_bf16(flux_cuda_ctx *ctx, const void *x, const void *w, void *
   }
   P.nprob = 1;
   P.err = ctx->err_dev;
+  P.trace = ctx->gemm_trace;
   P.p[0].x_f16 = x_f16;
   P.p[0].seg[0].out_f16 = out_f16;
   P.p[0].seg[0].mode = epilogue;
@@ -249,6 +260,7 @@ int flux_cuda_attention(flux_cuda_ctx *ctx, const void *qkv, int batch, int seq,
     set_error("attention: unsupported shape/alignment (rc %d)", rc);
     return FLUX_CUDA_ERR_ARG;
   }
+  A.trace = ctx->gemm_trace;  // measurement aid, normally null (flux_cuda_ctx_set_gemm_trace)
   rc = attn_launch_version(ctx->attn_version, &A, ctx->stream);
   if (rc) {
     set_error("attention: launch failed: %s", cudaGetErrorString(cudaGetLastError()));

@@ -20,6 +20,8 @@ struct alignas(64) AttnParams {
   int causal;              // key j is visible to query i only if j <= i
   const uint32_t *key_mask;  // [batch, ceil(seq/32)] bit j%32 of word j/32 set = key j is valid; NULL = all valid
   int *err;
+  long long *trace;        // optional (attention2.cu): clock64 stamps of CTA (0,0,0), 16 per key tile, for timeline
+                           // measurements: 0-4 MMA issuer, 5-9 softmax warp of tile a, 10-14 of tile b, 15 producer
 };
 
 // Second-generation kernel (attention2.cu): two query tiles per CTA, P and the output accumulator in TMEM.

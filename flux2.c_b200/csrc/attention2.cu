@@ -91,6 +91,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     *abort_flag = 1;
     atomicCAS(P.err, 0, KERR_WAIT_ATTN);
   };
+  const bool traced = P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int j, int slot) {
+    if (traced) P.trace[j * 16 + slot] = clock64();
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -110,6 +114,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
         }
         uint8_t *sk = smem + OFF_KV + s * 65536;
         uint8_t *sv = sk + 32768;
+        stamp(j, 15);
         mbar_arrive_expect_tx(&B->k_full[s], 2 * CHUNK_BYTES);
         tma_load_3d(sk, &P.tm, &B->k_full[s], P.k_col + kv_head * 128, j * TILE, batch);
         tma_load_3d(sk + CHUNK_BYTES, &P.tm, &B->k_full[s], P.k_col + kv_head * 128 + 64, j * TILE, batch);
@@ -147,10 +152,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
       for (int j = 0; ok && j < T; ++j) {
         const int st = j & 1;
         ok = mbar_wait(&B->v_full[st], (j >> 1) & 1, abort_flag);
+        stamp(j, 0);
         const uint32_t sv = smem_u32(smem + OFF_KV + st * 65536 + 32768);
         for (int t = 0; ok && t < QTILES; ++t) {
           ok = mbar_wait(&B->p_ready[t], j & 1, abort_flag);
           if (!ok) break;
+          stamp(j, 1 + 2 * t);
           tc_fence_after_sync();
           // O_t (+)= P_t V: P_t sits in the first 64 columns of S_t, 16 keys = 8 columns per MMA
           const uint32_t d = tmem + 256 + t * 128;
@@ -171,6 +178,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
             }
             issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
           }
+          stamp(j, 2 + 2 * t);
         }
       }
       if (!ok) fail();
@@ -194,10 +202,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     for (int j = 0; j < T; ++j) {
       ok = mbar_wait_warp(&B->s_ready[t], j & 1, abort_flag);
       if (!ok) break;
+      const bool tr = q == 2 && lane == 0;  // warps 2 and 6: the first warp of each tile
+      if (tr) stamp(j, 5 + 5 * t);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_32x32(s_addr + c * 32, s[c]);
       tc_wait_ld();
+      if (tr) stamp(j, 6 + 5 * t);
       // keys of this tile this row may see: inside the sequence, not after the query (causal), not masked out
       int limit = P.seq - j * TILE;
       if (P.causal) {
@@ -249,6 +260,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
           m_ref = mloc;
         }
       }
+      if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
       float rowsum = 0.f;
 #pragma unroll
@@ -266,10 +278,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
         tc_st_32x32(s_addr + h * 32, pk);
       }
       l += rowsum;
+      if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&B->p_ready[t]);
+      if (tr) stamp(j, 9 + 5 * t);
     }
     if (ok) ok = mbar_wait_warp(&B->o_done[t], (T - 1) & 1, abort_flag);
     if (!ok) {
@@ -359,6 +373,7 @@ int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long l
   p->causal = 0;
   p->key_mask = nullptr;
   p->err = err;
+  p->trace = nullptr;
   return 0;
 }
 

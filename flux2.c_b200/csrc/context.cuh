@@ -13,9 +13,10 @@ struct flux_cuda_ctx {
   int *err_host = nullptr;        // pinned mirror of both
   long long saturated = 0;        // saturated f16 stores seen by the synchronisations so far
   bool f16 = true;                // 16-bit tensors (weights and activations) are f16; false: bf16
-  int attn_version = 3;           // 3: attention3.cu (default), 2: attention2.cu (FLUX_CUDA_ATTN=2)
+  int attn_version = 2;           // 2: attention2.cu (default), 3: attention3.cu (FLUX_CUDA_ATTN=3, measured slower)
   bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
   float *gn_scratch = nullptr;    // lazily allocated scratch of the kernel-level GroupNorm entry point
+  long long *gemm_trace = nullptr;  // device buffer for the paired GEMM's timeline stamps (measurements only)
 };
 
 namespace fx {

@@ -31,7 +31,10 @@ struct QkvNormRope {
   int pos0, seq, n_txt, q_cols, k_cols, half_split;
 };
 
-struct EpiSeg {
+struct alignas(64) EpiSeg {
+  CUtensorMap tm_out;  // paired kernel, f32 store modes: f32 view [M, col0 + width] of `out`, box 32 x 32, 128-byte swizzle
+  int tma_out;         // tm_out is valid: the epilogue stages 32 x 32 blocks in shared memory and lets the TMA unit
+                       // store them (STORE_F32) or add them to the destination in L2 (GATED_RES_F32)
   int mode;
   int out_f16;        // 16-bit outputs are written as f16 (saturating) instead of bf16
   int col0;           // first destination column of this segment
@@ -59,7 +62,10 @@ struct alignas(64) GemmParams {
   int nprob;
   int tile_end[GEMM_MAX_PROBLEMS];   // exclusive prefix sums of the problems' tile counts
   int total_tiles;
-  int *err;          // device word; first failing role stores a KernelError here
+  int *err;          // device words: [0] first failing role's KernelError, [1] count of saturated f16 stores
+  long long *trace;  // optional (paired kernel only): 8 clock64 stamps of CTA 0's roles, for timeline measurements:
+                     // 0 entry, 1 prologue done, 2 first operands landed, 3 last MMA issued, 4 first accumulator
+                     // ready, 5 last epilogue done, 6 before teardown, 7 TMEM freed
 };
 
 // Fills the tensor maps and tile counts of `p` for tile width bn (128 or 256). Returns 0 on success.
@@ -80,5 +86,8 @@ int gemm_init();  // resolves cuTensorMapEncodeTiled and opts the kernels into l
 // row pitch `ld` elements, box = box_cols x box_rows, 128-byte swizzle.
 int make_tmap_2d_bf16(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
                       uint32_t box_cols);
+// The same for f32 elements (box_cols * 4 bytes must be 128: one swizzle span).
+int make_tmap_2d_f32(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t box_cols);
 
 }  // namespace fx

@@ -10,6 +10,7 @@
 // and "accumulator full" barriers exist in both CTAs and are signalled by one multicast tcgen05.commit;
 // "accumulator drained" lives in the leader and collects the arrivals of all eight epilogue warps of the pair.
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 #include "gemm.cuh"
 #include "gemm_epilogue.cuh"
@@ -25,13 +26,17 @@ static constexpr int P_STAGES = 6;
 static constexpr int P_A_BYTES = P_BM * P_BK * 2;        // 16 KB
 static constexpr int P_B_BYTES = (P_BN / 2) * P_BK * 2;  // 16 KB: this CTA's half of the W tile
 static constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-static constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 256 + 1024;
+static constexpr int P_EPI_STAGE = 4 * EPI_STAGE_BYTES_PER_WARP;  // staging blocks of the four epilogue warps
+static constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + P_EPI_STAGE + 256 + 1024;
+static_assert(P_SMEM <= 232448, "shared memory of the paired GEMM exceeds what an SM offers");
+static_assert(sizeof(GemmParams) <= 4096, "kernel parameters must stay within the classic 4 KB limit");
 static constexpr int P_THREADS = 192;
 
 __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __grid_constant__ GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P_STAGES * P_STAGE_BYTES);
+  uint8_t *epi_stage = smem + P_STAGES * P_STAGE_BYTES;  // 1024-byte aligned
+  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_stage + P_EPI_STAGE);
   uint64_t *full = bars;                  // used in the leader only
   uint64_t *empty = bars + P_STAGES;      // both CTAs
   uint64_t *tfull = bars + 2 * P_STAGES;  // both CTAs
@@ -44,6 +49,11 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  const bool traced = P.trace != nullptr && blockIdx.x == 0;
+  auto stamp = [&](int slot) {
+    if (traced) P.trace[slot] = clock64();
+  };
+  if (threadIdx.x == 0) stamp(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -65,6 +75,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
   pdl_wait();  // everything above touched only shared memory and TMEM
+  if (threadIdx.x == 0) stamp(1);
 
   auto fail = [&](int code) {
     *abort_flag = 1;
@@ -140,6 +151,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
             break;
           }
           tc_fence_after_sync();
+          if (kiter == 0) stamp(2);
           const uint32_t sa = smem_u32(smem + s * P_STAGE_BYTES);
           const uint64_t ad = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sa + P_A_BYTES, 16, 1024);
@@ -149,6 +161,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
         }
         if (ok) tc_commit_pair(&tfull[acc], 3);
       }
+      stamp(3);
     }
     __syncwarp();
   } else {
@@ -165,15 +178,20 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
         break;
       }
       tc_fence_after_sync();
+      if (it == 0 && warp == 2 && lane == 0) stamp(4);
       const uint32_t taddr = tmem_base + acc * P_BN + (static_cast<uint32_t>(q * 32) << 16);
-      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane, P.err + 1);
+      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane, P.err + 1,
+                          epi_stage + q * EPI_STAGE_BYTES_PER_WARP);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
     }
+    if (lane == 0) bulk_wait<0>();  // this warp's TMA stores have been performed before the CTA leaves
+    if (warp == 2 && lane == 0) stamp(5);
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == 0) stamp(6);
   if (*abort_flag) {
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) __nanosleep(1000);
@@ -184,6 +202,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, 512);
+    if (lane == 0) stamp(7);
   }
 }
 
@@ -203,6 +222,20 @@ int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
     P->tile_end[i] = acc;
   }
   P->total_tiles = acc;
+  // f32 outputs leave through the TMA unit when the destination allows it (16-byte aligned base and pitch);
+  // FLUX_CUDA_EPI_TMA=0 keeps the direct global stores (for comparisons)
+  static const bool tma_epilogue = !(getenv("FLUX_CUDA_EPI_TMA") && atoi(getenv("FLUX_CUDA_EPI_TMA")) == 0);
+  for (int i = 0; i < P->nprob; ++i) {
+    GemmProblem &pb = P->p[i];
+    for (int sgi = 0; sgi < 2; ++sgi) {
+      EpiSeg &sg = pb.seg[sgi];
+      sg.tma_out = 0;
+      const int width = sgi == 0 ? pb.n_split : pb.N - pb.n_split;
+      if (!tma_epilogue || width <= 0 || !sg.out || (sg.mode != EPI_STORE_F32 && sg.mode != EPI_GATED_RES_F32) || (sg.col0 & 3)) continue;
+      if (make_tmap_2d_f32(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + width, sg.ld, 32, 32) == 0)
+        sg.tma_out = 1;
+    }
+  }
   int pairs = num_sms / 2;
   if (acc < pairs) pairs = acc;
   return launch_kernel(gemm2_bf16_tn_kernel, dim3(2 * pairs), dim3(P_THREADS), P_SMEM, stream, 2, *P) == cudaSuccess

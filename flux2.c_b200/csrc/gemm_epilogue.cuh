@@ -8,9 +8,36 @@ namespace fx {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Shared-memory staging of the TMA-store epilogues: two 32 x 32 f32 blocks (4 KB each, 1024-byte aligned) per warp.
+static constexpr int EPI_STAGE_BYTES_PER_WARP = 2 * 4096;
+
+// One 32-column chunk of this warp's 32 rows goes out through the TMA unit: every lane writes its row's 32 floats
+// into the staging block (16-byte pieces permuted as the 128-byte swizzle wants them, which also keeps the eight
+// lanes of a store phase on different banks), then one lane hands the block to the TMA unit.
+template <bool REDUCE>
+__device__ __forceinline__ void stage_and_store_chunk(const CUtensorMap *tm, uint8_t *buf, const float (&v)[32], int lane,
+                                                      int x, int y, bool issue) {
+  const uint32_t base = smem_u32(buf) + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t a = base + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                 "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                 : "memory");
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && issue) {
+    if (REDUCE) tma_reduce_add_2d(tm, buf, x, y);
+    else tma_store_2d(tm, buf, x, y);
+    bulk_commit();
+  }
+}
+
+// stage: this warp's staging blocks (paired kernel) or nullptr (direct global stores).
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row,
-                                              int *sat_counter) {
+                                              int *sat_counter, uint8_t *stage = nullptr) {
   const bool second = n0 >= pb.n_split;
   const EpiSeg &sg = second ? pb.seg[1] : pb.seg[0];
   const int nrel = n0 - (second ? pb.n_split : 0);  // segment-relative first column of this tile
@@ -42,6 +69,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
       }
     } break;
     case EPI_STORE_F32: {
+      if (stage != nullptr && sg.tma_out) {
+        const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tc_ld_32x32(taddr + c * 32, r);
+          if (c >= 2) {  // the store that last used this block has read it
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+          }
+          tc_wait_ld();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          stage_and_store_chunk<false>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
+                                       y < pb.M);
+        }
+        if (lane == 0) bulk_wait_read<0>();  // the next tile's epilogue writes these blocks again
+        __syncwarp();
+        break;
+      }
       float *dst = reinterpret_cast<float *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -55,6 +102,34 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
       }
     } break;
     case EPI_GATED_RES_F32: {
+      if (stage != nullptr && sg.tma_out) {
+        // out += gate * acc as a TMA reduce-add: the residual is read and updated in L2, the SM only sends gate * acc
+        const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+        const float4 *g4 = reinterpret_cast<const float4 *>(sg.gate + nrel);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tc_ld_32x32(taddr + c * 32, r);
+          if (c >= 2) {
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+          }
+          tc_wait_ld();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 g = __ldg(g4 + c * 8 + j);
+            v[4 * j + 0] = g.x * __uint_as_float(r[4 * j + 0]);
+            v[4 * j + 1] = g.y * __uint_as_float(r[4 * j + 1]);
+            v[4 * j + 2] = g.z * __uint_as_float(r[4 * j + 2]);
+            v[4 * j + 3] = g.w * __uint_as_float(r[4 * j + 3]);
+          }
+          stage_and_store_chunk<true>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
+                                      y < pb.M);
+        }
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+        break;
+      }
       float *dst = reinterpret_cast<float *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
       const float *gate = sg.gate + nrel;
 #pragma unroll 1

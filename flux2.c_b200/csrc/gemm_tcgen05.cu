@@ -231,6 +231,20 @@ int make_tmap_2d_bf16(CUtensorMap *m, const void *base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -4;
 }
 
+int make_tmap_2d_f32(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t box_cols) {
+  if (!g_encode && gemm_init() != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 4) & 15) || box_cols * 4 != 128) return -3;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -4;
+}
+
 int gemm_make_problem(GemmProblem *p, const void *X, long long ldx, const void *W, int M, int N, int K, int bn,
                       long long ldw) {
   if (ldw == 0) ldw = K;

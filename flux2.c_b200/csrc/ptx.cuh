@@ -26,6 +26,7 @@ enum KernelError : int {
   KERR_BAD_SHAPE = 6,
   KERR_SELFTEST = 7,        // the self-test kernel's wait ran out, as it is meant to
   KERR_BAD_INDEX = 8,       // checked build only: a kernel computed an address outside its buffer and skipped it
+  KERR_PEER_TIMEOUT = 9,    // the other GPU of a guidance pair did not deliver its half of a step in time
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -133,6 +134,35 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
           "r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+// TMA stores from shared memory (bulk async-group completion). The source must have been made visible to the async
+// proxy (fence_proxy_async_smem by the writing threads, then a barrier) and must stay untouched until
+// bulk_wait_read says the copy has read it. x * sizeof(elem) must be a multiple of 16 bytes; rows and columns beyond
+// the tensor's extent are clipped. Never started at a negative coordinate.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// dst += src, element by element, performed at the destination (f32 add in L2): the read-modify-write of a residual
+// stream without the read ever reaching the SM.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *m, const void *smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most N of this thread's bulk groups may still be reading their shared-memory source / may still be in flight.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---------------------------------------------------------------- TMEM allocation (one full warp)

@@ -35,6 +35,7 @@ typedef struct flux_transformer {
   flux_cuda_model *model;
   safetensors_file_t *owned_sf; /* set by the _mmap loader, which takes ownership of the file */
   flux_cuda_dims dims;
+  int grouped;                  /* the replicas belong to the GPU group (FLUX_CUDA_DEVICES=a,b) */
 } flux_transformer_t;
 
 typedef struct { /* flux.c:68-72 */
@@ -62,6 +63,7 @@ void flux_reset_timing(void) {
 }
 
 static flux_cuda_ctx *g_ctx = NULL;
+static flux_cuda_group *g_group = NULL; /* FLUX_CUDA_DEVICES=a,b: guided sampling splits its two passes over a and b */
 
 static double now_ms(void) {
   struct timeval tv;
@@ -71,10 +73,23 @@ static double now_ms(void) {
 
 static flux_cuda_ctx *seam_ctx(void) {
   if (!g_ctx) {
-    const char *dev = getenv("FLUX_CUDA_DEVICE");
-    if (flux_cuda_ctx_create(dev ? atoi(dev) : 0, &g_ctx) != FLUX_CUDA_OK) {
-      fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
-      g_ctx = NULL;
+    const char *list = getenv("FLUX_CUDA_DEVICES");
+    int devs[2], n = 0;
+    if (list && sscanf(list, "%d,%d", &devs[0], &devs[1]) == 2) n = 2;
+    if (n == 2) {
+      if (flux_cuda_group_create(2, devs, &g_group) == FLUX_CUDA_OK) {
+        g_ctx = flux_cuda_group_context(g_group, 0);
+      } else {
+        fprintf(stderr, "flux_cuda: FLUX_CUDA_DEVICES=%s ignored: %s\n", list, flux_cuda_last_error());
+        g_group = NULL;
+      }
+    }
+    if (!g_ctx) {
+      const char *dev = getenv("FLUX_CUDA_DEVICE");
+      if (flux_cuda_ctx_create(dev ? atoi(dev) : 0, &g_ctx) != FLUX_CUDA_OK) {
+        fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+        g_ctx = NULL;
+      }
     }
   }
   return g_ctx;
@@ -90,7 +105,15 @@ static flux_transformer_t *load_from(safetensors_file_t *sf) {
   flux_transformer_t *tf = (flux_transformer_t *)calloc(1, sizeof(*tf));
   if (!tf) return NULL;
   /* the file is already open and mapped by the caller: hand the path to the engine's own validating loader */
-  if (flux_cuda_model_load_safetensors(ctx, sf->path, &tf->model) != FLUX_CUDA_OK) {
+  int rc;
+  if (g_group) { /* one replica per GPU of the pair, loaded concurrently */
+    rc = flux_cuda_group_load_safetensors(g_group, sf->path);
+    tf->model = rc == FLUX_CUDA_OK ? flux_cuda_group_model(g_group, 0) : NULL;
+    tf->grouped = 1;
+  } else {
+    rc = flux_cuda_model_load_safetensors(ctx, sf->path, &tf->model);
+  }
+  if (rc != FLUX_CUDA_OK) {
     fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
     free(tf);
     return NULL;
@@ -116,7 +139,8 @@ flux_transformer_t *flux_transformer_load(FILE *f) {
 
 void flux_transformer_free(flux_transformer_t *tf) {
   if (!tf) return;
-  flux_cuda_model_free(tf->model);
+  if (tf->grouped) flux_cuda_group_unload(g_group);
+  else flux_cuda_model_free(tf->model);
   if (tf->owned_sf) safetensors_close(tf->owned_sf);
   free(tf);
 }
@@ -210,6 +234,42 @@ static float *sample_common(flux_transformer_t *tf, const float *z, int batch, i
   float *out = (float *)malloc(n * sizeof(float));
   flux_cuda_sampler *s = NULL;
   int rc = out ? FLUX_CUDA_OK : FLUX_CUDA_ERR_NOMEM;
+  if (!rc && emb_uncond && tf->grouped && g_group && !flux_verbose &&
+      !(flux_step_callback || progress_callback || flux_substep_callback ||
+        (flux_step_image_callback && flux_step_image_vae))) {
+    /* two GPUs and nobody watching the steps: the conditional pass runs on one, the unconditional pass on the other
+     * (the reference runs them one after the other, flux_sample.c:485-499) */
+    flux_cuda_ref cr[16];
+    for (int i = 0; i < num_refs; i++) {
+      cr[i].latent = refs[i].latent;
+      cr[i].h = refs[i].h;
+      cr[i].w = refs[i].w;
+      cr[i].t_offset = refs[i].t_offset;
+    }
+    flux_cuda_sample_params sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.h = h;
+    sp.w = w;
+    sp.num_steps = num_steps;
+    sp.schedule = schedule;
+    sp.ctx = emb_cond;
+    sp.ctx_uncond = emb_uncond;
+    sp.txt_seq = seq_cond;
+    sp.guidance = guidance;
+    sp.refs = cr;
+    sp.num_refs = num_refs;
+    flux_reset_timing();
+    const double t_pair = now_ms();
+    rc = flux_cuda_group_sample_cfg_pair(g_group, &sp, z, out);
+    flux_timing_transformer_total = now_ms() - t_pair;
+    warn_if_saturated();
+    if (rc) {
+      fprintf(stderr, "flux_cuda: %s\n", flux_cuda_last_error());
+      free(out);
+      return NULL;
+    }
+    return out;
+  }
   if (!rc) rc = flux_cuda_sampler_create(tf->model, h, w, seq_cond, shapes, num_refs, emb_uncond ? 2 : 1, num_steps, &s);
   if (!rc) rc = flux_cuda_sampler_upload(s, z, emb_cond, emb_uncond, lat);
 

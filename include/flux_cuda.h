@@ -23,6 +23,7 @@ extern "C" {
 #define FLUX_CUDA_ERR_IO (-4)      /* file missing / truncated / malformed */
 #define FLUX_CUDA_ERR_MODEL (-5)   /* tensor missing, wrong shape or dtype */
 #define FLUX_CUDA_ERR_NOMEM (-6)
+#define FLUX_CUDA_ERR_PEER_TIMEOUT (-7) /* the other GPU of a pair did not show up in time (host rendezvous or kernel wait) */
 
 typedef struct flux_cuda_ctx flux_cuda_ctx;
 
@@ -68,6 +69,15 @@ int flux_cuda_ctx_set_half_format(flux_cuda_ctx *ctx, int dtype);
  * neighbouring SMs per 256 x 256 tile (tcgen05 cta_group::2; each CTA stages half of the weight tile). Also
  * settable with the environment variable FLUX_CUDA_GEMM_PAIR before the context is created. */
 int flux_cuda_ctx_set_gemm_pair(flux_cuda_ctx *ctx, int on);
+/* Measurement aid: while stamps_dev (device memory, int64) is set, kernels launched through the kernel-level entry
+ * points write the SM clock of their first CTA at fixed points of its life. flux_cuda_gemm_bf16 (paired kernel),
+ * 8 stamps: 0 entry, 1 prologue done, 2 first operands landed, 3 last MMA issued, 4 first accumulator ready, 5 last
+ * epilogue done, 6 before teardown, 7 TMEM freed. flux_cuda_attention, 16 stamps per key tile j at [16 j + ..]:
+ * 0-4 MMA issuer (V landed, P of tile a seen, a's MMAs issued, P of tile b seen, b's MMAs issued), 5-9 first softmax
+ * warp of tile a (S ready, S loaded, maximum known, P computed, P released), 10-14 the same for tile b, 15 producer
+ * (K/V tile j requested); the buffer must hold 16 x ceil(seq / 128) values. NULL switches it off. No counterpart in
+ * the reference. */
+int flux_cuda_ctx_set_gemm_trace(flux_cuda_ctx *ctx, long long *stamps_dev);
 
 /* ------------------------------------------------------------------------------------------------
  * Model: the FLUX.2-klein diffusion transformer resident on one GPU (bf16 weights).
@@ -198,6 +208,56 @@ int flux_cuda_sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long lon
 int flux_cuda_sampler_profile_groups(flux_cuda_sampler *s, float *ms_by_group);
 /* The same per launch, in launch order: ms[i] and kernel_class[i] for up to `capacity` launches. */
 int flux_cuda_sampler_profile_launches(flux_cuda_sampler *s, float *ms, int *kernel_class, int capacity, int *count);
+
+/* ------------------------------------------------------------------------------------------------
+ * Several GPUs of one machine. The reference drives one device and runs the two passes of a guided step one after
+ * the other (flux_sample_euler_cfg, flux_sample.c:485-499); these calls let a plain C host use more than one GPU:
+ * one internal host thread per GPU, a full replica of the model on each.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct flux_cuda_group flux_cuda_group;
+
+/* One context per listed device (devices == NULL: 0 .. n_gpus-1). Members 0 and 1 get access to each other's memory
+ * when the hardware allows it (needed by flux_cuda_group_sample_cfg_pair only). FLUX_CUDA_PEER_TIMEOUT_MS overrides
+ * the 20 s the host threads of a pair wait for each other. */
+int flux_cuda_group_create(int n_gpus, const int *devices, flux_cuda_group **out);
+void flux_cuda_group_destroy(flux_cuda_group *g);
+int flux_cuda_group_size(const flux_cuda_group *g);
+/* The member's context, e.g. to create a model on it from tensors. Owned by the group. */
+flux_cuda_ctx *flux_cuda_group_context(flux_cuda_group *g, int member);
+/* A replica on every member, loaded concurrently (flux_transformer_load_safetensors, once per GPU); owned by the
+ * group. Or: hand the group models the caller created on the members' contexts (the caller keeps ownership). */
+int flux_cuda_group_load_safetensors(flux_cuda_group *g, const char *path);
+int flux_cuda_group_set_models(flux_cuda_group *g, flux_cuda_model *const *models);
+/* The member's replica (NULL before a load), and: drop the replicas (frees the ones the group loaded itself). */
+flux_cuda_model *flux_cuda_group_model(flux_cuda_group *g, int member);
+void flux_cuda_group_unload(flux_cuda_group *g);
+/*
+ * n_images independent images, image i on member i % n_gpus: z0[i], ctx[i] (host f32, shapes as in `p`; p->ctx,
+ * p->ctx_uncond and p->guidance are ignored, p->refs are shared by all images) -> latent_out[i]. No data moves
+ * between the GPUs. The loop per image is flux_sample_euler / _with_multi_refs (flux_sample.c:212-290, 381-444).
+ */
+int flux_cuda_group_sample_batch(flux_cuda_group *g, const flux_cuda_sample_params *p, int n_images,
+                                 const float *const *z0, const float *const *ctx, float *const *latent_out);
+/*
+ * One guided image on members 0 and 1: member 0 runs the conditional pass, member 1 the unconditional one, every
+ * step; each stores its pre-scaled velocity (g v_c, (1 - g) v_u) into the other's memory with plain stores, waits for
+ * the other's, and adds both into its own latent (one kernel per step and GPU; 128 h w floats cross NVLink each
+ * way). Same result as flux_cuda_sample with ctx_uncond set (flux_sample_euler_cfg*, flux_sample.c:457-691), in
+ * about half the time. The two host threads meet before every step; if one of them failed or does not arrive in
+ * time the other returns FLUX_CUDA_ERR_PEER_TIMEOUT without having launched anything that waits, and the wait inside
+ * the kernel is bounded too (reported by the same code).
+ */
+int flux_cuda_group_sample_cfg_pair(flux_cuda_group *g, const flux_cuda_sample_params *p, const float *z0,
+                                    float *latent_out);
+
+/* The rendezvous the pair's host threads use, on its own (plain host code, no GPU involved): `parties` threads call
+ * arrive_and_wait with the same growing sequence number; it returns once every other party has announced a number
+ * >= seq, or FLUX_CUDA_ERR_PEER_TIMEOUT after timeout_ms, or at once if a missing party has called abandon. */
+typedef struct flux_cuda_rendezvous flux_cuda_rendezvous;
+int flux_cuda_rendezvous_create(int parties, flux_cuda_rendezvous **out);
+void flux_cuda_rendezvous_destroy(flux_cuda_rendezvous *r);
+int flux_cuda_rendezvous_arrive_and_wait(flux_cuda_rendezvous *r, int party, long long seq, int timeout_ms);
+void flux_cuda_rendezvous_abandon(flux_cuda_rendezvous *r, int party);
 
 /* ------------------------------------------------------------------------------------------------
  * Host-side pieces of the sampler (plain C, no GPU involved).

@@ -1,0 +1,95 @@
+"""flux_cuda_group_*: several GPUs of one machine behind the C ABI, driven from one process. On a one-GPU box the
+group of one is checked against the single-context path and the pair call must refuse; with two or more GPUs the
+guidance pair split over two GPUs is checked against the batch-of-two path on one GPU and against the numpy oracle,
+and independent images are spread over the members."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+LATENT_TOL = 3e-2
+
+
+def rel(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+def _gpus():
+    import torch
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.fixture(scope="module")
+def tiny_group(fx):
+    import flux2_c_b200.synth as synth
+    n = min(_gpus(), 2)
+    if n < 1:
+        pytest.skip("no GPU")
+    d = synth.Dims.tiny()
+    W = synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08)
+    g = fx.Group(range(n))
+    models = [fx.Model.from_tensors(g.context(r), d, W) for r in range(n)]
+    g.set_models(models)
+    yield synth, d, W, g, models, n
+    for m in models:
+        m.close()
+    g.close()
+
+
+def test_group_batch_spreads_independent_images(tiny_group, fx):
+    synth, d, W, g, models, n = tiny_group
+    h, w, ntxt, steps = 6, 4, 24, 3
+    sch = fx.official_schedule(steps, h * w)
+    z0s = [fx.init_noise(d.latent_ch, h, w, i) for i in range(5)]
+    cs = [synth.make_context(10000 + i, ntxt, d.text_dim) for i in range(5)]
+    outs = g.sample_batch(z0s, cs, h, w, sch)
+    for i in range(5):  # whichever member ran image i, the result is the single-context one, bit for bit
+        assert np.array_equal(outs[i], models[0].sample(z0s[i], h, w, cs[i], sch))
+    assert not np.array_equal(outs[0], outs[1])
+    assert g.sample_batch([], [], h, w, sch) == []
+    r1 = [(synth.make_latent(4, d.latent_ch, 2, 4), 10)]
+    outs = g.sample_batch(z0s[:2], cs[:2], h, w, sch, refs=r1)
+    assert np.array_equal(outs[1], models[0].sample(z0s[1], h, w, cs[1], sch, refs=r1))
+
+
+def test_group_pair_needs_two_gpus_or_matches_batch_of_two(tiny_group, fx):
+    from oracle import flux_oracle as fo
+    synth, d, W, g, models, n = tiny_group
+    h, w, ntxt, steps, guidance = 6, 6, 48, 5, 4.0
+    z0 = fx.init_noise(d.latent_ch, h, w, 7)
+    cc = synth.make_context(41, ntxt, d.text_dim)
+    cu = synth.make_context(42, ntxt, d.text_dim)
+    sch = fx.official_schedule(steps, h * w)
+    if n < 2:
+        with pytest.raises(fx.FluxCudaError, match="two GPUs"):
+            g.sample_cfg_pair(z0, h, w, cc, cu, guidance, sch)
+        return
+    one_gpu = models[0].sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=guidance)
+    for _ in range(3):  # several images through the same group: the flags only grow, nothing is reset in between
+        pair = g.sample_cfg_pair(z0, h, w, cc, cu, guidance, sch)
+        assert rel(pair, one_gpu) < 2e-3  # same math; the batch of two rounds g (v_c - v_u) differently
+    want = fo.OracleModel(W, d).sample_euler_cfg(z0, h, w, cc, cu, guidance, sch)
+    assert rel(pair, want) < LATENT_TOL
+    r1 = [(synth.make_latent(4, d.latent_ch, 3, 4), 10)]
+    assert rel(g.sample_cfg_pair(z0, h, w, cc, cu, guidance, sch, refs=r1),
+               models[0].sample(z0, h, w, cc, sch, ctx_uncond=cu, guidance=guidance, refs=r1)) < 2e-3
+    # guidance 1 needs no partner's half at all, yet takes the same path: (1 - g) = 0 on the unconditional side
+    assert rel(g.sample_cfg_pair(z0, h, w, cc, cu, 1.0, sch), models[0].sample(z0, h, w, cc, sch)) < 1e-3
+
+
+def test_group_rejects_bad_arguments(tiny_group, fx):
+    synth, d, W, g, models, n = tiny_group
+    with pytest.raises(fx.FluxCudaError):
+        fx.Group([0, 0])
+    with pytest.raises(fx.FluxCudaError):
+        fx.Group([_gpus() + 3])
+    other = fx.Context(0)
+    try:
+        stray = fx.Model.from_tensors(other, d, W)
+        with pytest.raises(fx.FluxCudaError, match="not created from the group"):
+            g.set_models([stray] * n)
+        stray.close()
+    finally:
+        other.close()
+    g.set_models(models)
