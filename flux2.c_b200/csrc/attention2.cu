@@ -30,7 +30,10 @@
 
 namespace fx {
 
-static constexpr int ATT_THREADS = 320;
+static constexpr int ATT_THREADS = 384;
+static constexpr int REGS_LAUNCH = 160;   // a floor of what 384 threads per block get at launch (ptxas reports 168)
+static constexpr int REGS_ISSUE = 64;     // producer / MMA-issuer warp group after giving registers back
+static constexpr int REGS_SOFTMAX = 208;  // the two softmax warp groups after taking them
 static constexpr int TILE = 128;           // queries per tile, keys per step, head dim
 static constexpr int QTILES = 2;           // query tiles per CTA
 static constexpr int CHUNK_BYTES = 16384;  // 128 rows x 64 16-bit elements
@@ -96,6 +99,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     if (traced) P.trace[j * 16 + slot] = clock64();
   };
 
+  // Registers follow the work: the producer / issuer warp group gives registers back (64 per thread), the two
+  // softmax groups, which hold a row's 128 scores plus the packed probabilities, take 216. The reallocation sits at
+  // the top of each group's own branch, so that the compiler budgets each branch separately. The increase waits
+  // (in hardware, without a bound) until the block's pool holds enough registers, so the sum after reallocation
+  // must not exceed what the block was launched with - checked at compile time below.
+  static_assert(128 * REGS_ISSUE + 256 * REGS_SOFTMAX <= ATT_THREADS * REGS_LAUNCH,
+                "register reallocation asks for more than the block owns: setmaxnreg.inc would wait forever");
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_ISSUE));
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -126,67 +138,74 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
-      const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
-      const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (TMEM)   x V (MN-major)
-      auto issue_s = [&](int t, int j) {
-        const uint32_t sq = smem_u32(smem + OFF_Q + t * 32768);
-        const uint32_t sk = smem_u32(smem + OFF_KV + (j & 1) * 65536);
-        const uint32_t d = tmem + t * 128;
+    // All 32 lanes run this loop and one elected lane issues each instruction: the operand descriptors and TMEM
+    // addresses then stay warp-uniform values, which the compiler keeps in the uniform datapath the tcgen05
+    // instructions read their operands from. (With the whole role inside `if (lane == 0)` every descriptor had to be
+    // moved over from a per-thread register, and the issue of a 64-cycle MMA took ~100 cycles.)
+    const bool leader = elect_one();
+    const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
+    const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
+    const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (TMEM)   x V (MN-major)
+    const uint32_t smem_base = smem_u32(smem);
+    auto issue_s = [&](int t, int j) {
+      const uint32_t d = tmem + t * 128;
+      const uint32_t sq = smem_base + OFF_Q + t * 32768;
+      const uint32_t sk = smem_base + OFF_KV + (j & 1) * 65536;
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc) {
-          const uint64_t ad = make_smem_desc_sw128(sq + kc * CHUNK_BYTES, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(sk + kc * CHUNK_BYTES, 16, 1024);
+      for (int kc = 0; kc < 2; ++kc) {
+        const uint64_t ad = make_smem_desc_sw128(sq + kc * CHUNK_BYTES, 16, 1024);
+        const uint64_t bd = make_smem_desc_sw128(sk + kc * CHUNK_BYTES, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc_s, (kc | k) ? 1u : 0u);
-        }
-        tc_commit(&B->s_ready[t]);
-      };
-      bool ok = mbar_wait(&B->q_full, 0, abort_flag) && mbar_wait(&B->k_full[0], 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0, 0);
-        issue_s(1, 0);
+        for (int k = 0; k < 4; ++k)
+          if (leader) tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc_s, (kc | k) ? 1u : 0u);
       }
-      for (int j = 0; ok && j < T; ++j) {
-        const int st = j & 1;
-        ok = mbar_wait(&B->v_full[st], (j >> 1) & 1, abort_flag);
-        stamp(j, 0);
-        const uint32_t sv = smem_u32(smem + OFF_KV + st * 65536 + 32768);
-        for (int t = 0; ok && t < QTILES; ++t) {
-          ok = mbar_wait(&B->p_ready[t], j & 1, abort_flag);
-          if (!ok) break;
-          stamp(j, 1 + 2 * t);
-          tc_fence_after_sync();
-          // O_t (+)= P_t V: P_t sits in the first 64 columns of S_t, 16 keys = 8 columns per MMA
-          const uint32_t d = tmem + 256 + t * 128;
-          const uint32_t pa = tmem + t * 128;
+      if (leader) tc_commit(&B->s_ready[t]);
+    };
+    bool ok = mbar_wait_warp(&B->q_full, 0, abort_flag) && mbar_wait_warp(&B->k_full[0], 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      issue_s(0, 0);
+      issue_s(1, 0);
+    }
+    for (int j = 0; ok && j < T; ++j) {
+      const int st = j & 1;
+      ok = mbar_wait_warp(&B->v_full[st], (j >> 1) & 1, abort_flag);
+      if (leader) stamp(j, 0);
+      // V tile: rows = keys (128 B each, one 64-wide half of d per chunk); 16 keys (2048 B) per MMA
+      const uint64_t vd = make_smem_desc_sw128(smem_base + OFF_KV + st * 65536 + 32768, CHUNK_BYTES, 1024);
+      for (int t = 0; ok && t < QTILES; ++t) {
+        ok = mbar_wait_warp(&B->p_ready[t], j & 1, abort_flag);
+        if (!ok) break;
+        if (leader) stamp(j, 1 + 2 * t);
+        tc_fence_after_sync();
+        // O_t (+)= P_t V: P_t sits in the first 64 columns of S_t, 16 keys = 8 columns per MMA
+        const uint32_t d = tmem + 256 + t * 128;
+        const uint32_t pa = tmem + t * 128;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            // V tile: rows = keys (128 B each, one 64-wide half of d per chunk); 16 keys per MMA.
-            const uint64_t bd = make_smem_desc_sw128(sv + k * 16 * 128, CHUNK_BYTES, 1024);
-            tc_mma_ts(d, pa + k * 8, bd, idesc_o, (j | k) ? 1u : 0u);
-          }
+        for (int k = 0; k < 8; ++k)
+          if (leader) tc_mma_ts(d, pa + k * 8, vd + static_cast<uint64_t>(k) * (2048 >> 4), idesc_o, (j | k) ? 1u : 0u);
+        if (leader) {
           tc_commit(&B->o_done[t]);
           if (t == QTILES - 1) tc_commit(&B->kv_empty[st]);
-          if (j + 1 < T) {
-            if (t == 0) {
-              ok = mbar_wait(&B->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after_sync();
-            }
-            issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
-          }
-          stamp(j, 2 + 2 * t);
         }
+        if (j + 1 < T) {
+          if (t == 0) {
+            ok = mbar_wait_warp(&B->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
+        }
+        if (leader) stamp(j, 2 + 2 * t);
       }
-      if (!ok) fail();
     }
+    if (!ok && lane == 0) fail();
     __syncwarp();
+  }
   } else {
-    // ---------------------------------------------------------------- softmax + output (warps 2..9)
-    const int t = (warp - 2) >> 2;  // query tile
+    // ---------------------------------------------------------------- softmax + output (warps 4..11)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
+    const int t = (warp - 4) >> 2;  // query tile
     const int q = warp & 3;         // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;  // row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
@@ -202,7 +221,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     for (int j = 0; j < T; ++j) {
       ok = mbar_wait_warp(&B->s_ready[t], j & 1, abort_flag);
       if (!ok) break;
-      const bool tr = q == 2 && lane == 0;  // warps 2 and 6: the first warp of each tile
+      const bool tr = q == 0 && lane == 0;  // warps 4 and 8: the first warp of each tile
       if (tr) stamp(j, 5 + 5 * t);
       tc_fence_after_sync();
 #pragma unroll
@@ -229,12 +248,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= limit || !((mw[c] >> i) & 1u)) s[c][i] = __float_as_uint(-1e30f);
       }
-      float mloc = -1e30f;
+      // four independent chains for the maximum of the row's 128 scores (one chain would cost 128 dependent steps)
+      float m4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mloc = fmaxf(mloc, __uint_as_float(s[c][i]));
-      mloc *= scale;
+        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s[c][i]));
+      const float mloc = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale;
       // Raise the reference maximum only when this tile exceeds it by more than the threshold.
       const bool raise = mloc > m_ref + RESCALE_THRESHOLD;
       if (j == 0) {
@@ -262,7 +282,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
       }
       if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
-      float rowsum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[32];
@@ -272,12 +292,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
           for (int i = 0; i < 16; ++i) {
             const float p0 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i]), scale, -m_ref));
             const float p1 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i + 1]), scale, -m_ref));
-            rowsum += p0 + p1;
+            sum4[i & 3] += p0 + p1;
             pk[c * 16 + i] = pack_16x2(p0, p1, f16);
           }
         tc_st_32x32(s_addr + h * 32, pk);
       }
-      l += rowsum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();

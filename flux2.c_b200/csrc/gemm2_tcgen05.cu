@@ -125,9 +125,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (rank == 0 && lane == 0) {
+    // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and loop state are then
+    // warp-uniform values that stay in the uniform datapath the tcgen05 instructions take their operands from.
+    // (With the role inside `if (lane == 0)` each descriptor is a per-thread value that has to be moved across for
+    // every instruction; measured on the attention kernel that made the issue of one MMA cost ~100 cycles.)
+    if (rank == 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_bf16 = make_idesc_16(2 * P_BM, P_BN, FMT_BF16, FMT_BF16, 0, 0);
       constexpr uint32_t idesc_f16 = make_idesc_16(2 * P_BM, P_BN, FMT_F16, FMT_F16, 0, 0);
+      const uint32_t smem_base = smem_u32(smem);
       uint32_t kiter = 0, it = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < P.total_tiles; tile += num_pairs, ++it) {
@@ -136,8 +142,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
         const int KB = P.p[prob].K / P_BK;
         const uint32_t idesc = P.p[prob].x_f16 ? idesc_f16 : idesc_bf16;
         const int acc = it & 1;
-        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
-          fail(KERR_WAIT_TMEM_EMPTY);
+        if (!mbar_wait_warp(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          if (lane == 0) fail(KERR_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after_sync();
@@ -145,23 +151,25 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
         for (int kb = 0; kb < KB; ++kb, ++kiter) {
           const int s = kiter % P_STAGES;
           const uint32_t ph = (kiter / P_STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag)) {
-            fail(KERR_WAIT_FULL);
+          if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+            if (lane == 0) fail(KERR_WAIT_FULL);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (kiter == 0) stamp(2);
-          const uint32_t sa = smem_u32(smem + s * P_STAGE_BYTES);
+          if (kiter == 0 && leader) stamp(2);
+          const uint32_t sa = smem_base + s * P_STAGE_BYTES;
           const uint64_t ad = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sa + P_A_BYTES, 16, 1024);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < P_BK / 16; ++k) tc_mma_ss_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
-          tc_commit_pair(&empty[s], 3);  // frees the stage in both CTAs
+            for (int k = 0; k < P_BK / 16; ++k) tc_mma_ss_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(&empty[s], 3);  // frees the stage in both CTAs
+          }
         }
-        if (ok) tc_commit_pair(&tfull[acc], 3);
+        if (ok && leader) tc_commit_pair(&tfull[acc], 3);
       }
-      stamp(3);
+      if (leader) stamp(3);
     }
     __syncwarp();
   } else {
