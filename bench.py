@@ -355,6 +355,28 @@ def run_micro(args):
         emit({"micro": "gn", "pixels": side * side, "channels": C, "ms": ms, "gbs": algo / ms / 1e6,
                           "frac_of_hbm_peak": algo / ms / 1e6 / peaks["hbm_gbs"], "algorithmic_bytes": algo,
                           "peak_source": peaks["source"]})
+    elif args.micro == "step":
+        # Every kernel of the denoising loop at its real shape in a process that holds about 1.5 GB on the device (for
+        # profiler captures of the small kernels): a model with the klein-4B widths but ONE double-stream and ONE
+        # single-stream block, 512x512, 512 text tokens, 4 steps; --guidance 4 runs the guidance pair as a batch of two.
+        import numpy as np
+        synth = importlib.import_module("flux2_c_b200.synth")
+        dims = synth.Dims(n_double=1, n_single=1)
+        model = fx.Model.from_tensors(ctx, dims, synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count()))
+        guided = args.guidance != 1.0
+        sampler = fx.Sampler(model, H_LAT, W_LAT, TXT, batch=2 if guided else 1, max_steps=STEPS_PER_IMAGE)
+        z0 = torch.from_numpy(fx.init_noise(dims.latent_ch, H_LAT, W_LAT, 42)).pin_memory()
+        cc = torch.from_numpy(synth.make_context(1234, TXT, dims.text_dim)).pin_memory()
+        cu = torch.from_numpy(synth.make_context(4321, TXT, dims.text_dim)).pin_memory()
+        sched = fx.official_schedule(STEPS_PER_IMAGE, H_LAT * W_LAT)
+        sampler.upload(z0.data_ptr(), cc.data_ptr(), cu.data_ptr() if guided else None)
+        ms = timed(lambda: sampler.run(sched, guidance=args.guidance))
+        out = torch.zeros(z0.numel(), dtype=torch.float32).pin_memory()
+        sampler.download(out.data_ptr())
+        emit({"micro": "step", "blocks": [1, 1], "guided": guided, "ms_per_image": ms,
+              "launches": sampler.last_run()[1], "finite": bool(torch.isfinite(out).all())})
+        sampler.close()
+        model.close()
     elif args.micro == "load":
         # Load time of the klein-4B-shaped transformer file (7.75 GB, bf16) through the engine's safetensors loader:
         # map, validate, copy, convert bf16 -> f16 and re-lay on the device. The file sits in RAM-backed storage, so
@@ -433,7 +455,8 @@ def run_micro(args):
         # of --seq tokens through the host-buffer entry point: token ids in, [seq, 7680] f32 embeddings out.
         import numpy as np
         synth = importlib.import_module("flux2_c_b200.synth")
-        d = synth.QwenDims(layers=27)
+        d = synth.QwenDims(layers=27) if args.layers >= 27 else synth.QwenDims(
+            layers=args.layers, out_layers=(0, max(0, args.layers // 2), args.layers - 1))
         W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count())
         B = max(1, args.prompt_batch)
         enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=max(512, args.seq) * B)
@@ -449,9 +472,9 @@ def run_micro(args):
         dev_ms = timed(lambda: enc.forward_batch(ids, None, device=True)) / B
         qd, kd = d.heads * d.head_dim, d.kv_heads * d.head_dim
         per_layer = 2.0 * seq * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter) + 2.0 * seq * seq * qd
-        flops = 27 * per_layer
-        wbytes = 27 * 2.0 * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter)
-        emit({"micro": "qwen3", "seq": seq, "prompts_per_pass": B, "layers_run": 27, "ms_per_prompt_e2e": ms,
+        flops = d.layers * per_layer
+        wbytes = d.layers * 2.0 * (d.hidden * (qd + 2 * kd) + qd * d.hidden + 3 * d.hidden * d.inter)
+        emit({"micro": "qwen3", "seq": seq, "prompts_per_pass": B, "layers_run": d.layers, "ms_per_prompt_e2e": ms,
                           "ms_per_prompt_device": dev_ms, "model_tflops_device": flops / dev_ms / 1e9,
                           "model_tflops": flops / ms / 1e9, "weight_gb_per_pass": wbytes / 1e9,
                           "weight_stream_ms_at_hbm_peak": wbytes / peaks["hbm_gbs"] / 1e6,
@@ -624,6 +647,8 @@ def run_config(args):
     fx = load_package()
     import flux2_c_b200.synth as synth
     c = CONFIGS[args.config]
+    if args.group:
+        return run_config_group(args, fx, synth, c)
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -715,6 +740,48 @@ def run_config(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return 0
+
+
+def run_config_group(args, fx, synth, c):
+    """--config 3 --group: the guidance pair split over GPUs 0 and 1 through the C ABI's own group calls
+    (flux_cuda_group_sample_cfg_pair: one process, one internal host thread per GPU, peer-memory exchange), timed as a
+    host call with host buffers in and the latent out, against the same image as a batch of two on GPU 0."""
+    import numpy as np
+    import torch
+    if args.config != 3 or torch.cuda.device_count() < 2:
+        raise SystemExit("--group: configuration 3 on a box with at least two GPUs")
+    dims = synth.Dims.klein4b()
+    W = synth.make_transformer_weights(dims, seed=0, threads=os.cpu_count())
+    g = fx.Group([0, 1])
+    models = [fx.Model.from_tensors(g.context(r), dims, W) for r in range(2)]
+    del W
+    g.set_models(models)
+    h, w, steps, guidance = c["h"], c["w"], c["steps"], c["guidance"]
+    z0 = fx.init_noise(dims.latent_ch, h, w, 42)
+    cc = synth.make_context(1234, TXT, dims.text_dim)
+    cu = synth.make_context(4321, TXT, dims.text_dim)
+    sched = fx.official_schedule(steps, h * w)
+    pair = g.sample_cfg_pair(z0, h, w, cc, cu, guidance, sched)  # warm-up, and the result to compare
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        pair = g.sample_cfg_pair(z0, h, w, cc, cu, guidance, sched)
+    pair_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    one = models[0].sample(z0, h, w, cc, sched, ctx_uncond=cu, guidance=guidance)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one = models[0].sample(z0, h, w, cc, sched, ctx_uncond=cu, guidance=guidance)
+    one_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    err = float(np.linalg.norm(pair.astype(np.float64) - one) / np.linalg.norm(one.astype(np.float64)))
+    emit({"config": 3, "workload": "klein4b_base_512x512_50step_cfg4_pair_split_across_2_gpus_c_abi_group",
+          "value": 1e3 / pair_ms, "unit": "images/s", "n_gpus": 2, "ms_per_image": pair_ms,
+          "ms_per_dit_step": pair_ms / steps, "one_gpu_batch_of_two_ms_per_image": one_ms,
+          "speedup_over_one_gpu": one_ms / pair_ms, "rel_l2_against_one_gpu": err, "images_timed": args.steps,
+          "timing": "host wall clock around the call: host buffers in, latent out", "dtype": "f16",
+          "data": "synthetic"})
+    for m in models:
+        m.close()
+    g.close()
     return 0
 
 
@@ -977,15 +1044,18 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load", "step"])
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--epi", default="store", choices=["store", "qkv", "gated", "f32"], help="epilogue of --micro gemm")
     ap.add_argument("--trace", action="store_true", help="--micro gemm --tile-n 512: timeline of the first CTA")
     ap.add_argument("--seq", type=int, default=1536)
+    ap.add_argument("--guidance", type=float, default=1.0, help="--micro step: 4 runs the guidance pair (batch of two)")
+    ap.add_argument("--layers", type=int, default=27, help="--micro qwen3: encoder layers to build and run")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--size", type=int, default=512, help="image side for --micro vae")
     ap.add_argument("--config", type=int, default=2, help="1, 3 or 4: another configuration of the workload list")
+    ap.add_argument("--group", action="store_true", help="--config 3: the pair through flux_cuda_group_* in one process")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-text-encoder", action="store_true", help="skip the prompt -> latent leg")
     ap.add_argument("--prompt-batch", type=int, default=4, help="prompts encoded per text-encoder pass")

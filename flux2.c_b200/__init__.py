@@ -10,7 +10,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflux_cuda.so")
+# FLUX_CUDA_LIBRARY selects another build of the same library, e.g. the checked one (libflux_cuda_debug.so)
+LIB_PATH = os.environ.get("FLUX_CUDA_LIBRARY") or os.path.join(_HERE, "libflux_cuda.so")
 
 EPI_STORE_BF16, EPI_STORE_F32, EPI_GATED_RES_F32, EPI_SWIGLU_BF16, EPI_STORE_F32_T = range(5)
 EPI_X_F16, EPI_OUT_F16 = 0x100, 0x200  # or-ed into the epilogue: f16 activations in / out
@@ -38,6 +39,8 @@ def _declare(L):
     c_void_p, c_int, c_ll, c_char_p = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_char_p
     L.flux_cuda_last_error.restype = c_char_p
     L.flux_cuda_last_error.argtypes = []
+    L.flux_cuda_build_checked.restype = c_int
+    L.flux_cuda_build_checked.argtypes = []
     L.flux_cuda_ctx_create.restype = c_int
     L.flux_cuda_ctx_create.argtypes = [c_int, ctypes.POINTER(c_void_p)]
     L.flux_cuda_ctx_destroy.restype = None

@@ -47,6 +47,10 @@ int ctx_sync_check(flux_cuda_ctx *ctx) {
   if (ctx->err_host[0] != 0) {
     const int code = ctx->err_host[0];
     cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), ctx->stream);
+    if (code == 8) {  // KERR_BAD_INDEX
+      set_error("checked build: a kernel computed an address outside its buffer or off its alignment and skipped it");
+      return FLUX_CUDA_ERR_KERNEL;
+    }
     if (code == 9) {  // KERR_PEER_TIMEOUT
       set_error("the other GPU of the pair did not deliver its half of a step within the kernel's wait limit");
       return FLUX_CUDA_ERR_PEER_TIMEOUT;
@@ -63,6 +67,14 @@ using namespace fx;
 extern "C" {
 
 const char *flux_cuda_last_error(void) { return g_err; }
+
+int flux_cuda_build_checked(void) {
+#ifdef FLUX_CUDA_DEBUG
+  return 1;
+#else
+  return 0;
+#endif
+}
 
 int flux_cuda_ctx_create(int device, flux_cuda_ctx **out) {
   if (!out) return FLUX_CUDA_ERR_ARG;
@@ -203,7 +215,10 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   }
   GemmParams P;
   memset(&P, 0, sizeof(P));
-  int rc = gemm_make_problem(&P.p[0], x, K, w, M, 3 * hidden, K, 256);
+  // the kernel the engine itself uses for this projection: CTA pairs unless the context was told otherwise
+  const bool pair = ctx->gemm_pair && (3 * hidden) % 256 == 0;
+  int rc = pair ? gemm_make_problem_pair(&P.p[0], x, K, w, M, 3 * hidden, K)
+                : gemm_make_problem(&P.p[0], x, K, w, M, 3 * hidden, K, 256);
   if (rc) {
     set_error("gemm_qkv_norm_rope: unsupported shape/alignment M=%d hidden=%d K=%d (rc %d)", M, hidden, K, rc);
     return FLUX_CUDA_ERR_ARG;
@@ -224,7 +239,7 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   sg.qk.q_cols = hidden;
   sg.qk.k_cols = hidden;
   sg.qk.half_split = 0;
-  rc = gemm_launch(&P, 256, ctx->num_sms, ctx->stream);
+  rc = pair ? gemm2_launch(&P, ctx->num_sms, ctx->stream) : gemm_launch(&P, 256, ctx->num_sms, ctx->stream);
   if (rc) {
     set_error("gemm_qkv_norm_rope: launch failed (rc %d)", rc);
     return FLUX_CUDA_ERR_CUDA;

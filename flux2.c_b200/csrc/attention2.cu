@@ -68,6 +68,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
     if (t_causal < T) T = t_causal;
   }
   const int kv_head = P.kv_group > 1 ? head / P.kv_group : head;
+#ifdef FLUX_CUDA_DEBUG
+  // Checked build: every TMA coordinate of this CTA must start on a 16-byte boundary and inside the row; otherwise
+  // the CTA records the fact and leaves before anything is loaded.
+  if (((P.q_col + head * 128) | (P.k_col + kv_head * 128) | (P.v_col + kv_head * 128) | P.out_col) & 7 || q0 < 0 ||
+      q0 >= P.seq + QTILES * TILE || T < 1) {
+    if (threadIdx.x == 0) atomicCAS(P.err, 0, KERR_BAD_INDEX);
+    return;
+  }
+#endif
 
   if (threadIdx.x == 0) {
     mbar_init(&B->q_full, 1);

@@ -110,6 +110,10 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
     *abort_flag = 1;
     atomicCAS(P.err, 0, KERR_WAIT_ATTN);
   };
+  const bool traced = P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int j, int slot) {
+    if (traced) P.trace[j * 16 + slot] = clock64();
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -145,61 +149,67 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
-      const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
-      const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (TMEM)   x V (MN-major)
-      auto issue_s = [&](int t, int j) {
-        const uint32_t sq = smem_u32(smem + OFF_Q + t * 32768);
-        const uint32_t sk = smem_u32(smem + OFF_K + (j & 1) * 32768);
-        const uint32_t d = tmem + t * 128;
+    // all 32 lanes run the loop, one elected lane issues (see gemm2_tcgen05.cu): descriptors stay warp-uniform
+    const bool leader = elect_one();
+    const uint32_t fmt = P.f16 ? FMT_F16 : FMT_BF16;
+    const uint32_t idesc_s = make_idesc_16(128, 128, fmt, fmt, 0, 0);  // Q (K-major) x K (K-major)
+    const uint32_t idesc_o = make_idesc_16(128, 128, fmt, fmt, 0, 1);  // P (TMEM)   x V (MN-major)
+    const uint32_t smem_base = smem_u32(smem);
+    auto issue_s = [&](int t, int j) {
+      const uint32_t sq = smem_base + OFF_Q + t * 32768;
+      const uint32_t sk = smem_base + OFF_K + (j & 1) * 32768;
+      const uint32_t d = tmem + t * 128;
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc) {
-          const uint64_t ad = make_smem_desc_sw128(sq + kc * CHUNK_BYTES, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(sk + kc * CHUNK_BYTES, 16, 1024);
+      for (int kc = 0; kc < 2; ++kc) {
+        const uint64_t ad = make_smem_desc_sw128(sq + kc * CHUNK_BYTES, 16, 1024);
+        const uint64_t bd = make_smem_desc_sw128(sk + kc * CHUNK_BYTES, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc_s, (kc | k) ? 1u : 0u);
-        }
+        for (int k = 0; k < 4; ++k)
+          if (leader) tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc_s, (kc | k) ? 1u : 0u);
+      }
+      if (leader) {
         tc_commit(&B->s_ready[t]);
         if (t == QTILES - 1) tc_commit(&B->k_empty[j & 1]);  // both tiles have read this K tile
-      };
-      bool ok = mbar_wait(&B->q_full, 0, abort_flag) && mbar_wait(&B->k_full[0], 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0, 0);
-        issue_s(1, 0);
       }
-      for (int j = 0; ok && j < T; ++j) {
-        const int st = j & 1;
-        ok = mbar_wait(&B->v_full[st], (j >> 1) & 1, abort_flag);
-        const uint32_t sv = smem_u32(smem + OFF_V + st * 32768);
-        for (int t = 0; ok && t < QTILES; ++t) {
-          ok = mbar_wait(&B->p_ready[t], j & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          // O_t (+)= P_t V: P_t sits in the first 64 columns of S_t, 16 keys = 8 columns per MMA
-          const uint32_t d = tmem + 256 + t * 128;
-          const uint32_t pa = tmem + t * 128;
+    };
+    bool ok = mbar_wait_warp(&B->q_full, 0, abort_flag) && mbar_wait_warp(&B->k_full[0], 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      issue_s(0, 0);
+      issue_s(1, 0);
+    }
+    for (int j = 0; ok && j < T; ++j) {
+      const int st = j & 1;
+      ok = mbar_wait_warp(&B->v_full[st], (j >> 1) & 1, abort_flag);
+      if (leader) stamp(j, 0);
+      // V tile: rows = keys (128 B each, one 64-wide half of d per chunk); 16 keys (2048 B) per MMA
+      const uint64_t vd = make_smem_desc_sw128(smem_base + OFF_V + st * 32768, CHUNK_BYTES, 1024);
+      for (int t = 0; ok && t < QTILES; ++t) {
+        ok = mbar_wait_warp(&B->p_ready[t], j & 1, abort_flag);
+        if (!ok) break;
+        if (leader) stamp(j, 1 + 2 * t);
+        tc_fence_after_sync();
+        const uint32_t d = tmem + 256 + t * 128;
+        const uint32_t pa = tmem + t * 128;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            // V tile: rows = keys (128 B each, one 64-wide half of d per chunk); 16 keys per MMA.
-            const uint64_t bd = make_smem_desc_sw128(sv + k * 16 * 128, CHUNK_BYTES, 1024);
-            tc_mma_ts(d, pa + k * 8, bd, idesc_o, (j | k) ? 1u : 0u);
-          }
+        for (int k = 0; k < 8; ++k)
+          if (leader) tc_mma_ts(d, pa + k * 8, vd + static_cast<uint64_t>(k) * (2048 >> 4), idesc_o, (j | k) ? 1u : 0u);
+        if (leader) {
           tc_commit(&B->o_done[t]);
           if (t == QTILES - 1) tc_commit(&B->v_empty[st]);
-          if (j + 1 < T) {
-            if (t == 0) {
-              ok = mbar_wait(&B->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after_sync();
-            }
-            issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
-          }
         }
+        if (j + 1 < T) {
+          if (t == 0) {
+            ok = mbar_wait_warp(&B->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          issue_s(t, j + 1);  // overwrites P_t(j): issued after P_t V(j), executed after it
+        }
+        if (leader) stamp(j, 2 + 2 * t);
       }
-      if (!ok) fail();
     }
+    if (!ok && lane == 0) fail();
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax + output (warps 2..17)
@@ -244,10 +254,13 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
     for (int j = 0; j < T; ++j) {
       ok = mbar_wait_warp(&B->s_ready[t], j & 1, abort_flag);
       if (!ok) break;
+      const bool tr = (sw & 7) == 0 && lane == 0;  // the first warp of each tile
+      if (tr) stamp(j, 5 + 5 * t);
       tc_fence_after_sync();
       tc_ld_32x32(s_addr, s[0]);
       tc_ld_32x32(s_addr + 32, s[1]);
       tc_wait_ld();
+      if (tr) stamp(j, 6 + 5 * t);
       // keys of this tile this row may see: inside the sequence, not after the query (causal), not masked out
       int limit = P.seq - j * TILE;
       if (P.causal) {
@@ -306,6 +319,7 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
           m_ref = mloc;
         }
       }
+      if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs: keys 2c, 2c+1 of the tile in column c of S
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -321,10 +335,12 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
         tc_st_32x16(p_addr + c * 16, pk);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&B->p_ready[t]);
+      if (tr) stamp(j, 9 + 5 * t);
     }
     if (ok) {
       l += exchange(l, T + 1, ok);  // the row's sum over all keys

@@ -264,16 +264,19 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (rank == 0 && lane == 0) {
+    // the whole warp runs the loop, one elected lane issues (see gemm2_tcgen05.cu): descriptors stay warp-uniform
+    if (rank == 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_bf16 = make_idesc_16(2 * C_BM, BN, FMT_BF16, FMT_BF16, 0, 0);
       constexpr uint32_t idesc_f16 = make_idesc_16(2 * C_BM, BN, FMT_F16, FMT_F16, 0, 0);
       const uint32_t idesc = P.x_f16 ? idesc_f16 : idesc_bf16;
+      const uint32_t smem_base = smem_u32(smem);
       uint32_t kiter = 0, it = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++it) {
         const int acc = it & 1;
-        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
-          fail(KERR_WAIT_TMEM_EMPTY);
+        if (!mbar_wait_warp(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          if (lane == 0) fail(KERR_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after_sync();
@@ -281,20 +284,22 @@ __global__ void __launch_bounds__(C_THREADS, 1) conv2_tn_kernel(const __grid_con
         for (int kb = 0; kb < KB; ++kb, ++kiter) {
           const int s = kiter % C_STAGES;
           const uint32_t ph = (kiter / C_STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag)) {
-            fail(KERR_WAIT_FULL);
+          if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+            if (lane == 0) fail(KERR_WAIT_FULL);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
           const uint64_t ad = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sa + Cfg::A_BYTES, 16, 1024);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < C_BK / 16; ++k) tc_mma_ss_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
-          tc_commit_pair(&empty[s], 3);
+            for (int k = 0; k < C_BK / 16; ++k) tc_mma_ss_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(&empty[s], 3);
+          }
         }
-        if (ok) tc_commit_pair(&tfull[acc], 3);
+        if (ok && leader) tc_commit_pair(&tfull[acc], 3);
       }
     }
     __syncwarp();

@@ -28,6 +28,12 @@ __global__ void __launch_bounds__(128, 3) adaln_kernel(const float *__restrict__
   const int lane = threadIdx.x & 31;
   if (local >= rows) return;
   const int row = row0 + local;
+#ifdef FLUX_CUDA_DEBUG
+  if (row < 0 || seq <= 0 || hidden != VPL * 128 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15)) {
+    if (sat != nullptr && lane == 0) atomicCAS(sat - 1, 0, KERR_BAD_INDEX);  // checked build: record and skip
+    return;
+  }
+#endif
   const bool is_txt = (row % seq) < n_txt;  // position inside the [txt ; img ; refs] sequence picks the stream
   const float *shift = is_txt ? shift_txt : shift_img;
   const float *scale = is_txt ? scale_txt : scale_img;

@@ -230,18 +230,30 @@ int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
     P->tile_end[i] = acc;
   }
   P->total_tiles = acc;
-  // f32 outputs leave through the TMA unit when the destination allows it (16-byte aligned base and pitch);
-  // FLUX_CUDA_EPI_TMA=0 keeps the direct global stores (for comparisons)
-  static const bool tma_epilogue = !(getenv("FLUX_CUDA_EPI_TMA") && atoi(getenv("FLUX_CUDA_EPI_TMA")) == 0);
+  // Outputs leave through the TMA unit when the destination allows it (16-byte aligned base and pitch). For
+  // comparisons: FLUX_CUDA_EPI_TMA=0 keeps the direct global stores everywhere, =1 uses the TMA unit for the f32
+  // outputs only.
+  static const int tma_level = getenv("FLUX_CUDA_EPI_TMA") ? atoi(getenv("FLUX_CUDA_EPI_TMA")) : 2;
+  const bool tma_epilogue = tma_level >= 1;
   for (int i = 0; i < P->nprob; ++i) {
     GemmProblem &pb = P->p[i];
     for (int sgi = 0; sgi < 2; ++sgi) {
       EpiSeg &sg = pb.seg[sgi];
       sg.tma_out = 0;
       const int width = sgi == 0 ? pb.n_split : pb.N - pb.n_split;
-      if (!tma_epilogue || width <= 0 || !sg.out || (sg.mode != EPI_STORE_F32 && sg.mode != EPI_GATED_RES_F32) || (sg.col0 & 3)) continue;
-      if (make_tmap_2d_f32(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + width, sg.ld, 32, 32) == 0)
-        sg.tma_out = 1;
+      if (!tma_epilogue || width <= 0 || !sg.out) continue;
+      if (sg.mode == EPI_STORE_F32 || sg.mode == EPI_GATED_RES_F32) {
+        if (!(sg.col0 & 3) &&
+            make_tmap_2d_f32(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + width, sg.ld, 32, 32) == 0)
+          sg.tma_out = 1;
+      } else if (tma_level >= 2 && (sg.mode == EPI_STORE_BF16 || sg.mode == EPI_SWIGLU_BF16 ||
+                                    (sg.mode == EPI_QKV_NORM_ROPE && !sg.qk.half_split))) {
+        // 16-bit outputs: blocks of 32 rows x 64 columns (SwiGLU writes half as many columns as it computes)
+        const int out_cols = sg.mode == EPI_SWIGLU_BF16 ? width / 2 : width;
+        if (!(sg.col0 & 7) && make_tmap_2d_bf16(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + out_cols,
+                                                sg.ld, 32, 64) == 0)
+          sg.tma_out = 1;
+      }
     }
   }
   int pairs = num_sms / 2;

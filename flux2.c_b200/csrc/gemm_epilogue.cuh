@@ -34,6 +34,45 @@ __device__ __forceinline__ void stage_and_store_chunk(const CUtensorMap *tm, uin
   }
 }
 
+// 16-bit outputs through the TMA unit: a staging block holds 32 rows x 64 columns (128 bytes per row), i.e. two
+// 32-column chunks of the accumulator. Chunks are written four 16-byte pieces at a time; the two blocks of a warp
+// alternate so that one is being filled while the TMA unit still reads the other.
+__device__ __forceinline__ void stage_pieces4(uint8_t *buf, int lane, const uint32_t (&w)[16], int piece0) {
+  const uint32_t base = smem_u32(buf) + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t a = base + static_cast<uint32_t>(((piece0 + j) ^ (lane & 7)) * 16);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(w[4 * j]), "r"(w[4 * j + 1]),
+                 "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                 : "memory");
+  }
+}
+struct Stage16 {
+  uint8_t *stage;
+  int lane;
+  int n;  // blocks handed to the TMA unit so far
+  __device__ __forceinline__ uint8_t *acquire() {
+    if (n >= 2) {  // the store that last used this block has read it
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+    }
+    return stage + (n & 1) * 4096;
+  }
+  __device__ __forceinline__ void release(const CUtensorMap *tm, uint8_t *buf, int x, int y, bool issue) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && issue) {
+      tma_store_2d(tm, buf, x, y);
+      bulk_commit();
+    }
+    ++n;
+  }
+  __device__ __forceinline__ void drain() {  // before anything else writes the blocks again
+    if (lane == 0) bulk_wait_read<0>();
+    __syncwarp();
+  }
+};
+
 // stage: this warp's staging blocks (paired kernel) or nullptr (direct global stores).
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row,
@@ -46,9 +85,48 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
   const bool f16 = sg.out_f16 != 0;
   float mx = 0.f;  // largest magnitude this thread converted to 16 bits (f16 stores saturate at 65504)
   uint32_t r[32];
+#ifdef FLUX_CUDA_DEBUG
+  {
+    // Checked build: the tile must lie inside the problem and this row's destination inside the row pitch and on a
+    // 16-byte boundary. A violation is recorded in the error word and the tile is skipped - nothing is accessed.
+    const int width = sg.mode == EPI_SWIGLU_BF16 ? BN / 2 : BN;
+    const int first = sg.mode == EPI_SWIGLU_BF16 ? sg.col0 + nrel / 2 : sg.col0 + nrel;
+    const int esz = (sg.mode == EPI_STORE_BF16 || sg.mode == EPI_SWIGLU_BF16 || sg.mode == EPI_QKV_NORM_ROPE) ? 2 : 4;
+    bool bad = m0 < 0 || n0 < 0 || n0 + BN > pb.N || m0 >= pb.M + 128 || nrel < 0 || sg.out == nullptr;
+    if (sg.mode != EPI_STORE_F32_T) {
+      bad = bad || first < 0 || static_cast<long long>(first) + width > sg.ld ||
+            ((reinterpret_cast<uintptr_t>(sg.out) + (static_cast<size_t>(row_ok ? row : 0) * sg.ld + first) * esz) & 15);
+    } else {
+      bad = bad || sg.ld < pb.M;
+    }
+    if (bad) {
+      if (sat_counter != nullptr) atomicCAS(sat_counter - 1, 0, KERR_BAD_INDEX);
+      return;
+    }
+  }
+#endif
 
   switch (sg.mode) {
     case EPI_STORE_BF16: {
+      if (stage != nullptr && sg.tma_out) {
+        const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+        Stage16 st{stage, lane, 0};
+        uint8_t *buf = nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tc_ld_32x32(taddr + c * 32, r);
+          if ((c & 1) == 0) buf = st.acquire();
+          tc_wait_ld();
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            w[j] = pack_16x2_t(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), f16, mx);
+          stage_pieces4(buf, lane, w, (c & 1) * 4);
+          if (c & 1) st.release(&sg.tm_out, buf, sg.col0 + nrel + (c - 1) * 32, y, y < pb.M);
+        }
+        st.drain();
+        break;
+      }
       __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -154,9 +232,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
     } break;
     case EPI_SWIGLU_BF16: {
       if constexpr (BN == 256) {
+        uint32_t u[32];
+        if (stage != nullptr && sg.tma_out) {
+          const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+          Stage16 st{stage, lane, 0};
+          uint8_t *buf = nullptr;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tc_ld_32x32(taddr + c * 32, r);
+            tc_ld_32x32(taddr + 128 + c * 32, u);
+            if ((c & 1) == 0) buf = st.acquire();
+            tc_wait_ld();
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              w[j] = pack_16x2_t(silu_f(__uint_as_float(r[2 * j])) * __uint_as_float(u[2 * j]),
+                                 silu_f(__uint_as_float(r[2 * j + 1])) * __uint_as_float(u[2 * j + 1]), f16, mx);
+            stage_pieces4(buf, lane, w, (c & 1) * 4);
+            if (c & 1) st.release(&sg.tm_out, buf, sg.col0 + nrel / 2 + (c - 1) * 32, y, y < pb.M);
+          }
+          st.drain();
+          break;
+        }
         __nv_bfloat16 *dst =
             reinterpret_cast<__nv_bfloat16 *>(sg.out) + static_cast<size_t>(row) * sg.ld + sg.col0 + nrel / 2;
-        uint32_t u[32];
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           tc_ld_32x32(taddr + c * 32, r);
@@ -254,6 +353,43 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
               }
             }
           }
+          continue;
+        }
+        if (stage != nullptr && sg.tma_out) {
+          const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+          Stage16 st{stage, lane, 0};
+          uint8_t *buf = nullptr;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tc_ld_32x32(th + c * 32, r);
+            if ((c & 1) == 0) buf = st.acquire();
+            tc_wait_ld();
+            uint32_t wv[16];
+            if (rotate) {
+              const float4 *w4 = reinterpret_cast<const float4 *>(w + c * 32);
+              const float4 *c4 = reinterpret_cast<const float4 *>(qk.cos_t + static_cast<size_t>(pos) * 128 + c * 32);
+              const float4 *s4 = reinterpret_cast<const float4 *>(qk.sin_t + static_cast<size_t>(pos) * 128 + c * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 ww = __ldg(w4 + j);
+                const float4 cc = __ldg(c4 + j);
+                const float4 sn = __ldg(s4 + j);
+                const float x0 = __uint_as_float(r[4 * j + 0]) * rinv * ww.x;
+                const float x1 = __uint_as_float(r[4 * j + 1]) * rinv * ww.y;
+                const float x2 = __uint_as_float(r[4 * j + 2]) * rinv * ww.z;
+                const float x3 = __uint_as_float(r[4 * j + 3]) * rinv * ww.w;
+                wv[2 * j + 0] = pack_16x2_t(x0 * cc.x - x1 * sn.x, x1 * cc.x + x0 * sn.x, f16, mx);
+                wv[2 * j + 1] = pack_16x2_t(x2 * cc.z - x3 * sn.z, x3 * cc.z + x2 * sn.z, f16, mx);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                wv[j] = pack_16x2_t(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), f16, mx);
+            }
+            stage_pieces4(buf, lane, wv, (c & 1) * 4);
+            if (c & 1) st.release(&sg.tm_out, buf, sg.col0 + nrel + hd * 128 + (c - 1) * 32, y, y < pb.M);
+          }
+          st.drain();
           continue;
         }
 #pragma unroll 1

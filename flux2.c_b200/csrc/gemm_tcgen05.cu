@@ -124,7 +124,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // the whole warp runs the loop, one elected lane issues (see gemm2_tcgen05.cu): descriptors stay warp-uniform
+    {
+      const bool leader = elect_one();
+      const uint32_t smem_base = smem_u32(smem);
       constexpr uint32_t idesc_bf16 = make_idesc_16(BM, BN, FMT_BF16, FMT_BF16, 0, 0);
       constexpr uint32_t idesc_f16 = make_idesc_16(BM, BN, FMT_F16, FMT_F16, 0, 0);
       uint32_t kiter = 0, it = 0;
@@ -135,8 +138,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
         const int KB = P.p[prob].K / BK;
         const uint32_t idesc = P.p[prob].x_f16 ? idesc_f16 : idesc_bf16;
         const int acc = it & 1;
-        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
-          fail(KERR_WAIT_TMEM_EMPTY);
+        if (!mbar_wait_warp(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          if (lane == 0) fail(KERR_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after_sync();
@@ -144,21 +147,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tn_kernel(const __g
         for (int kb = 0; kb < KB; ++kb, ++kiter) {
           const int s = kiter % STAGES;
           const uint32_t ph = (kiter / STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag)) {
-            fail(KERR_WAIT_FULL);
+          if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+            if (lane == 0) fail(KERR_WAIT_FULL);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
           const uint64_t ad = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sa + Cfg::A_BYTES, 16, 1024);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // +32 bytes per K=16 slice inside the 128-byte swizzle row
-            tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
-          tc_commit(&empty[s]);
+            for (int k = 0; k < BK / 16; ++k)  // +32 bytes per K=16 slice inside the 128-byte swizzle row
+              tc_mma_ss(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit(&empty[s]);
+          }
         }
-        if (ok) tc_commit(&tfull[acc]);
+        if (ok && leader) tc_commit(&tfull[acc]);
       }
     }
     __syncwarp();

@@ -28,6 +28,11 @@ extern "C" {
 typedef struct flux_cuda_ctx flux_cuda_ctx;
 
 const char *flux_cuda_last_error(void);
+/* 1 for the checked build of the library (compiled with -DFLUX_CUDA_DEBUG: libflux_cuda_debug.so), whose kernels verify
+ * the tile, row and alignment arithmetic of what they are about to access and, on a violation, record it in the
+ * context's error word (reported as FLUX_CUDA_ERR_KERNEL by the next synchronising call) and skip the access - they
+ * never trap. 0 for the normal build. The reference's counterpart is its -fsanitize=address debug target. */
+int flux_cuda_build_checked(void);
 
 /* One context per GPU: creates the stream all work of this context is issued on. */
 int flux_cuda_ctx_create(int device, flux_cuda_ctx **out);

@@ -2,6 +2,8 @@
 group of one is checked against the single-context path and the pair call must refuse; with two or more GPUs the
 guidance pair split over two GPUs is checked against the batch-of-two path on one GPU and against the numpy oracle,
 and independent images are spread over the members."""
+import os
+
 import numpy as np
 import pytest
 
@@ -93,3 +95,52 @@ def test_group_rejects_bad_arguments(tiny_group, fx):
     finally:
         other.close()
     g.set_models(models)
+
+
+_SEAM_PAIR_SCRIPT = r"""
+import os, sys
+import numpy as np
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+from conftest import load_package
+fx = load_package()
+import flux2_c_b200.synth as synth
+from oracle import ref_binding as rb
+seam = rb.RefLib("seam")
+d = synth.Dims.tiny()
+tf = seam.load_transformer(sys.argv[2])
+h, w = 6, 4
+z = synth.make_latent(1, d.latent_ch, h, w)
+c = synth.make_context(2, 24, d.text_dim)
+cu = synth.make_context(3, 24, d.text_dim)
+sch = fx.official_schedule(4, h * w)
+out = tf.sample_euler_cfg(z, h, w, c, cu, 3.0, sch)
+plain = tf.sample_euler(z, h, w, c, sch)
+np.savez(sys.argv[3], cfg=out, plain=plain)
+tf.close()
+"""
+
+
+def test_seam_splits_guided_sampling_over_two_gpus(fx, tmp_path):
+    """FLUX_CUDA_DEVICES=0,1 makes the reference's flux_sample_euler_cfg (served by the seam) run its two passes on two
+    GPUs; the result must be the one the same call gives on one GPU, and unguided sampling is unaffected."""
+    import subprocess
+    import sys
+    import flux2_c_b200.synth as synth
+    from oracle import ref_binding as rb
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    if not rb.available("seam"):
+        pytest.skip("oracle/_ref/libflux_seam.so is not built")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d = synth.Dims.tiny()
+    wpath = str(tmp_path / "tiny.safetensors")
+    synth.write_safetensors(wpath, synth.make_transformer_weights(d, seed=3, sharp=True, std=0.08))
+    outs = {}
+    for tag, env in (("one", {}), ("two", {"FLUX_CUDA_DEVICES": "0,1"})):
+        out = str(tmp_path / (tag + ".npz"))
+        r = subprocess.run([sys.executable, "-c", _SEAM_PAIR_SCRIPT, root, wpath, out], capture_output=True, text=True,
+                           env=dict(os.environ, **env), timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        outs[tag] = np.load(out)
+    assert rel(outs["two"]["cfg"], outs["one"]["cfg"]) < 2e-3
+    assert np.array_equal(outs["two"]["plain"], outs["one"]["plain"])
