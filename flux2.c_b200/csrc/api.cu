@@ -130,6 +130,7 @@ void flux_cuda_ctx_destroy(flux_cuda_ctx *ctx) {
   if (ctx->err_dev) cudaFree(ctx->err_dev);
   if (ctx->err_host) cudaFreeHost(ctx->err_host);
   if (ctx->gn_scratch) cudaFree(ctx->gn_scratch);
+  if (ctx->rope_scratch) cudaFree(ctx->rope_scratch);
   delete ctx;
 }
 
@@ -235,6 +236,24 @@ int flux_cuda_gemm_qkv_norm_rope(flux_cuda_ctx *ctx, const void *x, const void *
   sg.qk.wk_txt = sg.qk.wk_img = wk;
   sg.qk.cos_t = cos_t;
   sg.qk.sin_t = sin_t;
+  {
+    // the engine hands the epilogue pair angles instead of the two tables; derive them here so that this entry point
+    // runs the epilogue the way the engine does
+    const size_t pairs = static_cast<size_t>(seq) * 64;
+    if (ctx->rope_scratch_floats < pairs) {
+      cudaStreamSynchronize(ctx->stream);
+      if (ctx->rope_scratch) cudaFree(ctx->rope_scratch);
+      ctx->rope_scratch = nullptr;
+      ctx->rope_scratch_floats = 0;
+      if (check_cuda(cudaMalloc(&ctx->rope_scratch, pairs * sizeof(float)), "cudaMalloc")) return FLUX_CUDA_ERR_NOMEM;
+      ctx->rope_scratch_floats = pairs;
+    }
+    if (launch_rope_angles(cos_t, sin_t, ctx->rope_scratch, static_cast<long long>(pairs), ctx->stream)) {
+      set_error("gemm_qkv_norm_rope: angle table launch failed");
+      return FLUX_CUDA_ERR_CUDA;
+    }
+    sg.qk.ang = ctx->rope_scratch;
+  }
   sg.qk.seq = seq;
   sg.qk.q_cols = hidden;
   sg.qk.k_cols = hidden;

@@ -16,6 +16,8 @@ struct flux_cuda_ctx {
   int attn_version = 2;           // 2: attention2.cu (default), 3: attention3.cu (FLUX_CUDA_ATTN=3, measured slower)
   bool gemm_pair = true;          // 256-wide GEMM tiles computed by CTA pairs (tcgen05 cta_group::2)
   float *gn_scratch = nullptr;    // lazily allocated scratch of the kernel-level GroupNorm entry point
+  float *rope_scratch = nullptr;  // lazily allocated pair-angle table of flux_cuda_gemm_qkv_norm_rope
+  size_t rope_scratch_floats = 0;
   long long *gemm_trace = nullptr;  // device buffer for the paired GEMM's timeline stamps (measurements only)
 };
 

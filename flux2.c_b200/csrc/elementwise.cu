@@ -372,6 +372,21 @@ int launch_cfg_euler(float *z, const float *v_cond, const float *v_uncond, float
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
+// Rotation angle of every consecutive pair from cos / sin tables that hold each value twice ([seq, 128] ->
+// [seq, 64], in [-pi, pi]): the form the fused projection epilogue reads (gemm.cuh, QkvNormRope::ang).
+__global__ void rope_angles_kernel(const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                   float *__restrict__ ang, long long pairs) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    ang[i] = atan2f(sin_t[2 * i], cos_t[2 * i]);
+}
+
+int launch_rope_angles(const float *cos_t, const float *sin_t, float *ang, long long pairs, cudaStream_t st) {
+  if (pairs <= 0) return 0;
+  rope_angles_kernel<<<ew_grid(pairs), 256, 0, st>>>(cos_t, sin_t, ang, pairs);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
 // ------------------------------------------------------------------------------------------------ 16-bit formats
 __device__ __forceinline__ uint32_t cvt16_pair(uint32_t u, bool to_f16) {
   if (to_f16) {

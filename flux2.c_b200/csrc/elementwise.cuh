@@ -27,6 +27,8 @@ int launch_f32_to_bf16(const float *in, void *out_16, long long n, int f16, cuda
 int launch_convert16_inplace(void *p, long long n, int to_f16, cudaStream_t st);
 // to_packed != 0: packed[B, C p p, H/p, W/p] = patchify(plain[B, C, H, W]); else the inverse.
 int launch_patchify(float *packed, float *plain, int batch, int C, int H, int W, int p, int to_packed, cudaStream_t st);
+// ang[i] = atan2(sin_t[2 i], cos_t[2 i]) for i < pairs
+int launch_rope_angles(const float *cos_t, const float *sin_t, float *ang, long long pairs, cudaStream_t st);
 int launch_euler(float *z, const float *v, const float *sched, int step, long long n, cudaStream_t st);
 int launch_scale_copy(float *dst, const float *src, float a, long long n, cudaStream_t st);
 int launch_cfg_euler(float *z, const float *v_cond, const float *v_uncond, float *v_out, float g, const float *sched,

@@ -339,7 +339,8 @@ int model_finalize(flux_cuda_model *m) {
 }
 
 // ------------------------------------------------------------------------------------------------ workspace
-static void build_rope(const ModelDims &d, const Workspace &ws, std::vector<float> &cs, std::vector<float> &sn) {
+static void build_rope(const ModelDims &d, const Workspace &ws, std::vector<float> &cs, std::vector<float> &sn,
+                       std::vector<float> &ang) {
   // cos/sin [N, 128] over [txt ; img ; refs]; 4 axes (T, Y, X, L) x 16 frequencies, each duplicated over its
   // (even, odd) pair (flux_transformer.c:591-779), evaluated in float like the reference.
   const int ax = d.axis_dim, half = ax / 2, hd = d.head_dim;
@@ -347,6 +348,7 @@ static void build_rope(const ModelDims &d, const Workspace &ws, std::vector<floa
   for (int k = 0; k < half; ++k) fr[k] = 1.0f / powf(d.rope_theta, static_cast<float>(2 * k) / static_cast<float>(ax));
   cs.assign(static_cast<size_t>(ws.N) * hd, 1.0f);
   sn.assign(static_cast<size_t>(ws.N) * hd, 0.0f);
+  ang.assign(static_cast<size_t>(ws.N) * (hd / 2), 0.0f);
   auto put = [&](int row, int axis, int pos) {
     for (int k = 0; k < half; ++k) {
       const float a = static_cast<float>(pos) * fr[k];
@@ -354,6 +356,10 @@ static void build_rope(const ModelDims &d, const Workspace &ws, std::vector<floa
       const size_t o = static_cast<size_t>(row) * hd + axis * ax + 2 * k;
       cs[o] = cs[o + 1] = c;
       sn[o] = sn[o + 1] = s;
+      // the same angle (the float product the reference forms), reduced in double to [-pi, pi] so that the device's
+      // fast sine / cosine work in their accurate range
+      ang[static_cast<size_t>(row) * (hd / 2) + (axis * ax) / 2 + k] =
+          static_cast<float>(remainder(static_cast<double>(a), 6.283185307179586476925286766559));
     }
   };
   for (int i = 0; i < ws.n_txt; ++i) put(i, 3, i);
@@ -447,6 +453,7 @@ int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec 
   WS_ALLOC(mod, S * 17 * hid);
   WS_ALLOC(rope_cos, static_cast<size_t>(ws->N) * d.head_dim);
   WS_ALLOC(rope_sin, static_cast<size_t>(ws->N) * d.head_dim);
+  WS_ALLOC(rope_ang, static_cast<size_t>(ws->N) * (d.head_dim / 2));
 #undef WS_ALLOC
   if (!rc) rc = check_cuda(cudaEventCreate(&ws->ev0), "cudaEventCreate");
   if (!rc) rc = check_cuda(cudaEventCreate(&ws->ev1), "cudaEventCreate");
@@ -456,10 +463,11 @@ int sampler_create(flux_cuda_model *m, int h, int w, int txt_seq, const RefSpec 
     cudaMemsetAsync(ws->tsin, 0, S * d.time_dim * 4, m->ctx->stream);
     cudaMemsetAsync(ws->th, 0, S * hid * 4, m->ctx->stream);
     cudaMemsetAsync(ws->svec, 0, S * hid * 4, m->ctx->stream);
-    std::vector<float> cs, sn;
-    build_rope(d, *ws, cs, sn);
+    std::vector<float> cs, sn, ang;
+    build_rope(d, *ws, cs, sn, ang);
     rc = check_cuda(upload_h2d(m->ctx->stream, ws->rope_cos, cs.data(), cs.size() * 4), "upload rope");
     if (!rc) rc = check_cuda(upload_h2d(m->ctx->stream, ws->rope_sin, sn.data(), sn.size() * 4), "upload rope");
+    if (!rc) rc = check_cuda(upload_h2d(m->ctx->stream, ws->rope_ang, ang.data(), ang.size() * 4), "upload rope");
   }
   if (rc) {
     sampler_free(s);
@@ -561,6 +569,7 @@ struct Launcher {
     s.qk.wk_img = nk_i;
     s.qk.cos_t = ws->rope_cos;
     s.qk.sin_t = ws->rope_sin;
+    s.qk.ang = ws->rope_ang;
     s.qk.pos0 = pos0;
     s.qk.seq = ws->N;
     s.qk.n_txt = ws->n_txt;

@@ -79,6 +79,7 @@ struct Workspace {
   float *z_in = nullptr, *ctx_in = nullptr, *ref_in = nullptr;  // raw uploads
   float *sched = nullptr, *tsin = nullptr, *th = nullptr, *svec = nullptr, *mod = nullptr;
   float *rope_cos = nullptr, *rope_sin = nullptr;
+  float *rope_ang = nullptr;  // [N, 64]: rotation angle of every consecutive pair, reduced to [-pi, pi]
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int last_steps = 0;
   long long launches = 0;  // kernels launched by the last run

@@ -28,6 +28,12 @@ enum EpiMode : int {
 struct QkvNormRope {
   const float *wq_txt, *wk_txt, *wq_img, *wk_img;
   const float *cos_t, *sin_t;
+  // half_split = 0 only, optional: the rotation ANGLE of every consecutive pair, f32 [seq, 64], reduced to [-pi, pi].
+  // When set it replaces the cos/sin tables: a row's 64 angles are a quarter of the bytes of its 2 x 128 table values
+  // (the tables hold every value twice), and an epilogue thread - which owns a whole row, so that its 32 lanes read 32
+  // different rows - issues a quarter of the scattered loads; cos and sin come from the special-function unit, which
+  // has nothing else to do in a GEMM.
+  const float *ang;
   int pos0, seq, n_txt, q_cols, k_cols, half_split;
 };
 

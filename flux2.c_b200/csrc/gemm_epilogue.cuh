@@ -362,10 +362,39 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             tc_ld_32x32(th + c * 32, r);
+            // 16 pair angles of this row and chunk: four scattered 16-byte loads instead of sixteen, issued before
+            // the wait for the accumulator so that the two latencies overlap
+            float4 an4[4];
+            if (rotate && qk.ang != nullptr) {
+              const float4 *a4 = reinterpret_cast<const float4 *>(qk.ang + static_cast<size_t>(pos) * 64 + c * 16);
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) an4[j4] = __ldg(a4 + j4);
+            }
             if ((c & 1) == 0) buf = st.acquire();
             tc_wait_ld();
             uint32_t wv[16];
-            if (rotate) {
+            if (rotate && qk.ang != nullptr) {
+              const float4 *w4 = reinterpret_cast<const float4 *>(w + c * 32);
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 an = an4[j4];
+                const float ang4[4] = {an.x, an.y, an.z, an.w};
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const int j = 2 * j4 + e;  // float4 index inside the chunk: elements 4j .. 4j+3 = pairs 2j, 2j+1
+                  const float4 ww = __ldg(w4 + j);
+                  float s0, c0, s1, c1;
+                  __sincosf(ang4[2 * e], &s0, &c0);
+                  __sincosf(ang4[2 * e + 1], &s1, &c1);
+                  const float x0 = __uint_as_float(r[4 * j + 0]) * rinv * ww.x;
+                  const float x1 = __uint_as_float(r[4 * j + 1]) * rinv * ww.y;
+                  const float x2 = __uint_as_float(r[4 * j + 2]) * rinv * ww.z;
+                  const float x3 = __uint_as_float(r[4 * j + 3]) * rinv * ww.w;
+                  wv[2 * j + 0] = pack_16x2_t(x0 * c0 - x1 * s0, x1 * c0 + x0 * s0, f16, mx);
+                  wv[2 * j + 1] = pack_16x2_t(x2 * c1 - x3 * s1, x3 * c1 + x2 * s1, f16, mx);
+                }
+              }
+            } else if (rotate) {
               const float4 *w4 = reinterpret_cast<const float4 *>(w + c * 32);
               const float4 *c4 = reinterpret_cast<const float4 *>(qk.cos_t + static_cast<size_t>(pos) * 128 + c * 32);
               const float4 *s4 = reinterpret_cast<const float4 *>(qk.sin_t + static_cast<size_t>(pos) * 128 + c * 32);
