@@ -305,6 +305,30 @@ def run_micro(args):
                      "last_epilogue_done", "before_teardown", "tmem_freed"]
             line["trace_cycles_since_entry"] = {n: int(v - st[0]) for n, v in zip(names, st)}
         emit(line)
+    elif args.micro == "gemmtable":
+        # The GEMM shapes of the 512x512 configuration (N x K of each projection) at M = 512, 1024 and 1536 rows, timed
+        # back to back in one process at burst clocks, with torch.matmul (cuBLAS) on the same operands as the yardstick
+        # column. Plain 16-bit store epilogue on both sides.
+        shapes = [("double qkv", 9216, 3072), ("double ff in", 18432, 3072), ("single linear1", 27648, 3072),
+                  ("single linear2", 3072, 12288), ("out proj", 3072, 3072), ("double ff out", 3072, 9216)]
+        rows = []
+        epi = fx.EPI_STORE_BF16 | fx.EPI_X_F16 | fx.EPI_OUT_F16
+        for name, N, K in shapes:
+            for M in (512, 1024, 1536):
+                x = torch.randn(M, K, device="cuda").to(torch.float16)
+                w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.float16)
+                out = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+                torch.cuda.synchronize()
+                ms = timed(lambda: ctx.gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi))
+                wt = w.t()
+                with torch.cuda.stream(stream):
+                    ms_lib = timed(lambda: torch.matmul(x, wt, out=out))
+                fl = 2.0 * M * N * K
+                rows.append({"name": name, "M": M, "N": N, "K": K, "us": round(ms * 1e3, 2),
+                             "tflops": round(fl / ms / 1e9, 1), "torch_matmul_us": round(ms_lib * 1e3, 2),
+                             "torch_matmul_tflops": round(fl / ms_lib / 1e9, 1)})
+                del x, w, out
+        emit({"micro": "gemmtable", "rows": rows, "peak_source": peaks["source"]})
     elif args.micro == "attn":
         seq, heads = args.seq, 24
         hid = heads * 128
@@ -455,8 +479,8 @@ def run_micro(args):
         # of --seq tokens through the host-buffer entry point: token ids in, [seq, 7680] f32 embeddings out.
         import numpy as np
         synth = importlib.import_module("flux2_c_b200.synth")
-        d = synth.QwenDims(layers=27) if args.layers >= 27 else synth.QwenDims(
-            layers=args.layers, out_layers=(0, max(0, args.layers // 2), args.layers - 1))
+        nl = max(3, args.layers)  # three distinct output layers are read
+        d = synth.QwenDims(layers=27) if nl >= 27 else synth.QwenDims(layers=nl, out_layers=(0, nl // 2, nl - 1))
         W = synth.make_qwen_weights(d, seed=0, threads=os.cpu_count())
         B = max(1, args.prompt_batch)
         enc = fx.TextEncoder.from_tensors(ctx, d, W, max_seq=max(512, args.seq) * B)
@@ -805,6 +829,8 @@ def run_ours(args):
     import flux2_c_b200.synth as synth
     dims = synth.Dims.klein4b()
     ctx = fx.Context(local)
+    if args.half != "f16":
+        ctx.set_half_format(args.half)  # before the model is loaded: the weights are stored in this format
 
     # ---- model: rank 0 generates the seeded weights once; other ranks read the same file through the loader
     # (all of this is set-up, outside every timed region; its duration is reported as setup_s)
@@ -982,7 +1008,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": args.half, "data": "synthetic",
         "config": bench_config(world),
         "ms_per_dit_step": ms_total / args.steps / STEPS_PER_IMAGE,
         "model_tflops": (STEPS_PER_IMAGE * (fl["gemm"] + fl["attn"]) + fl["ctx_embed_once"]) * args.steps /
@@ -1044,7 +1070,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro", default=None, choices=["gemm", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load", "step"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "gemmtable", "attn", "adaln", "qwen3", "vae", "conv", "gn", "load", "step"])
+    ap.add_argument("--half", default="f16", choices=["f16", "bf16"],
+                    help="16-bit storage format of weights and activations (f32 accumulation either way)")
     ap.add_argument("--shape", type=int, nargs=3, default=[1536, 27648, 3072])
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile width: 128, 256, or 512 = CTA pairs")
     ap.add_argument("--epi", default="store", choices=["store", "qkv", "gated", "f32"], help="epilogue of --micro gemm")

@@ -127,6 +127,7 @@ void flux_cuda_ctx_destroy(flux_cuda_ctx *ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
   }
+  fx::upload_ring_release(ctx);
   if (ctx->err_dev) cudaFree(ctx->err_dev);
   if (ctx->err_host) cudaFreeHost(ctx->err_host);
   if (ctx->gn_scratch) cudaFree(ctx->gn_scratch);

@@ -27,6 +27,7 @@
 #include "ptx.cuh"
 
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 namespace fx {
 
@@ -292,19 +293,33 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
       if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // Software pipeline over the row's 128 scores: the exponent argument of element e + DEPTH is formed right
+      // after the exponential of element e is issued, so that the special-function unit (8 cycles per warp
+      // instruction, the bound of this phase) starts after DEPTH multiply-adds instead of after all 128.
+      {
+        constexpr int DEPTH = 8;
+        const float neg_m = -m_ref;
+        float xq[DEPTH];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t pk[32];
+        for (int e = 0; e < DEPTH; ++e) xq[e] = fmaf_pinned(__uint_as_float(s[e >> 5][e & 31]), scale, neg_m);
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int h = 0; h < 2; ++h) {
+          uint32_t pk[32];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i]), scale, -m_ref));
-            const float p1 = ex2f_(fmaf(__uint_as_float(s[2 * h + c][2 * i + 1]), scale, -m_ref));
+          for (int i = 0; i < 32; ++i) {
+            const int e = h * 64 + 2 * i;  // elements e, e + 1 of the row -> one packed pair
+            const float p0 = ex2f_pinned(xq[e % DEPTH]);
+            if (e + DEPTH < 128)
+              xq[e % DEPTH] = fmaf_pinned(__uint_as_float(s[(e + DEPTH) >> 5][(e + DEPTH) & 31]), scale, neg_m);
+            const float p1 = ex2f_pinned(xq[(e + 1) % DEPTH]);
+            if (e + 1 + DEPTH < 128)
+              xq[(e + 1) % DEPTH] =
+                  fmaf_pinned(__uint_as_float(s[(e + 1 + DEPTH) >> 5][(e + 1 + DEPTH) & 31]), scale, neg_m);
             sum4[i & 3] += p0 + p1;
-            pk[c * 16 + i] = pack_16x2(p0, p1, f16);
+            pk[i] = pack_16x2(p0, p1, f16);
           }
-        tc_st_32x32(s_addr + h * 32, pk);
+          tc_st_32x32(s_addr + h * 32, pk);
+        }
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (tr) stamp(j, 8 + 5 * t);
@@ -321,23 +336,50 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
       tc_fence_after_sync();
       const float inv = 1.0f / l;
       const int grow = q0 + t * TILE + row;
-      __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
-                            (static_cast<size_t>(batch) * P.seq + grow) * P.out_ld + P.out_col + head * 128;
       uint32_t o[32];
+      if (P.tma_out) {
+        // The Q tile of this query tile is no longer read by anything (its last MMA completed before o_done), so its
+        // 32 KB hold the output on its way out: each warp packs its 32 rows x 128 columns into two swizzled blocks
+        // of 32 rows x 64 columns and hands them to the TMA unit, which clips rows past the end of the sequence.
+        uint8_t *stg = smem + OFF_Q + t * 32768 + q * 8192;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tc_ld_32x32(o_addr + c * 32, o);
-        tc_wait_ld();
-        if (grow < P.seq) {
-          uint4 *d4 = reinterpret_cast<uint4 *>(dstg + c * 32);
+        for (int c = 0; c < 4; ++c) {
+          tc_ld_32x32(o_addr + c * 32, o);
+          tc_wait_ld();
+          uint32_t w[16];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 v;
-            v.x = pack_16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv, f16);
-            v.y = pack_16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv, f16);
-            v.z = pack_16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv, f16);
-            v.w = pack_16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv, f16);
-            d4[u] = v;
+          for (int u = 0; u < 16; ++u)
+            w[u] = pack_16x2(__uint_as_float(o[2 * u]) * inv, __uint_as_float(o[2 * u + 1]) * inv, f16);
+          stage_pieces4(stg + (c >> 1) * 4096, lane, w, (c & 1) * 4);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int y0 = q0 + t * TILE + q * 32;
+        if (lane == 0 && y0 < P.seq) {
+          const int x0 = P.out_col + head * 128;
+          tma_store_3d(&P.tm_out, stg, x0, y0, batch);
+          tma_store_3d(&P.tm_out, stg + 4096, x0 + 64, y0, batch);
+          bulk_commit();
+          bulk_wait<0>();
+        }
+      } else {
+        __nv_bfloat16 *dstg = reinterpret_cast<__nv_bfloat16 *>(P.out) +
+                              (static_cast<size_t>(batch) * P.seq + grow) * P.out_ld + P.out_col + head * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tc_ld_32x32(o_addr + c * 32, o);
+          tc_wait_ld();
+          if (grow < P.seq) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dstg + c * 32);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 v;
+              v.x = pack_16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv, f16);
+              v.y = pack_16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv, f16);
+              v.z = pack_16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv, f16);
+              v.w = pack_16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv, f16);
+              d4[u] = v;
+            }
           }
         }
       }
@@ -387,6 +429,24 @@ int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long l
                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -4;
+  // The output as [batch, seq, out_ld] with a box of 32 rows x 64 columns: one warp's staging block. Opt out with
+  // FLUX_CUDA_ATTN_TMA_OUT=0 (per-row 16-byte stores instead).
+  static const int tma_out_env = [] {
+    const char *e = getenv("FLUX_CUDA_ATTN_TMA_OUT");
+    return e ? atoi(e) : 1;
+  }();
+  p->tma_out = 0;
+  if (tma_out_env) {
+    cuuint64_t odims[3] = {static_cast<cuuint64_t>(out_ld), static_cast<cuuint64_t>(seq),
+                           static_cast<cuuint64_t>(batch)};
+    cuuint64_t ostrides[2] = {static_cast<cuuint64_t>(out_ld) * 2, static_cast<cuuint64_t>(out_ld) * 2 * seq};
+    cuuint32_t obox[3] = {64, 32, 1};
+    r = g_encode4(&p->tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, odims, ostrides, obox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -4;
+    p->tma_out = 1;
+  }
   p->seq = seq;
   p->batch = batch;
   p->heads = heads;

@@ -5,6 +5,18 @@
 #include <cuda_runtime.h>
 #include <string>
 
+// Ring of pinned staging buffers for weight uploads: host threads copy the next piece of a (pageable, usually
+// memory-mapped) tensor into one slot while the DMA engine drains the previous slots.
+struct UploadRing {
+  static constexpr int SLOTS = 3;
+  static constexpr size_t SLOT_BYTES = 32u << 20;
+  void *buf[SLOTS] = {nullptr, nullptr, nullptr};
+  cudaEvent_t drained[SLOTS] = {nullptr, nullptr, nullptr};
+  int next = 0;
+  int state = 0;  // 0 not tried, 1 ready, -1 pinned memory unavailable (uploads fall back to pageable copies)
+  int threads = 1;
+};
+
 struct flux_cuda_ctx {
   int device = 0;
   int num_sms = 0;
@@ -18,6 +30,7 @@ struct flux_cuda_ctx {
   float *gn_scratch = nullptr;    // lazily allocated scratch of the kernel-level GroupNorm entry point
   float *rope_scratch = nullptr;  // lazily allocated pair-angle table of flux_cuda_gemm_qkv_norm_rope
   size_t rope_scratch_floats = 0;
+  UploadRing upload;              // created by the first weight upload, released with the context
   long long *gemm_trace = nullptr;  // device buffer for the paired GEMM's timeline stamps (measurements only)
 };
 
@@ -33,4 +46,8 @@ inline cudaError_t upload_h2d(cudaStream_t st, void *dst, const void *src, size_
   cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st);
   return e != cudaSuccess ? e : cudaStreamSynchronize(st);
 }
+// Copies `bytes` of pageable host memory to the device through the context's pinned ring, ordered on the context's
+// stream. The host memory has been read completely when this returns; the device copy completes in stream order.
+int upload_pipelined(flux_cuda_ctx *ctx, void *dst, const void *src, size_t bytes);
+void upload_ring_release(flux_cuda_ctx *ctx);
 }  // namespace fx

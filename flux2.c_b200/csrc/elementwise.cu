@@ -165,6 +165,12 @@ __global__ void timestep_sincos_kernel(const float *__restrict__ t, int S, int d
   (void)S;
 }
 
+// Four output rows per warp: the S x 8 activations a lane needs for its slice of K are read from shared memory ONCE
+// and applied to four rows' weights, whose 16-byte loads are all in flight together - a quarter of the shared-memory
+// traffic per weight byte of a one-row-per-warp kernel (which ran at 19 % of the HBM rate on the 320 MB modulation
+// matrix) and four times the memory-level parallelism.
+static constexpr int GEMV_ROWS = 4;
+
 template <int S>
 __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__restrict__ W,
                                                          const float *__restrict__ x, float *__restrict__ y, int R,
@@ -173,40 +179,57 @@ __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__
   for (int i = threadIdx.x; i < S * K / 4; i += blockDim.x)
     reinterpret_cast<float4 *>(xs)[i] = reinterpret_cast<const float4 *>(x)[i];
   __syncthreads();
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int r0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * GEMV_ROWS;
   const int lane = threadIdx.x & 31;
-  if (r >= R) return;
-  const uint4 *wr = reinterpret_cast<const uint4 *>(W + static_cast<size_t>(r) * K);
-  float acc[S];
+  if (r0 >= R) return;
+  const uint4 *wr[GEMV_ROWS];
 #pragma unroll
-  for (int s = 0; s < S; ++s) acc[s] = 0.f;
+  for (int q = 0; q < GEMV_ROWS; ++q) {
+    const int r = r0 + q < R ? r0 + q : R - 1;  // rows past the end repeat the last one; their results are dropped
+    wr[q] = reinterpret_cast<const uint4 *>(W + static_cast<size_t>(r) * K);
+  }
+  float acc[GEMV_ROWS][S];
+#pragma unroll
+  for (int q = 0; q < GEMV_ROWS; ++q)
+#pragma unroll
+    for (int s = 0; s < S; ++s) acc[q][s] = 0.f;
   for (int i = lane; i < K / 8; i += 32) {
-    const uint4 w = __ldg(wr + i);
-    float wf[8];
-    if (f16) {
-      const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w.x));
-      const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&w.y));
-      const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&w.z));
-      const float2 d = __half22float2(*reinterpret_cast<const __half2 *>(&w.w));
-      wf[0] = a.x, wf[1] = a.y, wf[2] = b.x, wf[3] = b.y, wf[4] = c.x, wf[5] = c.y, wf[6] = d.x, wf[7] = d.y;
-    } else {
-      wf[0] = bf16_lo(w.x), wf[1] = bf16_hi(w.x), wf[2] = bf16_lo(w.y), wf[3] = bf16_hi(w.y);
-      wf[4] = bf16_lo(w.z), wf[5] = bf16_hi(w.z), wf[6] = bf16_lo(w.w), wf[7] = bf16_hi(w.w);
-    }
+    uint4 w[GEMV_ROWS];
+#pragma unroll
+    for (int q = 0; q < GEMV_ROWS; ++q) w[q] = __ldg(wr[q] + i);
+    float4 xa[S], xb[S];
 #pragma unroll
     for (int s = 0; s < S; ++s) {
-      const float4 a = *reinterpret_cast<const float4 *>(xs + s * K + i * 8);
-      const float4 b = *reinterpret_cast<const float4 *>(xs + s * K + i * 8 + 4);
-      acc[s] += (wf[0] * a.x + wf[1] * a.y) + (wf[2] * a.z + wf[3] * a.w) + (wf[4] * b.x + wf[5] * b.y) +
-                (wf[6] * b.z + wf[7] * b.w);
+      xa[s] = *reinterpret_cast<const float4 *>(xs + s * K + i * 8);
+      xb[s] = *reinterpret_cast<const float4 *>(xs + s * K + i * 8 + 4);
+    }
+#pragma unroll
+    for (int q = 0; q < GEMV_ROWS; ++q) {
+      float wf[8];
+      if (f16) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w[q].x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&w[q].y));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&w[q].z));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2 *>(&w[q].w));
+        wf[0] = a.x, wf[1] = a.y, wf[2] = b.x, wf[3] = b.y, wf[4] = c.x, wf[5] = c.y, wf[6] = d.x, wf[7] = d.y;
+      } else {
+        wf[0] = bf16_lo(w[q].x), wf[1] = bf16_hi(w[q].x), wf[2] = bf16_lo(w[q].y), wf[3] = bf16_hi(w[q].y);
+        wf[4] = bf16_lo(w[q].z), wf[5] = bf16_hi(w[q].z), wf[6] = bf16_lo(w[q].w), wf[7] = bf16_hi(w[q].w);
+      }
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+        acc[q][s] += (wf[0] * xa[s].x + wf[1] * xa[s].y) + (wf[2] * xa[s].z + wf[3] * xa[s].w) +
+                     (wf[4] * xb[s].x + wf[5] * xb[s].y) + (wf[6] * xb[s].z + wf[7] * xb[s].w);
     }
   }
 #pragma unroll
-  for (int s = 0; s < S; ++s) {
-    float v = warp_sum(acc[s]);
-    if (silu_out) v = v / (1.0f + expf(-v));
-    if (lane == 0) y[static_cast<size_t>(s) * R + r] = v;
-  }
+  for (int q = 0; q < GEMV_ROWS; ++q)
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      float v = warp_sum(acc[q][s]);
+      if (silu_out) v = v / (1.0f + expf(-v));
+      if (lane == 0 && r0 + q < R) y[static_cast<size_t>(s) * R + r0 + q] = v;
+    }
 }
 
 int launch_timestep_sincos(const float *t, int S, int dim, float *out, cudaStream_t st) {
@@ -224,7 +247,7 @@ int elementwise_init() {
 int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int silu_out, int f16, cudaStream_t st) {
   if (K % 8 || K > 12288) return -1;
   const size_t smem = static_cast<size_t>(GEMV_S) * K * 4;
-  gemv_multi_kernel<GEMV_S><<<(R + 7) / 8, 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
+  gemv_multi_kernel<GEMV_S><<<(R + 8 * GEMV_ROWS - 1) / (8 * GEMV_ROWS), 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
                                                              silu_out, f16);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }

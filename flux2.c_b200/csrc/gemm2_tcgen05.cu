@@ -247,7 +247,7 @@ int gemm2_launch(GemmParams *P, int num_sms, cudaStream_t stream) {
             make_tmap_2d_f32(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + width, sg.ld, 32, 32) == 0)
           sg.tma_out = 1;
       } else if (tma_level >= 2 && (sg.mode == EPI_STORE_BF16 || sg.mode == EPI_SWIGLU_BF16 ||
-                                    (sg.mode == EPI_QKV_NORM_ROPE && !sg.qk.half_split))) {
+                                    (sg.mode == EPI_QKV_NORM_ROPE && (!sg.qk.half_split || sg.qk.ang != nullptr)))) {
         // 16-bit outputs: blocks of 32 rows x 64 columns (SwiGLU writes half as many columns as it computes)
         const int out_cols = sg.mode == EPI_SWIGLU_BF16 ? width / 2 : width;
         if (!(sg.col0 & 7) && make_tmap_2d_bf16(&sg.tm_out, sg.out, pb.M, static_cast<uint64_t>(sg.col0) + out_cols,

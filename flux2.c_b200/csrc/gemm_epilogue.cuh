@@ -35,18 +35,8 @@ __device__ __forceinline__ void stage_and_store_chunk(const CUtensorMap *tm, uin
 }
 
 // 16-bit outputs through the TMA unit: a staging block holds 32 rows x 64 columns (128 bytes per row), i.e. two
-// 32-column chunks of the accumulator. Chunks are written four 16-byte pieces at a time; the two blocks of a warp
-// alternate so that one is being filled while the TMA unit still reads the other.
-__device__ __forceinline__ void stage_pieces4(uint8_t *buf, int lane, const uint32_t (&w)[16], int piece0) {
-  const uint32_t base = smem_u32(buf) + static_cast<uint32_t>(lane) * 128u;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t a = base + static_cast<uint32_t>(((piece0 + j) ^ (lane & 7)) * 16);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(w[4 * j]), "r"(w[4 * j + 1]),
-                 "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
-                 : "memory");
-  }
-}
+// 32-column chunks of the accumulator, written four 16-byte pieces at a time (stage_pieces4, ptx.cuh); the two blocks
+// of a warp alternate so that one is being filled while the TMA unit still reads the other.
 struct Stage16 {
   uint8_t *stage;
   int lane;
@@ -315,6 +305,61 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
           rinv = rsqrtf(ss * (1.0f / 128.0f) + 1e-6f);
           const bool is_k = col >= qk.q_cols;
           w = (pos < qk.n_txt) ? (is_k ? qk.wk_txt : qk.wq_txt) : (is_k ? qk.wk_img : qk.wq_img);
+        }
+        if (rotate && qk.half_split && stage != nullptr && sg.tma_out && qk.ang != nullptr) {
+          // pairs (i, i + 64) with the pair angles read 16 bytes at a time, and both halves of the head leaving
+          // through the TMA unit: staging block 0 collects columns 0..63 of the head, block 1 columns 64..127
+          const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+          uint32_t u[32];
+          if (lane == 0) bulk_wait_read<0>();  // both blocks are free
+          __syncwarp();
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            tc_ld_32x32(th + c * 32, r);
+            tc_ld_32x32(th + 64 + c * 32, u);
+            float4 an4[8];
+            const float4 *a4 = reinterpret_cast<const float4 *>(qk.ang + static_cast<size_t>(pos) * 64 + c * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) an4[j] = __ldg(a4 + j);
+            tc_wait_ld();
+            const float4 *wa4 = reinterpret_cast<const float4 *>(w + c * 32);
+            const float4 *wb4 = reinterpret_cast<const float4 *>(w + 64 + c * 32);
+            uint32_t oa[16], ob[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 wa = __ldg(wa4 + j), wb = __ldg(wb4 + j);
+              const float av[4] = {an4[j].x, an4[j].y, an4[j].z, an4[j].w};
+              const float wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+              float ya[4], yb[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float x0 = __uint_as_float(r[4 * j + k]) * rinv * wav[k];
+                const float x1 = __uint_as_float(u[4 * j + k]) * rinv * wbv[k];
+                float sn, cs;
+                __sincosf(av[k], &sn, &cs);
+                ya[k] = x0 * cs - x1 * sn;
+                yb[k] = x0 * sn + x1 * cs;
+              }
+              oa[2 * j] = pack_16x2_t(ya[0], ya[1], f16, mx);
+              oa[2 * j + 1] = pack_16x2_t(ya[2], ya[3], f16, mx);
+              ob[2 * j] = pack_16x2_t(yb[0], yb[1], f16, mx);
+              ob[2 * j + 1] = pack_16x2_t(yb[2], yb[3], f16, mx);
+            }
+            stage_pieces4(stage, lane, oa, c * 4);
+            stage_pieces4(stage + 4096, lane, ob, c * 4);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (y < pb.M) {
+              tma_store_2d(&sg.tm_out, stage, sg.col0 + nrel + hd * 128, y);
+              tma_store_2d(&sg.tm_out, stage + 4096, sg.col0 + nrel + hd * 128 + 64, y);
+              bulk_commit();
+            }
+            bulk_wait_read<0>();  // whatever uses the blocks next finds them free
+          }
+          __syncwarp();
+          continue;
         }
         if (rotate && qk.half_split) {
           // pairs (i, i + 64): chunk c of the first half rotates with chunk c of the second half

@@ -165,6 +165,27 @@ __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+// Staging for those stores: a block of 32 rows x 128 bytes in the 128-byte-swizzle layout the tensor maps use. Lane
+// `lane` owns row `lane`; this writes four consecutive 16-byte pieces of its row, starting at piece `piece0` (0 or 4).
+// The 16-byte pieces of a row are permuted by the row's low three bits, which is what the swizzle prescribes and also
+// puts the eight lanes of a store phase on different banks.
+__device__ __forceinline__ void stage_pieces4(uint8_t *buf, int lane, const uint32_t (&w)[16], int piece0) {
+  const uint32_t base = smem_u32(buf) + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t a = base + static_cast<uint32_t>(((piece0 + j) ^ (lane & 7)) * 16);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(w[4 * j]), "r"(w[4 * j + 1]),
+                 "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                 : "memory");
+  }
+}
+
 // ---------------------------------------------------------------- TMEM allocation (one full warp)
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -247,6 +268,19 @@ __device__ __forceinline__ float ex2f_(float x) {
   return y;
 }
 
+// Order-pinned variants for software-pipelined loops: volatile asm statements keep their program order, so a loop
+// written as "exponential of element i, argument of element i + D" really interleaves the two pipes instead of
+// running all multiply-adds first and all exponentials afterwards.
+__device__ __forceinline__ float ex2f_pinned(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fmaf_pinned(float a, float b, float c) {
+  float y;
+  asm volatile("fma.rn.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 // Two exponentials per special-function-unit instruction: 2^x of a packed f16 pair, result packed f16 (which is the
 // format the probabilities are stored in, so no conversion follows). The argument is rounded to f16 first: an absolute
 // error of at most 2^-12 for |x| < 1 (where the large probabilities are) growing to 2^-8 at |x| = 16.

@@ -134,7 +134,7 @@ struct flux_cuda_qwen3 {
   size_t expected = 0;
   bool finalized = false;
   // workspace for max_seq tokens
-  float *hidden = nullptr, *out = nullptr, *ones = nullptr, *cos_t = nullptr, *sin_t = nullptr, *part = nullptr;
+  float *hidden = nullptr, *out = nullptr, *ones = nullptr, *cos_t = nullptr, *sin_t = nullptr, *ang_t = nullptr, *part = nullptr;
   bool split_k = true;  // FLUX_CUDA_QWEN_SPLITK=0: every projection as one problem
   uint16_t *norm = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr;
   int *ids = nullptr;
@@ -230,6 +230,7 @@ int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims,
   if (!rc) rc = q_alloc(m, &m->ones, h);
   if (!rc) rc = q_alloc(m, &m->cos_t, S * 64);
   if (!rc) rc = q_alloc(m, &m->sin_t, S * 64);
+  if (!rc) rc = q_alloc(m, &m->ang_t, S * 64);
   if (!rc) rc = q_alloc(m, &m->norm, S * h);
   if (!rc) rc = q_alloc(m, &m->qkv, S * static_cast<size_t>(qkv_n));
   if (!rc) rc = q_alloc(m, &m->attn, S * qd);
@@ -237,17 +238,21 @@ int flux_cuda_qwen3_create(flux_cuda_ctx *ctx, const flux_cuda_qwen3_dims *dims,
   if (!rc) rc = q_alloc(m, &m->ids, S);
   if (!rc) rc = q_alloc(m, &m->mask, S / 32 + S + 4);  // [batch, ceil(seq / 32)] words for any split of S tokens
   if (!rc) {
-    std::vector<float> ones(h, 1.0f), cs(S * 64), sn(S * 64);
+    std::vector<float> ones(h, 1.0f), cs(S * 64), sn(S * 64), an(S * 64);
     for (size_t p = 0; p < S; ++p)
       for (int i = 0; i < 64; ++i) {  // compute_rope_freqs, flux_qwen3.c:253-262, in float like the reference
         const float freq = 1.0f / powf(d.rope_theta, static_cast<float>(2 * i) / static_cast<float>(hd));
         const float ang = static_cast<float>(p) * freq;
         cs[p * 64 + i] = cosf(ang);
         sn[p * 64 + i] = sinf(ang);
+        // the same angle reduced to [-pi, pi] (in double): what the fused projection epilogue reads, taking cos and
+        // sin from the special-function unit in its accurate range
+        an[p * 64 + i] = static_cast<float>(remainder(static_cast<double>(ang), 6.283185307179586476925286766559));
       }
     rc = check_cuda(upload_h2d(ctx->stream, m->ones, ones.data(), h * 4), "upload");
     if (!rc) rc = check_cuda(upload_h2d(ctx->stream, m->cos_t, cs.data(), cs.size() * 4), "upload");
     if (!rc) rc = check_cuda(upload_h2d(ctx->stream, m->sin_t, sn.data(), sn.size() * 4), "upload");
+    if (!rc) rc = check_cuda(upload_h2d(ctx->stream, m->ang_t, an.data(), an.size() * 4), "upload");
   }
   if (rc) {
     flux_cuda_qwen3_free(m);
@@ -352,6 +357,8 @@ int flux_cuda_qwen3_finalize(flux_cuda_qwen3 *m) {
     set_error("text encoder incomplete: %zu of %zu tensors were provided", m->seen.size(), m->expected);
     return FLUX_CUDA_ERR_MODEL;
   }
+  int rc = check_cuda(cudaStreamSynchronize(m->ctx->stream), "upload weights");  // uploads are stream-ordered
+  if (rc) return rc;
   m->finalized = true;
   return FLUX_CUDA_OK;
 }
@@ -504,6 +511,7 @@ static int qwen3_enqueue(flux_cuda_qwen3 *m, const int *input_ids, const int *at
     sq.qk.wk_txt = sq.qk.wk_img = w.kn;
     sq.qk.cos_t = m->cos_t;
     sq.qk.sin_t = m->sin_t;
+    sq.qk.ang = m->ang_t;
     sq.qk.pos0 = 0;
     sq.qk.seq = seq;
     sq.qk.n_txt = 0;

@@ -144,6 +144,36 @@ def test_reference_cli_default_call_path(fx, model_dir, tmp_path):
     assert "Denoising timing breakdown" in log and "Single blocks:" in log
 
 
+def test_reference_cli_debug_py_path(fx, model_dir, tmp_path):
+    """`flux --debug-py` (flux_img2img_debug_py, flux.c:1125-1232): noise, reference latent and text embeddings come
+    from three files under /tmp, the loop is flux_sample_euler_with_refs with T offset 10, then the VAE."""
+    synth, d, mdir = model_dir
+    files = {"/tmp/py_noise.bin": fx.init_noise(128, 8, 8, 11),
+             "/tmp/py_ref_latent.bin": synth.make_latent(7, 128, 8, 8),
+             "/tmp/py_text_emb.bin": synth.make_context(1234, 512, d.text_dim)}
+    try:
+        for path, arr in files.items():
+            arr.astype(np.float32).tofile(path)
+        psnr = _run_both(["-d", mdir, "--debug-py", "-W", "128", "-H", "128", "-s", "4"], tmp_path, "debugpy")
+    finally:
+        for path in files:
+            if os.path.exists(path):
+                os.remove(path)
+    assert psnr >= 30.0, "PSNR %.1f dB" % psnr
+
+
+def _repl_session(mdir, tmp_path, lines):
+    """Drives the engine build of the reference's interactive mode (flux_cli.c) through its standard input and returns
+    (stdout, [paths of the images it saved])."""
+    site = os.path.dirname(os.path.dirname(np.__file__))
+    env = dict(os.environ, HOME=str(tmp_path), TERM="dumb")
+    r = subprocess.run([os.path.join(REF, "flux_cuda_cli"), "-d", mdir], input="\n".join(lines) + "\n",
+                       capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    paths = [ln.split("Done -> ")[1].split(" (ref")[0] for ln in r.stdout.splitlines() if "Done -> " in ln]
+    return r.stdout, paths
+
+
 def test_reference_cli_from_a_text_prompt(fx, model_dir, tmp_path):
     """`flux -p "..."`: the reference's tokenizer feeds the text encoder, which runs on the GPU in one build and on the
     CPU in the other; a byte-level tokenizer file and seeded Qwen3-4B-shaped weights stand in for the real ones."""
@@ -167,7 +197,21 @@ def test_reference_cli_from_a_text_prompt(fx, model_dir, tmp_path):
             f.write(b"P6\n128 128\n255\n" + pic.tobytes())
         psnr_i2i = _run_both(["-d", mdir, "-p", "the man in the rain", "-i", ppm, "-W", "128", "-H", "128", "-s", "4",
                               "-S", "7"], tmp_path, "img2img")
+        # the interactive mode's embedding cache (flux_cli.c:380-400): the second and third time a prompt is entered
+        # its embeddings come from the cache (4-bit block quantised, embcache.c:30-120, so slightly different from
+        # the encoder's output) and go straight to flux_generate_with_embeddings
+        out, imgs = _repl_session(mdir, tmp_path, ["!seed 42", "!size 128x128", "!steps 4",
+                                                   "a cat in the rain and the thin man",
+                                                   "a cat in the rain and the thin man",
+                                                   "a cat in the rain and the thin man", "!quit"])
+        assert len(imgs) == 3 and out.count("(using cached embedding)") == 2, out[-1500:]
+        first, second, third = (read_png_rgb(p) for p in imgs)
+        one_shot = read_png_rgb(str(tmp_path / "out_prompt_cuda.png"))
     finally:
         shutil.rmtree(os.path.join(mdir, "text_encoder"), ignore_errors=True)
     assert psnr >= 30.0, "PSNR %.1f dB" % psnr
     assert psnr_i2i >= 30.0, "img2img PSNR %.1f dB" % psnr_i2i
+    assert np.array_equal(first, one_shot)   # the same prompt, seed and size as the `flux -p` run above: same picture
+    assert np.array_equal(second, third)     # both from the cached embedding: the engine repeats itself bit for bit
+    mse = np.mean((first - second) ** 2)     # the cache is lossy: close, not equal
+    assert 10 * np.log10(255.0 ** 2 / max(mse, 1e-12)) >= 30.0
