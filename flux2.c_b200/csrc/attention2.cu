@@ -44,6 +44,49 @@ static constexpr int OFF_BAR = OFF_KV + 2 * 65536;
 static constexpr int ATT_SMEM = OFF_BAR + 256 + 1024;
 static constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
+// p = 2^(s * scale - m) for the 128 scores of one row, packed to 16-bit pairs and written over the first 64 columns
+// of S in TMEM; returns the row's sum. The special-function unit takes 8 cycles per warp instruction and its results
+// come back tens of cycles later, so the instruction stream is laid out by hand (every statement below is a volatile
+// asm, which keeps this order): each exponential is followed by the multiply-add that forms the argument LEAD
+// elements ahead and by the add / convert that consume the pair issued LAG pairs earlier - never by an instruction
+// that needs a result still in flight.
+template <bool F16>
+__device__ __forceinline__ float exps_row_lagged(const uint32_t (&s)[4][32], float scale, float neg_m, uint32_t s_addr) {
+  constexpr int LEAD = 8, LAG = 4;
+  float x[LEAD], p0[LAG], p1[LAG];
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t pk[32];
+#pragma unroll
+  for (int e = 0; e < LEAD; ++e) x[e] = fmaf_pinned(__uint_as_float(s[e >> 5][e & 31]), scale, neg_m);
+#pragma unroll
+  for (int i = 0; i < 64 + LAG; ++i) {
+    const int e = 2 * i;
+    float t = 0.f;
+    const int c = i - LAG;  // pair consumed in this slot
+    float q0 = 0.f, q1 = 0.f;
+    if (c >= 0) {
+      q0 = p0[c % LAG];
+      q1 = p1[c % LAG];
+    }
+    if (i < 64) {
+      p0[i % LAG] = ex2f_pinned(x[e % LEAD]);
+      if (e + LEAD < 128) x[e % LEAD] = fmaf_pinned(__uint_as_float(s[(e + LEAD) >> 5][(e + LEAD) & 31]), scale, neg_m);
+    }
+    if (c >= 0) t = addf_pinned(q0, q1);
+    if (i < 64) {
+      p1[i % LAG] = ex2f_pinned(x[(e + 1) % LEAD]);
+      if (e + 1 + LEAD < 128)
+        x[(e + 1) % LEAD] = fmaf_pinned(__uint_as_float(s[(e + 1 + LEAD) >> 5][(e + 1 + LEAD) & 31]), scale, neg_m);
+    }
+    if (c >= 0) {
+      sum4[c & 3] = addf_pinned(sum4[c & 3], t);
+      pk[c & 31] = pack_16x2_pinned<F16>(q0, q1);
+      if ((c & 31) == 31) tc_st_32x32(s_addr + (c >> 5) * 32, pk);
+    }
+  }
+  return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
 struct Attn2Bars {
   uint64_t q_full;
   uint64_t k_full[2], v_full[2], kv_empty[2];
@@ -292,36 +335,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
       }
       if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      // Software pipeline over the row's 128 scores: the exponent argument of element e + DEPTH is formed right
-      // after the exponential of element e is issued, so that the special-function unit (8 cycles per warp
-      // instruction, the bound of this phase) starts after DEPTH multiply-adds instead of after all 128.
-      {
-        constexpr int DEPTH = 8;
-        const float neg_m = -m_ref;
-        float xq[DEPTH];
-#pragma unroll
-        for (int e = 0; e < DEPTH; ++e) xq[e] = fmaf_pinned(__uint_as_float(s[e >> 5][e & 31]), scale, neg_m);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int e = h * 64 + 2 * i;  // elements e, e + 1 of the row -> one packed pair
-            const float p0 = ex2f_pinned(xq[e % DEPTH]);
-            if (e + DEPTH < 128)
-              xq[e % DEPTH] = fmaf_pinned(__uint_as_float(s[(e + DEPTH) >> 5][(e + DEPTH) & 31]), scale, neg_m);
-            const float p1 = ex2f_pinned(xq[(e + 1) % DEPTH]);
-            if (e + 1 + DEPTH < 128)
-              xq[(e + 1) % DEPTH] =
-                  fmaf_pinned(__uint_as_float(s[(e + 1 + DEPTH) >> 5][(e + 1 + DEPTH) & 31]), scale, neg_m);
-            sum4[i & 3] += p0 + p1;
-            pk[i] = pack_16x2(p0, p1, f16);
-          }
-          tc_st_32x32(s_addr + h * 32, pk);
-        }
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
+      l += f16 ? exps_row_lagged<true>(s, scale, -m_ref, s_addr) : exps_row_lagged<false>(s, scale, -m_ref, s_addr);
       if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();

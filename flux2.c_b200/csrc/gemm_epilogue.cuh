@@ -102,15 +102,16 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
         Stage16 st{stage, lane, 0};
         uint8_t *buf = nullptr;
+        tc_ld_32x32(taddr, r);  // chunk c + 1 is loaded while chunk c is staged
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          tc_ld_32x32(taddr + c * 32, r);
           if ((c & 1) == 0) buf = st.acquire();
           tc_wait_ld();
           uint32_t w[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             w[j] = pack_16x2_t(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), f16, mx);
+          if (c + 1 < BN / 32) tc_ld_32x32(taddr + (c + 1) * 32, r);
           stage_pieces4(buf, lane, w, (c & 1) * 4);
           if (c & 1) st.release(&sg.tm_out, buf, sg.col0 + nrel + (c - 1) * 32, y, y < pb.M);
         }
@@ -139,9 +140,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
     case EPI_STORE_F32: {
       if (stage != nullptr && sg.tma_out) {
         const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
+        // The TMEM load of chunk c + 1 is issued as soon as chunk c sits in `v`, so that it runs under the staging
+        // stores, the proxy fence and the TMA issue of chunk c.
+        tc_ld_32x32(taddr, r);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          tc_ld_32x32(taddr + c * 32, r);
           if (c >= 2) {  // the store that last used this block has read it
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
@@ -150,6 +153,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (c + 1 < BN / 32) tc_ld_32x32(taddr + (c + 1) * 32, r);
           stage_and_store_chunk<false>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
                                        y < pb.M);
         }
@@ -174,9 +178,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         // out += gate * acc as a TMA reduce-add: the residual is read and updated in L2, the SM only sends gate * acc
         const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
         const float4 *g4 = reinterpret_cast<const float4 *>(sg.gate + nrel);
+        // Pipelined like the plain f32 store; the chunk's gate values are requested before the wait for its
+        // accumulator, so that their latency runs under it.
+        tc_ld_32x32(taddr, r);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          tc_ld_32x32(taddr + c * 32, r);
+          float4 g[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = __ldg(g4 + c * 8 + j);
           if (c >= 2) {
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
@@ -185,12 +194,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
           float v[32];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float4 g = __ldg(g4 + c * 8 + j);
-            v[4 * j + 0] = g.x * __uint_as_float(r[4 * j + 0]);
-            v[4 * j + 1] = g.y * __uint_as_float(r[4 * j + 1]);
-            v[4 * j + 2] = g.z * __uint_as_float(r[4 * j + 2]);
-            v[4 * j + 3] = g.w * __uint_as_float(r[4 * j + 3]);
+            v[4 * j + 0] = g[j].x * __uint_as_float(r[4 * j + 0]);
+            v[4 * j + 1] = g[j].y * __uint_as_float(r[4 * j + 1]);
+            v[4 * j + 2] = g[j].z * __uint_as_float(r[4 * j + 2]);
+            v[4 * j + 3] = g[j].w * __uint_as_float(r[4 * j + 3]);
           }
+          if (c + 1 < BN / 32) tc_ld_32x32(taddr + (c + 1) * 32, r);
           stage_and_store_chunk<true>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
                                       y < pb.M);
         }

@@ -281,6 +281,18 @@ __device__ __forceinline__ float fmaf_pinned(float a, float b, float c) {
   asm volatile("fma.rn.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
+__device__ __forceinline__ float addf_pinned(float a, float b) {
+  float y;
+  asm volatile("add.f32 %0, %1, %2;" : "=f"(y) : "f"(a), "f"(b));
+  return y;
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_16x2_pinned(float lo, float hi) {
+  uint32_t y;
+  if (F16) asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
+  else asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
+  return y;
+}
 // Two exponentials per special-function-unit instruction: 2^x of a packed f16 pair, result packed f16 (which is the
 // format the probabilities are stored in, so no conversion follows). The argument is rounded to f16 first: an absolute
 // error of at most 2^-12 for |x| < 1 (where the large probabilities are) growing to 2^-8 at |x| = 16.
