@@ -28,6 +28,7 @@ static constexpr int P_B_BYTES = (P_BN / 2) * P_BK * 2;  // 16 KB: this CTA's ha
 static constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 static constexpr int P_EPI_STAGE = 4 * EPI_STAGE_BYTES_PER_WARP;  // staging blocks of the four epilogue warps
 static constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + P_EPI_STAGE + 256 + 1024;
+static_assert(4 * 8 * 4096 <= P_STAGES * P_STAGE_BYTES, "the last tile's staging must fit the operand ring");
 static_assert(P_SMEM <= 232448, "shared memory of the paired GEMM exceeds what an SM offers");
 static_assert(sizeof(GemmParams) <= 4096, "kernel parameters must stay within the classic 4 KB limit");
 static constexpr int P_THREADS = 192;
@@ -188,8 +189,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm2_bf16_tn_kernel(const __gri
       tc_fence_after_sync();
       if (it == 0 && warp == 2 && lane == 0) stamp(4);
       const uint32_t taddr = tmem_base + acc * P_BN + (static_cast<uint32_t>(q * 32) << 16);
-      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane, P.err + 1,
-                          epi_stage + q * EPI_STAGE_BYTES_PER_WARP);
+      // During this CTA's last tile nothing reads or fills the operand ring any more (the accumulator barrier says
+      // every MMA of the pair has completed), so each warp stages its whole 32 x 256 part of the tile there (eight
+      // blocks) and all of its TMA stores are in flight at once. This part of a launch is never hidden by a next tile.
+      const bool last = tile + num_pairs >= P.total_tiles;
+      uint8_t *stage = last ? smem + q * (8 * 4096) : epi_stage + q * EPI_STAGE_BYTES_PER_WARP;
+      epilogue_tile<P_BN>(P.p[prob], m0 + static_cast<int>(rank) * P_BM, n0, taddr, q * 32 + lane, P.err + 1, stage,
+                          last ? 8 : 2);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));

@@ -40,13 +40,14 @@ __device__ __forceinline__ void stage_and_store_chunk(const CUtensorMap *tm, uin
 struct Stage16 {
   uint8_t *stage;
   int lane;
-  int n;  // blocks handed to the TMA unit so far
+  int n;   // blocks handed to the TMA unit so far
+  int nb;  // blocks available (a power of two)
   __device__ __forceinline__ uint8_t *acquire() {
-    if (n >= 2) {  // the store that last used this block has read it
+    if (n >= nb) {  // every store but the latest has read its block, the one that last used this block among them
       if (lane == 0) bulk_wait_read<1>();
       __syncwarp();
     }
-    return stage + (n & 1) * 4096;
+    return stage + (n & (nb - 1)) * 4096;
   }
   __device__ __forceinline__ void release(const CUtensorMap *tm, uint8_t *buf, int x, int y, bool issue) {
     fence_proxy_async_smem();
@@ -63,10 +64,12 @@ struct Stage16 {
   }
 };
 
-// stage: this warp's staging blocks (paired kernel) or nullptr (direct global stores).
+// stage: this warp's staging blocks (paired kernel) or nullptr (direct global stores); nblk: how many 4 KB blocks it
+// holds (a power of two, at least 2). With two blocks a chunk waits for the TMA unit to have read the chunk before
+// last; with eight (the operand ring, free during a CTA's last tile) a whole tile is staged without waiting.
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int n0, uint32_t taddr, int lane_row,
-                                              int *sat_counter, uint8_t *stage = nullptr) {
+                                              int *sat_counter, uint8_t *stage = nullptr, int nblk = 2) {
   const bool second = n0 >= pb.n_split;
   const EpiSeg &sg = second ? pb.seg[1] : pb.seg[0];
   const int nrel = n0 - (second ? pb.n_split : 0);  // segment-relative first column of this tile
@@ -100,7 +103,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
     case EPI_STORE_BF16: {
       if (stage != nullptr && sg.tma_out) {
         const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
-        Stage16 st{stage, lane, 0};
+        Stage16 st{stage, lane, 0, nblk};
         uint8_t *buf = nullptr;
         tc_ld_32x32(taddr, r);  // chunk c + 1 is loaded while chunk c is staged
 #pragma unroll 1
@@ -145,7 +148,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         tc_ld_32x32(taddr, r);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          if (c >= 2) {  // the store that last used this block has read it
+          if (c >= nblk) {  // the store that last used this block has read it
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
           }
@@ -154,7 +157,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (c + 1 < BN / 32) tc_ld_32x32(taddr + (c + 1) * 32, r);
-          stage_and_store_chunk<false>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
+          stage_and_store_chunk<false>(&sg.tm_out, stage + (c & (nblk - 1)) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
                                        y < pb.M);
         }
         if (lane == 0) bulk_wait_read<0>();  // the next tile's epilogue writes these blocks again
@@ -186,7 +189,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
           float4 g[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) g[j] = __ldg(g4 + c * 8 + j);
-          if (c >= 2) {
+          if (c >= nblk) {
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
           }
@@ -200,7 +203,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
             v[4 * j + 3] = g[j].w * __uint_as_float(r[4 * j + 3]);
           }
           if (c + 1 < BN / 32) tc_ld_32x32(taddr + (c + 1) * 32, r);
-          stage_and_store_chunk<true>(&sg.tm_out, stage + (c & 1) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
+          stage_and_store_chunk<true>(&sg.tm_out, stage + (c & (nblk - 1)) * 4096, v, lane, sg.col0 + nrel + c * 32, y,
                                       y < pb.M);
         }
         if (lane == 0) bulk_wait_read<0>();
@@ -234,7 +237,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         uint32_t u[32];
         if (stage != nullptr && sg.tma_out) {
           const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
-          Stage16 st{stage, lane, 0};
+          Stage16 st{stage, lane, 0, nblk};
           uint8_t *buf = nullptr;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -411,7 +414,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmProblem &pb, int m0, int
         }
         if (stage != nullptr && sg.tma_out) {
           const int lane = lane_row & 31, y = m0 + (lane_row & ~31);
-          Stage16 st{stage, lane, 0};
+          Stage16 st{stage, lane, 0, nblk};
           uint8_t *buf = nullptr;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
