@@ -999,7 +999,7 @@ def run_ours(args):
                     "frac": a1 / peaks["bf16_sustained"],
                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this very shape under ncu: a
                     # figure quoted from the committed capture, not measured by this run; algorithmic bytes 264.2 MB
-                    "traffic": 242.3e6, "traffic_source": "profiles/gemm2_bf16_tn_1536x27648x3072.md (ncu, one launch)",
+                    "traffic": 243.6e6, "traffic_source": "profiles/gemm2_bf16_tn_1536x27648x3072.md (ncu, one launch)",
                     "launches": len(lin1), "avg_launch_ms": ms1,
                     "flops_per_launch": f1, "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                     "frac_of_burst_peak": a1 / peaks["bf16"]}

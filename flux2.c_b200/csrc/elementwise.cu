@@ -179,9 +179,9 @@ __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__
   for (int i = threadIdx.x; i < S * K / 4; i += blockDim.x)
     reinterpret_cast<float4 *>(xs)[i] = reinterpret_cast<const float4 *>(x)[i];
   __syncthreads();
-  const int r0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * GEMV_ROWS;
   const int lane = threadIdx.x & 31;
-  if (r0 >= R) return;
+  // Persistent blocks: x is staged once per block, then the block walks over groups of 8 * GEMV_ROWS rows.
+  for (int r0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * GEMV_ROWS; r0 < R; r0 += gridDim.x * 8 * GEMV_ROWS) {
   const uint4 *wr[GEMV_ROWS];
 #pragma unroll
   for (int q = 0; q < GEMV_ROWS; ++q) {
@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(256) gemv_multi_kernel(const __nv_bfloat16 *__
       if (silu_out) v = v / (1.0f + expf(-v));
       if (lane == 0 && r0 + q < R) y[static_cast<size_t>(s) * R + r0 + q] = v;
     }
+  }
 }
 
 int launch_timestep_sincos(const float *t, int S, int dim, float *out, cudaStream_t st) {
@@ -247,7 +248,12 @@ int elementwise_init() {
 int launch_gemv_multi(const void *W, const float *x, float *y, int R, int K, int silu_out, int f16, cudaStream_t st) {
   if (K % 8 || K > 12288) return -1;
   const size_t smem = static_cast<size_t>(GEMV_S) * K * 4;
-  gemv_multi_kernel<GEMV_S><<<(R + 8 * GEMV_ROWS - 1) / (8 * GEMV_ROWS), 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int groups = (R + 8 * GEMV_ROWS - 1) / (8 * GEMV_ROWS);
+  const int grid = groups < 2 * sms ? groups : 2 * sms;  // two blocks per SM (registers), each staging x once
+  gemv_multi_kernel<GEMV_S><<<grid, 256, smem, st>>>(reinterpret_cast<const __nv_bfloat16 *>(W), x, y, R, K,
                                                              silu_out, f16);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
