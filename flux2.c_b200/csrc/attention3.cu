@@ -43,7 +43,7 @@ static constexpr int OFF_K = QTILES * 32768;   // slot s at OFF_K + s * 32768
 static constexpr int OFF_V = OFF_K + 2 * 32768;
 static constexpr int OFF_BAR = OFF_V + 2 * 32768;
 static constexpr int OFF_X = OFF_BAR + 256;    // row-statistics exchange between the two column halves
-static constexpr int X_BYTES = (2 * 2 * 2 * 128 + 2 * 2 * 128) * 4;  // values [tile][half][parity][row], flags [tile][half][row]
+static constexpr int X_BYTES = 2 * 2 * 128 * 8;  // one 8-byte slot per [tile][half][row]
 static constexpr int SMEM = OFF_X + X_BYTES + 1024;
 static constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -56,9 +56,50 @@ struct Bars {
 };
 
 struct Xchg {
-  float val[QTILES][2][2][TILE];  // [tile][half][iteration parity][row]
-  int seq[QTILES][2][TILE];       // [tile][half][row]: number of values this thread has published
+  // [tile][half][row]: the thread's latest row maximum (low word) and its number, 1-based (high word), published
+  // with ONE 8-byte store so that a reader never sees a number without its value
+  unsigned long long slot[QTILES][2][TILE];
 };
+
+// p = 2^(s * scale - m) for this thread's 64 scores, packed to 16-bit pairs and written to 32 columns of TMEM;
+// returns their sum. Laid out by hand like the loop of attention2.cu: every statement is a volatile asm, each
+// exponential is followed by the multiply-add that forms the argument LEAD elements ahead and by the add / convert
+// that consume the pair issued LAG pairs earlier.
+template <bool F16>
+__device__ __forceinline__ float exps64_lagged(const uint32_t (&s)[2][32], float scale, float neg_m, uint32_t p_addr) {
+  constexpr int LEAD = 8, LAG = 4, NE = 64;
+  float x[LEAD], p0[LAG], p1[LAG];
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t pk[16];
+#pragma unroll
+  for (int e = 0; e < LEAD; ++e) x[e] = fmaf_pinned(__uint_as_float(s[e >> 5][e & 31]), scale, neg_m);
+#pragma unroll
+  for (int i = 0; i < NE / 2 + LAG; ++i) {
+    const int e = 2 * i;
+    const int c = i - LAG;  // pair consumed in this slot
+    float t = 0.f, q0 = 0.f, q1 = 0.f;
+    if (c >= 0) {
+      q0 = p0[c % LAG];
+      q1 = p1[c % LAG];
+    }
+    if (i < NE / 2) {
+      p0[i % LAG] = ex2f_pinned(x[e % LEAD]);
+      if (e + LEAD < NE) x[e % LEAD] = fmaf_pinned(__uint_as_float(s[(e + LEAD) >> 5][(e + LEAD) & 31]), scale, neg_m);
+    }
+    if (c >= 0) t = addf_pinned(q0, q1);
+    if (i < NE / 2) {
+      p1[i % LAG] = ex2f_pinned(x[(e + 1) % LEAD]);
+      if (e + 1 + LEAD < NE)
+        x[(e + 1) % LEAD] = fmaf_pinned(__uint_as_float(s[(e + 1 + LEAD) >> 5][(e + 1 + LEAD) & 31]), scale, neg_m);
+    }
+    if (c >= 0) {
+      sum4[c & 3] = addf_pinned(sum4[c & 3], t);
+      pk[c & 15] = pack_16x2_pinned<F16>(q0, q1);
+      if ((c & 15) == 15) tc_st_32x16(p_addr + (c >> 4) * 16, pk);
+    }
+  }
+  return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
 
 // 32 lanes x 32 consecutive f32 columns (ptx.cuh) is used for S and O; P is written 16 columns at a time.
 }  // namespace a3
@@ -97,7 +138,7 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
     B->abort_flag = 0;
     mbar_fence_init();
   }
-  for (int i = threadIdx.x; i < QTILES * 2 * TILE; i += THREADS) (&X->seq[0][0][0])[i] = 0;
+  for (int i = threadIdx.x; i < QTILES * 2 * TILE; i += THREADS) (&X->slot[0][0][0])[i] = 0ull;
   if (warp == 1) tmem_alloc(&B->tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
@@ -224,27 +265,26 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
     const uint32_t o_addr = tmem + lane_base + 256 + t * 128 + half * 64;  // its half of the row's output columns
     const float scale = P.scale_log2;
     const bool f16 = P.f16 != 0;
-    volatile float *x_mine = &X->val[t][half][0][row];
-    volatile float *x_other = &X->val[t][half ^ 1][0][row];
-    volatile int *seq_mine = &X->seq[t][half][row];
-    volatile int *seq_other = &X->seq[t][half ^ 1][row];
+    volatile unsigned long long *slot_mine = &X->slot[t][half][row];
+    volatile unsigned long long *slot_other = &X->slot[t][half ^ 1][row];
 
-    // Publishes `v` as this thread's value number n (1-based) and returns the partner's value number n.
+    // Publishes `v` as this thread's value number n (1-based) and returns the partner's value number n. The partner
+    // cannot publish number n + 1 before this thread has arrived on p_ready for step n, i.e. after this read.
     auto exchange = [&](float v, int n, bool &ok) -> float {
-      x_mine[(n & 1) * TILE] = v;
-      __threadfence_block();
-      *seq_mine = n;
-      if (*seq_other < n) {
+      *slot_mine = (static_cast<unsigned long long>(n) << 32) | __float_as_uint(v);
+      unsigned long long o = *slot_other;
+      if (static_cast<int>(o >> 32) < n) {
         const long long t0 = clock64();
-        while (*seq_other < n) {
+        while (true) {
+          o = *slot_other;
+          if (static_cast<int>(o >> 32) >= n) break;
           if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) {
             ok = false;
             return v;
           }
         }
       }
-      __threadfence_block();
-      return x_other[(n & 1) * TILE];
+      return __uint_as_float(static_cast<uint32_t>(o));
     };
 
     float m_ref = -1e30f, l = 0.f;
@@ -321,20 +361,7 @@ __global__ void __launch_bounds__(a3::THREADS, 1) attn3_fwd_kernel(const __grid_
       }
       if (tr) stamp(j, 7 + 5 * t);
       // p = 2^(s*scale - m_ref); 16-bit pairs: keys 2c, 2c+1 of the tile in column c of S
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2f_(fmaf(__uint_as_float(s[c][2 * i]), scale, -m_ref));
-          const float p1 = ex2f_(fmaf(__uint_as_float(s[c][2 * i + 1]), scale, -m_ref));
-          sum4[i & 3] += p0 + p1;
-          pk[i] = pack_16x2(p0, p1, f16);
-        }
-        tc_st_32x16(p_addr + c * 16, pk);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l += f16 ? exps64_lagged<true>(s, scale, -m_ref, p_addr) : exps64_lagged<false>(s, scale, -m_ref, p_addr);
       if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();
