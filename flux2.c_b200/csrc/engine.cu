@@ -207,13 +207,20 @@ static void parallel_memcpy(void *dst, const void *src, size_t bytes, int thread
   }
   const size_t per = ((bytes + threads - 1) / threads + 4095) & ~static_cast<size_t>(4095);
   std::vector<std::thread> pool;
+  size_t handed = std::min(per, bytes);  // bytes [0, handed) are this thread's own part
   for (int t = 1; t < threads; ++t) {
     const size_t o = per * t;
     if (o >= bytes) break;
     const size_t n = std::min(per, bytes - o);
-    pool.emplace_back([=] { memcpy(static_cast<char *>(dst) + o, static_cast<const char *>(src) + o, n); });
+    try {
+      pool.emplace_back([=] { memcpy(static_cast<char *>(dst) + o, static_cast<const char *>(src) + o, n); });
+    } catch (...) {  // no thread to be had: this thread copies the rest itself (nothing may throw through the C ABI)
+      break;
+    }
+    handed = o + n;
   }
   memcpy(dst, src, std::min(per, bytes));
+  if (handed < bytes) memcpy(static_cast<char *>(dst) + handed, static_cast<const char *>(src) + handed, bytes - handed);
   for (auto &th : pool) th.join();
 }
 

@@ -186,6 +186,22 @@ void note(WorkerResult &r, int rc) {
   }
 }
 
+// Starts a host thread; a failure to create one becomes an error of that member instead of an exception (nothing may
+// throw through the C ABI).
+template <class F>
+bool spawn(std::thread &t, WorkerResult &r, F &&f) {
+  try {
+    t = std::thread(std::forward<F>(f));
+    return true;
+  } catch (...) {
+    if (!r.rc) {
+      r.rc = FLUX_CUDA_ERR_NOMEM;
+      r.msg = "could not start a host thread for this GPU";
+    }
+    return false;
+  }
+}
+
 int pair_buffers(flux_cuda_group *g, size_t floats) {
   if (g->inbox_floats >= floats) return 0;
   for (int r = 0; r < 2; ++r) {
@@ -283,10 +299,11 @@ int flux_cuda_group_load_safetensors(flux_cuda_group *g, const char *path) {
   const int n = static_cast<int>(g->ctx.size());
   std::vector<WorkerResult> res(n);
   std::vector<flux_cuda_model *> loaded(n, nullptr);
-  std::vector<std::thread> th;
+  std::vector<std::thread> th(n);
   for (int r = 0; r < n; ++r)
-    th.emplace_back([&, r]() { note(res[r], flux_cuda_model_load_safetensors(g->ctx[r], path, &loaded[r])); });
-  for (auto &t : th) t.join();
+    spawn(th[r], res[r], [&, r]() { note(res[r], flux_cuda_model_load_safetensors(g->ctx[r], path, &loaded[r])); });
+  for (auto &t : th)
+    if (t.joinable()) t.join();
   for (int r = 0; r < n; ++r)
     if (res[r].rc) {
       for (flux_cuda_model *m : loaded) flux_cuda_model_free(m);
@@ -343,9 +360,9 @@ int flux_cuda_group_sample_batch(flux_cuda_group *g, const flux_cuda_sample_para
       return FLUX_CUDA_ERR_MODEL;
     }
   std::vector<WorkerResult> res(n);
-  std::vector<std::thread> th;
+  std::vector<std::thread> th(n);
   for (int r = 0; r < n && r < n_images; ++r)
-    th.emplace_back([&, r]() {
+    spawn(th[r], res[r], [&, r]() {
       // image i runs on member i % n; each member keeps one sampler for the whole batch
       std::vector<flux_cuda_ref_shape> shapes;
       std::vector<const float *> lat;
@@ -363,7 +380,8 @@ int flux_cuda_group_sample_batch(flux_cuda_group *g, const flux_cuda_sample_para
       }
       flux_cuda_sampler_free(s);
     });
-  for (auto &t : th) t.join();
+  for (auto &t : th)
+    if (t.joinable()) t.join();
   for (int r = 0; r < n; ++r)
     if (res[r].rc) {
       set_error("GPU member %d: %s", r, res[r].msg.c_str());
@@ -398,7 +416,7 @@ int flux_cuda_group_sample_cfg_pair(flux_cuda_group *g, const flux_cuda_sample_p
   WorkerResult res[2];
   std::thread th[2];
   for (int r = 0; r < 2; ++r)
-    th[r] = std::thread([&, r]() {
+    if (!spawn(th[r], res[r], [&, r]() {
       flux_cuda_ctx *c = g->ctx[r];
       const int peer = r ^ 1;
       const float coef = r == 0 ? p->guidance : 1.0f - p->guidance;  // member 0 runs the conditional pass
@@ -434,9 +452,10 @@ int flux_cuda_group_sample_cfg_pair(flux_cuda_group *g, const flux_cuda_sample_p
       // member 0 returns the latent; member 1 only waits for its queue and reports kernel errors
       if (s) note(res[r], flux_cuda_sampler_download(s, r == 0 ? latent_out : nullptr, nullptr));
       flux_cuda_sampler_free(s);
-    });
-  th[0].join();
-  th[1].join();
+    }))
+      flux_cuda_rendezvous_abandon(g->rv, r);  // the other member must not wait for a thread that never started
+  for (int r = 0; r < 2; ++r)
+    if (th[r].joinable()) th[r].join();
   g->seq = seq0 + p->num_steps;
   for (int r = 0; r < 2; ++r)
     if (res[r].rc) {
