@@ -10,6 +10,7 @@ struct alignas(64) AttnParams {
   CUtensorMap tm;          // [batch, seq, ld] bf16 view of the fused projection output; box 64 x 128 x 1
   CUtensorMap tm_out;      // [batch, seq, out_ld] view of the output; box 64 x 32 x 1 (attention2.cu, when tma_out)
   int tma_out;
+  int spec;                // attention2.cu: exponentials against the current reference maximum first (see there)
   int seq, batch, heads;
   int q_col, k_col, v_col; // first column of head 0 of Q / K / V inside a row of that buffer
   void *out;               // bf16 [batch*seq, out_ld]; head h goes to columns out_col + 128*h ..

@@ -16,11 +16,16 @@
 //   warp 0      TMA producer: both Q tiles once, then a two-stage ring of K/V tiles (128 keys each);
 //   warp 1      MMA issuer: S_t = Q_t K^T (both operands K-major in shared memory) and
 //               O_t += P_t V (A = P_t from TMEM, B = V as an MN-major shared-memory operand);
-//   warps 2-5   softmax of tile a, warps 6-9 of tile b: one thread per query row (its TMEM lane).
-//               Online softmax in base 2 with f32 statistics. The running maximum is only raised when a
-//               tile exceeds it by more than 8 (p stays below 2^8), so the accumulator in TMEM rarely has
-//               to be rescaled; when it does, the row's thread multiplies its O row in place
-//               (tcgen05.ld / tcgen05.st) before it releases P for the next P V.
+//   warps 4-7   softmax of tile a, warps 8-11 of tile b: one thread per query row (its TMEM lane). Warps 2-3 only
+//               give their registers to the softmax warps.
+//               Online softmax in base 2 with f32 statistics. The reference maximum of a row is only raised when a
+//               tile exceeds it by more than 8 (p stays below 2^8), so the accumulator in TMEM rarely has to be
+//               rescaled; when it does, the row's thread multiplies its O row in place (tcgen05.ld / tcgen05.st)
+//               before it releases P for the next P V. After the first tile the exponentials are taken against the
+//               current reference right away and the tile's own maximum is not computed at all unless a partial sum
+//               says that a probability may have left that range (then the tile is redone exactly from the scores
+//               still in registers): the 128 comparisons per row and tile leave the serial chain
+//               S -> softmax -> P V -> next S that bounds this kernel.
 #include "attention.cuh"
 #include "gemm.cuh"
 #include "launch.cuh"
@@ -50,8 +55,11 @@ static constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 // asm, which keeps this order): each exponential is followed by the multiply-add that forms the argument LEAD
 // elements ahead and by the add / convert that consume the pair issued LAG pairs earlier - never by an instruction
 // that needs a result still in flight.
+// `smax` returns the largest of the four partial sums (32 probabilities each): no single probability can be above it,
+// which is the overflow check of the speculative pass at no cost inside the loop.
 template <bool F16>
-__device__ __forceinline__ float exps_row_lagged(const uint32_t (&s)[4][32], float scale, float neg_m, uint32_t s_addr) {
+__device__ __forceinline__ float exps_row_lagged(const uint32_t (&s)[4][32], float scale, float neg_m, uint32_t s_addr,
+                                                 float &smax) {
   constexpr int LEAD = 8, LAG = 4;
   float x[LEAD], p0[LAG], p1[LAG];
   float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -84,6 +92,7 @@ __device__ __forceinline__ float exps_row_lagged(const uint32_t (&s)[4][32], flo
       if ((c & 31) == 31) tc_st_32x32(s_addr + (c >> 5) * 32, pk);
     }
   }
+  smax = fmaxf(fmaxf(sum4[0], sum4[1]), fmaxf(sum4[2], sum4[3]));
   return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 }
 
@@ -301,42 +310,60 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn2_fwd_kernel(const __grid_
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= limit || !((mw[c] >> i) & 1u)) s[c][i] = __float_as_uint(-1e30f);
       }
-      // four independent chains for the maximum of the row's 128 scores (one chain would cost 128 dependent steps)
-      float m4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s[c][i]));
-      const float mloc = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale;
-      // Raise the reference maximum only when this tile exceeds it by more than the threshold.
-      const bool raise = mloc > m_ref + RESCALE_THRESHOLD;
-      if (j == 0) {
-        m_ref = mloc;
-      } else if (__any_sync(0xffffffffu, raise)) {
-        // rescale the accumulator row in TMEM once P V(j-1) has completed
-        ok = mbar_wait_warp(&B->o_done[t], (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const float alpha = raise ? ex2f_(m_ref - mloc) : 1.0f;
-        uint32_t o[32];
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tc_ld_32x32(o_addr + c * 32, o);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc_st_32x32(o_addr + c * 32, o);
-        }
-        tc_wait_st();
-        if (raise) {
-          l *= alpha;
-          m_ref = mloc;
-        }
+      // Speculative pass: the exponentials are taken against the CURRENT reference maximum right away, and the row
+      // maximum of this tile - which is only needed to decide whether the reference has to be raised - is not
+      // computed at all unless some probability may have come out above 2^8 (the bound the lazy rescaling keeps: a
+      // partial sum of 32 probabilities above 2^8 is the sign). In that
+      // rare case, and for the first tile, the exact path below redoes the tile from the scores still in registers.
+      float tile_sum = 0.f, smax = 0.f;
+      bool exact = j == 0 || !P.spec;
+      if (!exact) {
+        tile_sum = f16 ? exps_row_lagged<true>(s, scale, -m_ref, s_addr, smax)
+                       : exps_row_lagged<false>(s, scale, -m_ref, s_addr, smax);
+        exact = __any_sync(0xffffffffu, !(smax <= 256.0f));  // also catches inf / NaN
+        if (exact) tc_wait_st();  // the speculative P is overwritten below
       }
-      if (tr) stamp(j, 7 + 5 * t);
-      // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
-      // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
-      l += f16 ? exps_row_lagged<true>(s, scale, -m_ref, s_addr) : exps_row_lagged<false>(s, scale, -m_ref, s_addr);
+      if (exact) {
+        // four independent chains for the maximum of the row's 128 scores (one chain would cost 128 dependent steps)
+        float m4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s[c][i]));
+        const float mloc = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale;
+        // Raise the reference maximum only when this tile exceeds it by more than the threshold - or, when the
+        // speculative pass sent us here, by anything at all: a tile whose scores sit a few bits above the reference
+        // without reaching the threshold would otherwise fail the check of every following tile too.
+        const bool raise = mloc > m_ref + ((P.spec && j > 0) ? 0.0f : RESCALE_THRESHOLD);
+        if (j == 0) {
+          m_ref = mloc;
+        } else if (__any_sync(0xffffffffu, raise)) {
+          // rescale the accumulator row in TMEM once P V(j-1) has completed
+          ok = mbar_wait_warp(&B->o_done[t], (j - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const float alpha = raise ? ex2f_(m_ref - mloc) : 1.0f;
+          uint32_t o[32];
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tc_ld_32x32(o_addr + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc_st_32x32(o_addr + c * 32, o);
+          }
+          tc_wait_st();
+          if (raise) {
+            l *= alpha;
+            m_ref = mloc;
+          }
+        }
+        if (tr) stamp(j, 7 + 5 * t);
+        // p = 2^(s*scale - m_ref); 16-bit pairs into the first 64 columns of S (keys 2c, 2c+1 in column c)
+        tile_sum = f16 ? exps_row_lagged<true>(s, scale, -m_ref, s_addr, smax)
+                       : exps_row_lagged<false>(s, scale, -m_ref, s_addr, smax);
+      }
+      l += tile_sum;
       if (tr) stamp(j, 8 + 5 * t);
       tc_wait_st();
       tc_fence_before_sync();
@@ -450,6 +477,11 @@ int attn2_make_params(AttnParams *p, const void *qkv, int batch, int seq, long l
     const char *e = getenv("FLUX_CUDA_ATTN_TMA_OUT");
     return e ? atoi(e) : 1;
   }();
+  static const int spec_env = [] {
+    const char *e = getenv("FLUX_CUDA_ATTN_SPEC");
+    return e ? atoi(e) : 1;
+  }();
+  p->spec = spec_env;
   p->tma_out = 0;
   if (tma_out_env) {
     cuuint64_t odims[3] = {static_cast<cuuint64_t>(out_ld), static_cast<cuuint64_t>(seq),

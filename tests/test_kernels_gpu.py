@@ -34,25 +34,66 @@ def test_attention_matches_torch(fx, ctx, batch, seq, heads, sharp, dtype):
     assert _rel(out[:, :hid].float(), ref) < (2e-3 if dtype == torch.float16 else 1e-2)  # 16-bit P and output
 
 
+def _attention_ref(qkv, batch, seq, heads):
+    hid = heads * 128
+    q, k, v = [t.float().reshape(batch, seq, heads, 128).transpose(1, 2) for t in qkv.split(hid, dim=1)]
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(128.0)
+    return (torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(batch * seq, hid)
+
+
 @pytest.mark.parametrize("batch,seq,heads", [(1, 300, 3), (1, 1536, 24), (2, 200, 2)])
-def test_attention_previous_generation_matches_torch(fx, batch, seq, heads, monkeypatch):
-    """FLUX_CUDA_ATTN=2 selects the kernel with four softmax warps per query tile (attention2.cu), kept as the
-    yardstick the current one is measured against."""
-    monkeypatch.setenv("FLUX_CUDA_ATTN", "2")
-    c2 = fx.Context(0)
+def test_attention_eight_warp_variant_matches_torch(fx, batch, seq, heads, monkeypatch):
+    """FLUX_CUDA_ATTN=3 selects the variant with eight softmax warps per query tile (attention3.cu), kept for
+    comparison with the default kernel (attention2.cu)."""
+    monkeypatch.setenv("FLUX_CUDA_ATTN", "3")
+    c3 = fx.Context(0)
     try:
         hid = heads * 128
         g = torch.Generator(device="cuda").manual_seed(seq + heads)
         qkv = torch.randn(batch * seq, 3 * hid, device="cuda", generator=g).half()
         out = torch.zeros(batch * seq, hid, device="cuda", dtype=torch.float16)
         torch.cuda.synchronize()
-        c2.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid, 0, f16=True)
-        c2.sync()
-        q, k, v = [t.float().reshape(batch, seq, heads, 128).transpose(1, 2) for t in qkv.split(hid, dim=1)]
-        ref = (torch.softmax((q @ k.transpose(-1, -2)) / math.sqrt(128.0), dim=-1) @ v).transpose(1, 2)
-        assert _rel(out.float(), ref.reshape(batch * seq, hid)) < 2e-3
+        c3.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid, 0, f16=True)
+        c3.sync()
+        assert _rel(out.float(), _attention_ref(qkv, batch, seq, heads)) < 2e-3
     finally:
-        c2.close()
+        c3.close()
+
+
+@pytest.mark.parametrize("spec", ["1", "0"])
+@pytest.mark.parametrize("profile", ["growing", "plateau", "spikes"])
+def test_attention_when_the_row_maximum_moves(fx, profile, spec, monkeypatch):
+    """Key tiles whose scores climb from tile to tile: the reference maximum has to be raised and the accumulator
+    rescaled again and again ("growing"), the scores of the later tiles sit a few bits above the first tile's without
+    reaching the rescaling threshold ("plateau"), single keys far above everything else appear late ("spikes").
+    With FLUX_CUDA_ATTN_SPEC=1 (the default) the kernel takes the exponentials against the current reference first and
+    falls back to the exact path when its overflow check fails; =0 is the exact path on every tile."""
+    monkeypatch.setenv("FLUX_CUDA_ATTN_SPEC", spec)
+    c = fx.Context(0)
+    try:
+        batch, seq, heads = 1, 1024, 2
+        hid = heads * 128
+        g = torch.Generator(device="cuda").manual_seed(7)
+        q = torch.randn(seq, hid, device="cuda", generator=g)
+        k = torch.randn(seq, hid, device="cuda", generator=g)
+        v = torch.randn(seq, hid, device="cuda", generator=g)
+        tile = torch.arange(seq, device="cuda") // 128
+        if profile == "growing":
+            k = k * (1.0 + 1.5 * tile)[:, None]            # the score spread grows ~2 bits per tile
+        elif profile == "plateau":
+            k = k * torch.where(tile == 0, 0.2, 2.5)[:, None]  # later tiles a few bits above the first, not 8
+        else:
+            k[700] *= 12.0
+            k[1000] *= 25.0
+        qkv = torch.cat([q, k, v], dim=1).half()
+        out = torch.zeros(seq, hid, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        c.attention(qkv.data_ptr(), batch, seq, 3 * hid, 0, hid, 2 * hid, heads, out.data_ptr(), hid, 0, f16=True)
+        c.sync()
+        assert torch.isfinite(out.float()).all()
+        assert _rel(out.float(), _attention_ref(qkv, batch, seq, heads)) < 3e-3
+    finally:
+        c.close()
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
