@@ -293,33 +293,6 @@ __device__ __forceinline__ uint32_t pack_16x2_pinned(float lo, float hi) {
   else asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
   return y;
 }
-// Two exponentials per special-function-unit instruction: 2^x of a packed f16 pair, result packed f16 (which is the
-// format the probabilities are stored in, so no conversion follows). The argument is rounded to f16 first: an absolute
-// error of at most 2^-12 for |x| < 1 (where the large probabilities are) growing to 2^-8 at |x| = 16.
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-// acc += the two halves of a packed f16 pair, in f32 (mixed-precision add: no conversion instruction)
-__device__ __forceinline__ void add_f16x2_to_f32(uint32_t v, float &acc_lo, float &acc_hi) {
-  unsigned short lo, hi;
-  asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
-  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc_lo) : "h"(lo));
-  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc_hi) : "h"(hi));
-}
-// 2^x on the FMA pipe: x is split into the nearest integer n (exponent bits, by the 1.5 * 2^23 rounding trick) and
-// f = x - n in [-0.5, 0.5]; 2^f is a cubic with relative error 7.5e-5 (the 16-bit values it feeds round 6x coarser).
-// Valid for x in [-126, 126]; smaller x are clamped (the result is ~1e-38, i.e. zero for every use here).
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float xr = x + 12582912.0f;
-  const float f = x - (xr - 12582912.0f);
-  float p = fmaf(0.055171459913253784f, f, 0.2426108568906784f);
-  p = fmaf(p, f, 0.6932609677314758f);
-  p = fmaf(p, f, 0.9999281167984009f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
-}
 // 32 lanes x 32 consecutive 32-bit columns, registers -> TMEM.
 __device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -399,11 +372,6 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
 
