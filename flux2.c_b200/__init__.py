@@ -168,6 +168,10 @@ def _declare(L):
     L.flux_cuda_sampler_apply_velocity.argtypes = [c_void_p, c_void_p, c_int]
     L.flux_cuda_sampler_download.restype = c_int
     L.flux_cuda_sampler_download.argtypes = [c_void_p, c_void_p, c_void_p]
+    L.flux_cuda_sampler_stage_inputs.restype = c_int
+    L.flux_cuda_sampler_stage_inputs.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p)]
+    L.flux_cuda_sampler_download_async.restype = c_int
+    L.flux_cuda_sampler_download_async.argtypes = [c_void_p, c_void_p]
     L.flux_cuda_sampler_last_run.restype = c_int
     L.flux_cuda_sampler_last_run.argtypes = [c_void_p, fp, ctypes.POINTER(c_ll)]
     L.flux_cuda_sampler_set_profiling.restype = c_int
@@ -751,6 +755,16 @@ class Sampler:
 
     def download(self, latent_ptr, velocities_ptr=None):
         check(lib().flux_cuda_sampler_download(self.handle, latent_ptr, velocities_ptr))
+
+    def stage_inputs(self, z0_ptr, ctx_ptr, ctx_uncond_ptr=None, ref_ptrs=()):
+        """Inputs of the NEXT image, copied on a second stream while the current image runs; the next run() picks
+        them up. The (pinned) host buffers must stay valid until that run has been synchronised."""
+        refs = (ctypes.c_void_p * max(1, len(ref_ptrs)))(*ref_ptrs)
+        check(lib().flux_cuda_sampler_stage_inputs(self.handle, z0_ptr, ctx_ptr, ctx_uncond_ptr, refs))
+
+    def download_async(self, latent_ptr):
+        """Queues the device -> host copy of the latent behind the run; Context.sync() waits for it."""
+        check(lib().flux_cuda_sampler_download_async(self.handle, latent_ptr))
 
     def last_run(self):
         ms = ctypes.c_float()

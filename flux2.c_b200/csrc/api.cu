@@ -128,6 +128,10 @@ void flux_cuda_ctx_destroy(flux_cuda_ctx *ctx) {
     cudaStreamDestroy(ctx->stream);
   }
   fx::upload_ring_release(ctx);
+  if (ctx->copy_stream) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+  }
   if (ctx->err_dev) cudaFree(ctx->err_dev);
   if (ctx->err_host) cudaFreeHost(ctx->err_host);
   if (ctx->gn_scratch) cudaFree(ctx->gn_scratch);
@@ -532,6 +536,13 @@ int flux_cuda_sampler_apply_velocity(flux_cuda_sampler *s, const float *v_dev, i
 }
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out) {
   return sampler_download(s, latent_out, velocities_out);
+}
+int flux_cuda_sampler_stage_inputs(flux_cuda_sampler *s, const float *z0, const float *ctx, const float *ctx_uncond,
+                                   const float *const *ref_latents) {
+  return sampler_stage_inputs(s, z0, ctx, ctx_uncond, ref_latents);
+}
+int flux_cuda_sampler_download_async(flux_cuda_sampler *s, float *latent_out) {
+  return sampler_download_async(s, latent_out);
 }
 int flux_cuda_sampler_latent_device(flux_cuda_sampler *s, const float **latent_dev) {
   if (!s || !latent_dev) return FLUX_CUDA_ERR_ARG;

@@ -21,6 +21,7 @@ struct flux_cuda_ctx {
   int device = 0;
   int num_sms = 0;
   cudaStream_t stream = nullptr;  // owned
+  cudaStream_t copy_stream = nullptr;  // owned; created by the first staged upload (inputs of the next image)
   int *err_dev = nullptr;         // two device words: [0] first kernel error (0 = none), [1] saturated f16 stores
   int *err_host = nullptr;        // pinned mirror of both
   long long saturated = 0;        // saturated f16 stores seen by the synchronisations so far

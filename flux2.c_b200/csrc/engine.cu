@@ -459,11 +459,14 @@ void sampler_free(flux_cuda_sampler *s) {
   if (s->ws) {
     cudaSetDevice(s->model->ctx->device);
     cudaStreamSynchronize(s->model->ctx->stream);
+    if (s->model->ctx->copy_stream) cudaStreamSynchronize(s->model->ctx->copy_stream);
     for (void *p : s->ws->allocs) cudaFree(p);
     for (cudaEvent_t e : s->ws->prof_events) cudaEventDestroy(e);
     for (auto &g : s->ws->graphs) cudaGraphExecDestroy(g.exec);
     if (s->ws->ev0) cudaEventDestroy(s->ws->ev0);
     if (s->ws->ev1) cudaEventDestroy(s->ws->ev1);
+    if (s->ws->ev_staged) cudaEventDestroy(s->ws->ev_staged);
+    if (s->ws->ev_stage_free) cudaEventDestroy(s->ws->ev_stage_free);
     delete s->ws;
   }
   delete s;
@@ -901,6 +904,83 @@ static int enqueue_steps(flux_cuda_model *m, Workspace *ws, int num_steps, int f
   return rc;
 }
 
+// Inputs of the NEXT image: host -> device on the context's copy stream into staging buffers, so that the PCIe
+// transfer runs under the image that is being computed. The next run(first = 0) waits for the transfer and moves
+// the staged inputs into place with device-to-device copies on the context's stream.
+int sampler_stage_inputs(flux_cuda_sampler *s, const float *z0, const float *ctx0, const float *ctx1,
+                         const float *const *ref_latents) {
+  if (!s || !z0 || !ctx0) {
+    set_error("stage_inputs: null argument");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  Workspace *ws = s->ws;
+  flux_cuda_ctx *c = s->model->ctx;
+  const ModelDims &d = s->model->d;
+  cudaSetDevice(c->device);
+  if ((ws->B == 2 && !ctx1) || (ws->refs.size() && !ref_latents)) {
+    set_error("stage_inputs: a context or the reference latents are missing");
+    return FLUX_CUDA_ERR_ARG;
+  }
+  const size_t C = d.latent_ch, ctx_n = static_cast<size_t>(ws->n_txt) * d.text_dim;
+  int rc = 0;
+  if (!c->copy_stream) rc = check_cuda(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking), "copy stream");
+  if (!rc && !ws->stage_z) {
+    rc = dev_alloc(ws->allocs, &ws->stage_z, C * ws->n_img);
+    if (!rc) rc = dev_alloc(ws->allocs, &ws->stage_ctx, static_cast<size_t>(ws->B) * ctx_n);
+    if (!rc) rc = dev_alloc(ws->allocs, &ws->stage_ref, C * static_cast<size_t>(ws->n_ref ? ws->n_ref : 1));
+    if (!rc) rc = check_cuda(cudaEventCreateWithFlags(&ws->ev_staged, cudaEventDisableTiming), "cudaEventCreate");
+    if (!rc) rc = check_cuda(cudaEventCreateWithFlags(&ws->ev_stage_free, cudaEventDisableTiming), "cudaEventCreate");
+  }
+  if (rc) return rc;
+  cudaStream_t cs = c->copy_stream;
+  // the staging buffers are free once the previous staged inputs have been moved into place
+  if (ws->stage_used) rc = check_cuda(cudaStreamWaitEvent(cs, ws->ev_stage_free, 0), "stage wait");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->stage_z, z0, C * ws->n_img * 4, cudaMemcpyDefault, cs), "stage z");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->stage_ctx, ctx0, ctx_n * 4, cudaMemcpyDefault, cs), "stage ctx");
+  if (!rc && ws->B == 2)
+    rc = check_cuda(cudaMemcpyAsync(ws->stage_ctx + ctx_n, ctx1, ctx_n * 4, cudaMemcpyDefault, cs), "stage ctx");
+  size_t off = 0;
+  for (size_t i = 0; !rc && i < ws->refs.size(); ++i) {
+    const size_t n = static_cast<size_t>(ws->refs[i].h) * ws->refs[i].w;
+    if (!ref_latents[i]) {
+      set_error("stage_inputs: reference latent %zu is null", i);
+      return FLUX_CUDA_ERR_ARG;
+    }
+    rc = check_cuda(cudaMemcpyAsync(ws->stage_ref + off * C, ref_latents[i], C * n * 4, cudaMemcpyDefault, cs), "stage ref");
+    off += n;
+  }
+  if (!rc) rc = check_cuda(cudaEventRecord(ws->ev_staged, cs), "stage record");
+  if (!rc) ws->staged_pending = true;
+  return rc;
+}
+
+// Moves staged inputs into place (called by run at first == 0), ordered on the context's stream.
+static int consume_staged(flux_cuda_sampler *s) {
+  Workspace *ws = s->ws;
+  if (!ws->staged_pending) return 0;
+  const ModelDims &d = s->model->d;
+  cudaStream_t st = s->model->ctx->stream;
+  const size_t C = d.latent_ch, ctx_n = static_cast<size_t>(ws->B) * ws->n_txt * d.text_dim;
+  int rc = check_cuda(cudaStreamWaitEvent(st, ws->ev_staged, 0), "staged wait");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->z_in, ws->stage_z, C * ws->n_img * 4, cudaMemcpyDeviceToDevice, st), "staged z");
+  if (!rc) rc = check_cuda(cudaMemcpyAsync(ws->ctx_in, ws->stage_ctx, ctx_n * 4, cudaMemcpyDeviceToDevice, st), "staged ctx");
+  if (!rc && ws->n_ref)
+    rc = check_cuda(cudaMemcpyAsync(ws->ref_in, ws->stage_ref, C * ws->n_ref * 4, cudaMemcpyDeviceToDevice, st), "staged ref");
+  if (!rc) rc = check_cuda(cudaEventRecord(ws->ev_stage_free, st), "staged record");
+  ws->staged_pending = false;
+  ws->stage_used = true;
+  return rc;
+}
+
+// Device -> host copy of the latent, ordered on the context's stream; does not wait (flux_cuda_ctx_sync does).
+int sampler_download_async(flux_cuda_sampler *s, float *latent_out) {
+  if (!s || !latent_out) return FLUX_CUDA_ERR_ARG;
+  flux_cuda_model *m = s->model;
+  cudaSetDevice(m->ctx->device);
+  const size_t n = static_cast<size_t>(m->d.latent_ch) * s->ws->n_img;
+  return check_cuda(cudaMemcpyAsync(latent_out, s->ws->z, n * 4, cudaMemcpyDeviceToHost, m->ctx->stream), "download");
+}
+
 int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
                 int record_velocities, int apply_update) {
   if (!s || !schedule || num_steps < 1 || first < 0 || count < 1 || first + count > num_steps) {
@@ -920,6 +1000,8 @@ int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int 
   ws->last_steps = num_steps;
   cudaEventRecord(ws->ev0, st);
   int rc = 0;
+  if (first == 0) rc = consume_staged(s);
+  if (rc) return rc;
   if (first == 0)
     // A copy from pageable memory returns once the source has been staged, so `schedule` is free on return and
     // no host synchronisation is needed between consecutive runs. It stays outside the captured graph because a

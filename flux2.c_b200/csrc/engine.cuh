@@ -77,6 +77,10 @@ struct Workspace {
   __nv_bfloat16 *norm = nullptr, *qkv = nullptr, *cat = nullptr, *tok = nullptr, *ctx_bf = nullptr;
   float *z = nullptr, *v = nullptr, *vcomb = nullptr, *vel_rec = nullptr;
   float *z_in = nullptr, *ctx_in = nullptr, *ref_in = nullptr;  // raw uploads
+  // inputs of the NEXT image, copied in on the context's copy stream while the current image runs
+  float *stage_z = nullptr, *stage_ctx = nullptr, *stage_ref = nullptr;
+  cudaEvent_t ev_staged = nullptr, ev_stage_free = nullptr;
+  bool staged_pending = false, stage_used = false;
   float *sched = nullptr, *tsin = nullptr, *th = nullptr, *svec = nullptr, *mod = nullptr;
   float *rope_cos = nullptr, *rope_sin = nullptr;
   float *rope_ang = nullptr;  // [N, 64]: rotation angle of every consecutive pair, reduced to [-pi, pi]
@@ -134,6 +138,9 @@ int sampler_upload(flux_cuda_sampler *s, const float *z0, const float *ctx0, con
 int sampler_run(flux_cuda_sampler *s, const float *schedule, int num_steps, int first, int count, float guidance,
                 int record_velocities, int apply_update);
 int sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
+int sampler_stage_inputs(flux_cuda_sampler *s, const float *z0, const float *ctx0, const float *ctx1,
+                         const float *const *ref_latents);
+int sampler_download_async(flux_cuda_sampler *s, float *latent_out);
 // Sums the event pairs of the last profiled run per kernel class (call after a sync).
 int sampler_profile(flux_cuda_sampler *s, float *ms_by_class, long long *launches_by_class);
 // The same event pairs summed per BlockGroup.

@@ -197,6 +197,18 @@ int flux_cuda_sampler_velocity(flux_cuda_sampler *s, float *dst_dev, float scale
 int flux_cuda_sampler_apply_velocity(flux_cuda_sampler *s, const float *v_dev, int step);
 /* Device -> host copy of the latent (and recorded velocities), then waits and checks for kernel errors. */
 int flux_cuda_sampler_download(flux_cuda_sampler *s, float *latent_out, float *velocities_out);
+/*
+ * Pipelined generation of many images with one sampler (no counterpart in the reference, which generates one image
+ * per call): flux_cuda_sampler_stage_inputs copies the inputs of the NEXT image to the device on a second stream
+ * while the current image is being computed (pinned host memory makes that a real overlap; the buffers must stay
+ * valid until the next run has been queued and the stream synchronised past it); the next flux_cuda_sampler_run
+ * picks them up. flux_cuda_sampler_download_async queues the device -> host copy of the latent behind the run
+ * and returns; flux_cuda_ctx_sync waits for everything and reports kernel errors. Arguments as for
+ * flux_cuda_sampler_upload.
+ */
+int flux_cuda_sampler_stage_inputs(flux_cuda_sampler *s, const float *z0, const float *ctx, const float *ctx_uncond,
+                                   const float *const *ref_latents);
+int flux_cuda_sampler_download_async(flux_cuda_sampler *s, float *latent_out);
 /* CUDA-event time of the last flux_cuda_sampler_run in ms (valid after a sync), and its kernel count. */
 int flux_cuda_sampler_last_run(flux_cuda_sampler *s, float *ms, long long *kernel_launches);
 

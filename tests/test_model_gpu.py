@@ -276,6 +276,45 @@ def test_klein_loop_repeats_itself_bit_for_bit(klein, synth, fx):
     assert np.array_equal(model.sample(z0, h, w, c, sch), first)  # after a different shape of work in between
 
 
+def test_pipelined_generation_matches_one_image_at_a_time(tiny, synth, fx, ctx):
+    """flux_cuda_sampler_stage_inputs / download_async: the inputs of the next image cross on the copy stream while
+    the current one runs, downloads are queued behind the runs, one wait at the end. Same latents, bit for bit, as
+    upload / run / download per image - with and without a reference image, and when the two styles are mixed."""
+    import torch
+    d, W, model, om = tiny
+    h, w, ntxt, n = 8, 8, 64, 5
+    sch = fx.official_schedule(4, h * w)
+    for refs in ((), ((3, 4, 10),)):
+        zs = torch.stack([torch.from_numpy(synth.make_latent(100 + i, d.latent_ch, h, w)).reshape(-1) for i in range(n)]).pin_memory()
+        cs = torch.stack([torch.from_numpy(synth.make_context(200 + i, ntxt, d.text_dim)).reshape(-1) for i in range(n)]).pin_memory()
+        rs = torch.stack([torch.from_numpy(synth.make_latent(300 + i, d.latent_ch, 3, 4)).reshape(-1) for i in range(n)]).pin_memory()
+        rp = (lambda i: (rs[i].data_ptr(),)) if refs else (lambda i: ())
+        s = fx.Sampler(model, h, w, ntxt, ref_shapes=refs, batch=1, max_steps=4)
+        try:
+            want = torch.zeros(n, zs.shape[1]).pin_memory()
+            for i in range(n):
+                s.upload(zs[i].data_ptr(), cs[i].data_ptr(), None, rp(i))
+                s.run(sch)
+                s.download(want[i].data_ptr())
+            got = torch.zeros_like(want).pin_memory()
+            s.stage_inputs(zs[0].data_ptr(), cs[0].data_ptr(), None, rp(0))
+            for i in range(n):
+                s.run(sch)
+                if i + 1 < n:
+                    s.stage_inputs(zs[i + 1].data_ptr(), cs[i + 1].data_ptr(), None, rp(i + 1))
+                s.download_async(got[i].data_ptr())
+            ctx.sync()
+            assert torch.equal(got, want)
+            # a plain upload after staged ones: nothing stale is picked up
+            s.upload(zs[2].data_ptr(), cs[2].data_ptr(), None, rp(2))
+            s.run(sch)
+            one = torch.zeros(zs.shape[1]).pin_memory()
+            s.download(one.data_ptr())
+            assert torch.equal(one, want[2])
+        finally:
+            s.close()
+
+
 def test_upload_paths_give_the_same_weights(synth, fx, monkeypatch):
     """Weights go to the device through a ring of pinned buffers filled by host threads (one tensor here spans several
     32 MB slots and several threads); FLUX_CUDA_UPLOAD_THREADS=0 is the plain pageable copy. Same model either way."""
