@@ -2,14 +2,15 @@
 """Benchmark of the B200 denoising engine on the reference's headline workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|attn|adaln|qwen3|vae|conv|gn|load [...]            # one kernel, small memory (for ncu captures)
+    python bench.py --micro gemm|gemmtable|attn|adaln|qwen3|vae|conv|gn|load|step [...]   # one kernel or stage, small memory
 
 Workload ("step" = one image): FLUX.2-klein-4B-shaped DiT, seeded random bf16 weights N(0, 0.02), 512x512 output
-(1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1, noise
-seed 42. Metric: images/s (whole job). With N > 1 (launched by torchrun, one rank per GPU) every rank holds a
+(1024 image tokens + 512 text tokens), batch 1, 4-step Euler loop on the official schedule, guidance 1; image i of
+the job has noise seed i and the context of seed 10000 + i. Metric: images/s (whole job). With N > 1 (launched by torchrun, one rank per GPU) every rank holds a
 full replica and denoises its own images: independent seeds, no collective on the data path, weak scaling.
 
-The JSON line also carries the end-to-end figure through the library's host-buffer API (`e2e`), the roofline of
+The JSON line also carries the end-to-end figure through the library's host-buffer API (`e2e`: uploads and downloads
+inside the timed region, pipelined; the one-image-at-a-time figure beside it), the roofline of
 the dominant kernel (`roofline`) and the reference's CPU path timed on this machine's host cores
 (`cpu_baseline`). `--impl reference` times the reference's own CPU implementation (oracle/_ref, built from the
 reference's sources by oracle/Makefile) instead.
